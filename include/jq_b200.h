@@ -1,0 +1,173 @@
+/*
+ * jq_b200 -- C ABI of the B200 (sm_100a) Q4_0 x Q8_1 quantized-linear path.
+ *
+ * A drop-in for the two quantization operators of JJJetson_Ops:
+ *   src/cuda/q8_1.cu            (activation quantizer, fp32 -> block_q8_1_mmq)
+ *   src/cuda/mm_q4_0_q8_1.cu    (Q4_0 weights x Q8_1 activations -> fp32)
+ * Every entry point is extern "C", takes plain pointers and sizes, returns a jq_status
+ * (never exits the process, unlike CUDA_CHECK in the reference's include/cuda_utils.h:10-28)
+ * and leaves a human-readable message in jq_last_error() when it fails.
+ *
+ * Data layouts are the reference's, byte for byte:
+ *   Q4_0 block  (mm_q4_0_q8_1.cu:35-38): 18 bytes = fp16 d, then 16 bytes; byte j holds
+ *               weight j in its low nibble and weight j+16 in its high nibble;
+ *               value = (q - 8) * d.  W is N rows of K/32 consecutive blocks.
+ *   Q8_1 block  (q8_1.cu:14-18, block_q8_1_mmq): 144 bytes = 4 x (fp16 d, fp16 s), then
+ *               128 int8; four 32-value groups share one block.
+ *   X is M rows of K floats (K fastest); Y is M rows of N floats (y[m*N + n],
+ *   mm_q4_0_q8_1.cu:286).
+ *
+ * "Device" entry points are asynchronous on the given stream, allocate nothing and never
+ * synchronise.  "Host" entry points take host pointers and do the allocate / copy / launch /
+ * copy back / free round trip the reference's *_host style wrappers do.
+ */
+#ifndef JQ_B200_H_
+#define JQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum jq_status {
+    JQ_OK = 0,
+    JQ_ERR_INVALID_ARG = 1, /* null pointer, negative size, unknown enum value */
+    JQ_ERR_SHAPE = 2,       /* K not a multiple of 32 (quantize) or 128 (multiply) */
+    JQ_ERR_ALIGN = 3,       /* a pointer lacks the alignment its layout needs */
+    JQ_ERR_CUDA = 4,        /* a CUDA runtime call failed; jq_last_error() names it */
+    JQ_ERR_UNSUPPORTED = 5, /* no kernel for this request on this device */
+    JQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out (see jq_device_fault) */
+    JQ_ERR_TOO_LARGE = 7    /* the request exceeds a stated fixed capacity */
+} jq_status;
+
+/* Order of the 144-byte activation blocks in memory for M > 1.  The two reference kernels
+ * disagree: the quantizer writes block (k/128) * M + m (q8_1.cu:84-86, pinned by
+ * tests/test_q8_1.py:33) while the multiply reads block m * (K/128) + k/128
+ * (mm_q4_0_q8_1.cu:230,246).  They coincide for M == 1.  Both are supported. */
+typedef enum jq_q8_order {
+    JQ_ORDER_KSUPER_COL = 0, /* what q8_1() writes */
+    JQ_ORDER_COL_KSUPER = 1  /* what mat_mul_q4_0_q8_1_device() reads */
+} jq_q8_order;
+
+/* Meaning of the second fp16 of each (d, s) pair. */
+typedef enum jq_s_mode {
+    JQ_S_SUM_X = 0,  /* s = fp16(sum of the 32 input floats): the reference, q8_1.cu:62-68,102 */
+    JQ_S_D_SUM_Q = 1 /* s = fp16(fp16(d) * sum of the 32 int8): makes d4*(d8*sumi - 8*s) equal
+                        dequantise-then-matmul up to fp16 rounding of s */
+} jq_s_mode;
+
+/* Kernel families of the multiply; JQ_KERNEL_AUTO picks by shape. */
+typedef enum jq_kernel {
+    JQ_KERNEL_AUTO = 0,
+    JQ_KERNEL_GENERIC = 1,   /* any shape, plain loads; the safety net */
+    JQ_KERNEL_GEMV_DP4A = 2, /* M <= 2: bulk-copy ring, dp4a, warp per row */
+    JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
+    JQ_KERNEL_GEMM_MMA = 4   /* M > 8: tiled int8 tensor-core GEMM with per-block rescale */
+} jq_kernel;
+
+const char *jq_status_string(int status);
+/* Message of the last failure on the calling thread ("" if none). */
+const char *jq_last_error(void);
+int jq_version(void);
+
+/* Bytes of block_q8_1_mmq storage for M rows of K values: M * ceil(K/128) * 144
+ * (the n_blocks rule of q8_1.cu:160). */
+size_t jq_q8_1_bytes(int64_t K, int64_t M);
+/* Bytes of Q4_0 storage for N rows of K values: N * K/32 * 18. */
+size_t jq_q4_0_bytes(int64_t N, int64_t K);
+
+/* ---- device entry points -------------------------------------------------------------- */
+
+/* Replaces the kernel launch inside q8_1() (q8_1.cu:172-183, quantize_q8_1_kernel :20-104).
+ * d_x: M*K floats.  d_xq: jq_q8_1_bytes(K, M) bytes, 16-byte aligned.  K % 32 == 0; groups of a
+ * trailing partial 128-block are zero-filled.  An all-zero group stores d = 0 (the reference
+ * stores fp16(1/0) = +inf there, which poisons the multiply with NaN). */
+int jq_quantize_q8_1_device(void *stream, const float *d_x, void *d_xq, int64_t K, int64_t M,
+                            int order, int s_mode);
+
+/* Replaces mat_mul_q4_0_q8_1_device (mm_q4_0_q8_1.cu:394-398, contract :382-392).
+ * d_w: N*K/32 Q4_0 blocks.  d_xq: activations already in block_q8_1_mmq form, in `order`.
+ * d_y: M*N floats.  K % 128 == 0 (the check of mm_q4_0_q8_1.cu:335-340). */
+int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq, float *d_y,
+                                int64_t K, int64_t N, int64_t M, int order);
+
+/* Same, with the kernel family forced (for tests and benchmarks). */
+int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_xq, float *d_y,
+                                   int64_t K, int64_t N, int64_t M, int order, int kernel);
+
+/* Quantize + multiply in one call: what mat_mul_q4_0_q8_1 (mm_q4_0_q8_1.cu:318-380) does
+ * between its copies.  d_x: M*K floats.  d_ws: jq_q8_1_bytes(K, M) bytes of scratch that
+ * receives the quantized activations (JQ_ORDER_COL_KSUPER) as a side effect, like the
+ * reference's quant_workspace (:352).  For M <= 8 the quantization runs inside the multiply
+ * kernel's prologue. */
+int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y,
+                          int64_t K, int64_t N, int64_t M, int s_mode);
+
+/* Parity aid: the exact int32 dot product of every (row n, 32-wide block kb, column m),
+ * d_sums[(m*N + n)*(K/32) + kb], i.e. `sumi` of q4_0_q8_1_vec_dot_impl (mm_q4_0_q8_1.cu:71-93)
+ * before any scale is applied.  The reference never exposes it. */
+int jq_block_sums_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq, int32_t *d_sums,
+                                   int64_t K, int64_t N, int64_t M, int order);
+
+/* fp32 [N][K] -> Q4_0.  The reference has no weight quantizer; this is the ggml rule its block
+ * layout comes from (d = signed max-magnitude / -8, q = min(15, trunc(w/d + 8.5))). */
+int jq_quantize_q4_0_device(void *stream, const float *d_w, void *d_wq, int64_t N, int64_t K);
+
+/* Non-zero after a kernel of this library gave up on a bounded wait on the current device.
+ * Synchronises the device.  `clear` != 0 resets it. */
+int jq_device_fault(int clear, int *fault_out);
+
+/* ---- host entry points (reference-facing) ------------------------------------------------ */
+
+/* q8_1() (q8_1.cu:148-193) with a C signature: dims = {K, M, ne2, ne3}; writes
+ * M*ceil(K/128) blocks in JQ_ORDER_KSUPER_COL order with s = sum(x). */
+int jq_q8_1_host(const float *input, uint8_t *output, const int *dims, int ndims);
+
+/* parse_q8_1_output (q8_1.cu:197-216). */
+int jq_parse_q8_1_output(const uint8_t *input, int8_t *qs_out, float *scale_out, float *sum_out,
+                         int64_t n_blocks);
+
+/* mat_mul_q4_0_q8_1 (mm_q4_0_q8_1.cu:318-380): host weights, host activations, host outputs;
+ * quant_workspace receives the quantized activations exactly as q8_1() writes them.
+ * Unlike the reference, M > 1 gives the mathematically right product (the reference's two
+ * kernels disagree on block order there). */
+int jq_mat_mul_q4_0_q8_1_host(const void *weight_q4_0, const float *input, uint8_t *quant_workspace,
+                              float *output, const int *input_dims, int ndims, int nrows_out,
+                              int ncols_k);
+
+/* Same with the meaning of the stored `s` chosen (the plain entry uses JQ_S_SUM_X like the reference). */
+int jq_mat_mul_q4_0_q8_1_host_ex(const void *weight_q4_0, const float *input, uint8_t *quant_workspace,
+                                 float *output, const int *input_dims, int ndims, int nrows_out,
+                                 int ncols_k, int s_mode);
+
+/* Weights kept resident on the current device, for callers that run many multiplies. */
+typedef struct jq_weights jq_weights;
+int jq_weights_create(const void *host_w_q4_0, int64_t N, int64_t K, jq_weights **out);
+int jq_weights_destroy(jq_weights *w);
+const void *jq_weights_device_ptr(const jq_weights *w);
+/* x (host, M*K floats) -> y (host, M*N floats); pinned host buffers make the copies async.
+ * quant_workspace may be NULL. */
+int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace, float *y,
+                        int64_t M, int s_mode);
+
+/* ---- device description (include/device_hw_info.cuh:113-250 of the reference) ------------- */
+typedef struct jq_device_hw_info {
+    char name[256];
+    int device_id, cc_major, cc_minor, sm_count;
+    int sm_clock_khz, mem_clock_khz, mem_bus_width_bits;
+    int fp32_cores_per_sm, warp_schedulers_per_sm, max_warps_per_sm;
+    size_t smem_per_sm, smem_per_block_optin, l2_bytes, global_mem_bytes;
+    double peak_fp32_tflops;      /* 2 * cores * clock */
+    double peak_dram_gbs;         /* nominal, from the table for the chip when known */
+    double peak_int8_dense_tops;  /* nominal dense int8 tensor throughput, 0 if unknown */
+    double peak_bf16_dense_tflops;
+    double ridge_int8_ops_per_byte;
+} jq_device_hw_info;
+int jq_query_device_hw_info(int device, jq_device_hw_info *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JQ_B200_H_ */

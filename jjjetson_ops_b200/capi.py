@@ -1,0 +1,231 @@
+"""ctypes binding of ``libjq_b200.so`` with torch tensors as device memory.
+
+Every function here is a direct call through the C ABI declared in ``include/jq_b200.h``; torch
+only provides allocations and the current stream.  The library is loaded at import time and a
+missing build is an error, never a fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libjq_b200.so")
+
+OK = 0
+ERR_INVALID_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_TOO_LARGE = range(1, 8)
+ORDER_KSUPER_COL, ORDER_COL_KSUPER = 0, 1
+S_SUM_X, S_D_SUM_Q = 0, 1
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV_DP4A, KERNEL_GEMV_MMA, KERNEL_GEMM_MMA = range(5)
+KERNEL_NAMES = {
+    KERNEL_AUTO: "auto",
+    KERNEL_GENERIC: "generic",
+    KERNEL_GEMV_DP4A: "gemv_dp4a",
+    KERNEL_GEMV_MMA: "gemv_mma",
+    KERNEL_GEMM_MMA: "gemm_mma",
+}
+
+Q4_BYTES = 18
+Q8_BYTES = 144
+
+
+class JqError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__("jq status %d (%s): %s" % (status, status_string(status), message))
+        self.status = status
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "%s is missing: build it with `python -m jjjetson_ops_b200._build` "
+        "(there is no CPU or PyTorch fallback for this path)" % LIB_PATH
+    )
+_lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i64, _ci, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+_SIGS = {
+    "jq_status_string": (ctypes.c_char_p, [_ci]),
+    "jq_last_error": (ctypes.c_char_p, []),
+    "jq_version": (_ci, []),
+    "jq_q8_1_bytes": (_sz, [_i64, _i64]),
+    "jq_q4_0_bytes": (_sz, [_i64, _i64]),
+    "jq_quantize_q8_1_device": (_ci, [_vp, _vp, _vp, _i64, _i64, _ci, _ci]),
+    "jq_mul_mat_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_mul_mat_q4_0_q8_1_device_ex": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, _ci]),
+    "jq_linear_q4_0_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_block_sums_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_quantize_q4_0_device": (_ci, [_vp, _vp, _vp, _i64, _i64]),
+    "jq_device_fault": (_ci, [_ci, ctypes.POINTER(_ci)]),
+    "jq_q8_1_host": (_ci, [_vp, _vp, ctypes.POINTER(_ci), _ci]),
+    "jq_parse_q8_1_output": (_ci, [_vp, _vp, _vp, _vp, _i64]),
+    "jq_mat_mul_q4_0_q8_1_host": (_ci, [_vp, _vp, _vp, _vp, ctypes.POINTER(_ci), _ci, _ci, _ci]),
+    "jq_mat_mul_q4_0_q8_1_host_ex": (_ci, [_vp, _vp, _vp, _vp, ctypes.POINTER(_ci), _ci, _ci, _ci, _ci]),
+    "jq_weights_create": (_ci, [_vp, _i64, _i64, ctypes.POINTER(_vp)]),
+    "jq_weights_destroy": (_ci, [_vp]),
+    "jq_weights_device_ptr": (_vp, [_vp]),
+    "jq_linear_q4_0_host": (_ci, [_vp, _vp, _vp, _vp, _i64, _ci]),
+    "jq_query_device_hw_info": (_ci, [_ci, _vp]),
+}
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(_lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def lib() -> ctypes.CDLL:
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return _lib.jq_status_string(status).decode()
+
+
+def last_error() -> str:
+    return _lib.jq_last_error().decode()
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise JqError(status, last_error())
+
+
+def q8_1_bytes(K: int, M: int) -> int:
+    return int(_lib.jq_q8_1_bytes(K, M))
+
+
+def q4_0_bytes(N: int, K: int) -> int:
+    return int(_lib.jq_q4_0_bytes(N, K))
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dev(t: torch.Tensor, dtype: torch.dtype, name: str) -> int:
+    if not t.is_cuda or t.dtype != dtype or not t.is_contiguous():
+        raise ValueError("%s must be a contiguous CUDA tensor of dtype %s" % (name, dtype))
+    return t.data_ptr()
+
+
+def quantize_q8_1(x: torch.Tensor, order: int = ORDER_COL_KSUPER, s_mode: int = S_SUM_X,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``[M, K]`` -> raw ``block_q8_1_mmq`` bytes on the same device."""
+    M, K = x.shape
+    if out is None:
+        out = torch.empty(q8_1_bytes(K, M), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.jq_quantize_q8_1_device(_stream(x), _dev(x, torch.float32, "x"), _dev(out, torch.uint8, "out"),
+                                           K, M, order, s_mode))
+    return out
+
+
+def mul_mat_q4_0_q8_1(w: torch.Tensor, xq: torch.Tensor, K: int, N: int, M: int,
+                      order: int = ORDER_COL_KSUPER, kernel: int = KERNEL_AUTO,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Q4_0 weights x Q8_1 activations -> fp32 ``[M, N]``."""
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.jq_mul_mat_q4_0_q8_1_device_ex(_stream(w), _dev(w, torch.uint8, "w"), _dev(xq, torch.uint8, "xq"),
+                                                  _dev(out, torch.float32, "out"), K, N, M, order, kernel))
+    return out
+
+
+def linear_q4_0(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = S_D_SUM_Q,
+                ws: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 activations ``[M, K]`` -> quantize -> multiply -> fp32 ``[M, N]`` in one call."""
+    M, K = x.shape
+    if ws is None:
+        ws = torch.empty(max(q8_1_bytes(K, M), 16), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.jq_linear_q4_0_device(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
+                                         _dev(ws, torch.uint8, "ws"), _dev(out, torch.float32, "out"), K, N, M, s_mode))
+    return out
+
+
+def block_sums(w: torch.Tensor, xq: torch.Tensor, K: int, N: int, M: int,
+               order: int = ORDER_COL_KSUPER) -> torch.Tensor:
+    """Exact int32 block dot products ``[M, N, K/32]``."""
+    out = torch.empty((M, N, K // 32), dtype=torch.int32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.jq_block_sums_q4_0_q8_1_device(_stream(w), _dev(w, torch.uint8, "w"), _dev(xq, torch.uint8, "xq"),
+                                                  _dev(out, torch.int32, "out"), K, N, M, order))
+    return out
+
+
+def quantize_q4_0(w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``[N, K]`` -> Q4_0 bytes ``[N, K/32*18]``."""
+    N, K = w.shape
+    if out is None:
+        out = torch.empty((N, K // 32 * Q4_BYTES), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.jq_quantize_q4_0_device(_stream(w), _dev(w, torch.float32, "w"), _dev(out, torch.uint8, "out"), N, K))
+    return out
+
+
+def device_fault(clear: bool = True) -> int:
+    v = ctypes.c_int(0)
+    check(_lib.jq_device_fault(1 if clear else 0, ctypes.byref(v)))
+    return int(v.value)
+
+
+class DeviceHwInfo(ctypes.Structure):
+    _fields_ = [
+        ("name", ctypes.c_char * 256),
+        ("device_id", _ci), ("cc_major", _ci), ("cc_minor", _ci), ("sm_count", _ci),
+        ("sm_clock_khz", _ci), ("mem_clock_khz", _ci), ("mem_bus_width_bits", _ci),
+        ("fp32_cores_per_sm", _ci), ("warp_schedulers_per_sm", _ci), ("max_warps_per_sm", _ci),
+        ("smem_per_sm", _sz), ("smem_per_block_optin", _sz), ("l2_bytes", _sz), ("global_mem_bytes", _sz),
+        ("peak_fp32_tflops", ctypes.c_double), ("peak_dram_gbs", ctypes.c_double),
+        ("peak_int8_dense_tops", ctypes.c_double), ("peak_bf16_dense_tflops", ctypes.c_double),
+        ("ridge_int8_ops_per_byte", ctypes.c_double),
+    ]
+
+    def as_dict(self) -> dict:
+        d = {}
+        for f, _ in self._fields_:
+            v = getattr(self, f)
+            d[f] = v.decode() if isinstance(v, bytes) else v
+        return d
+
+
+def query_device_hw_info(device: int = 0) -> dict:
+    info = DeviceHwInfo()
+    check(_lib.jq_query_device_hw_info(device, ctypes.byref(info)))
+    return info.as_dict()
+
+
+class ResidentWeights:
+    """Host-facing linear with the weights uploaded once (``jq_weights_*`` of the C ABI)."""
+
+    def __init__(self, w_q4_0_host, N: int, K: int):
+        import numpy as np
+
+        w = np.ascontiguousarray(w_q4_0_host, dtype=np.uint8)
+        assert w.nbytes >= q4_0_bytes(N, K)
+        self.N, self.K = N, K
+        self._h = _vp()
+        check(_lib.jq_weights_create(w.ctypes.data, N, K, ctypes.byref(self._h)))
+
+    @property
+    def device_ptr(self) -> int:
+        return int(_lib.jq_weights_device_ptr(self._h) or 0)
+
+    def linear(self, x_host_ptr: int, y_host_ptr: int, M: int, s_mode: int = S_D_SUM_Q, ws_host_ptr: int = 0) -> None:
+        check(_lib.jq_linear_q4_0_host(self._h, x_host_ptr, ws_host_ptr or None, y_host_ptr, M, s_mode))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.jq_weights_destroy(self._h)
+            self._h = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

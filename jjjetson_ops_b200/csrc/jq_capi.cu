@@ -1,0 +1,494 @@
+// C ABI of the library: argument checking, kernel selection, the reference-style host wrappers,
+// resident weights, and the device description.  Declarations and the reference lines each entry
+// point replaces are in include/jq_b200.h.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "jq_common.cuh"
+
+namespace jq {
+
+namespace {
+
+thread_local std::string t_last_error;
+
+__device__ int g_device_fault_word = 0;
+
+constexpr int MAX_DEVICES = 64;
+struct PerDevice {
+    bool caps_ok = false;
+    DeviceCaps caps;
+    int *fault_ptr = nullptr;
+    bool fault_ok = false;
+};
+PerDevice g_dev[MAX_DEVICES];
+std::mutex g_dev_mutex;
+
+}  // namespace
+
+int set_error(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+    return status;
+}
+
+int cuda_error(cudaError_t e, const char *what) {
+    return set_error(JQ_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+
+int device_caps(DeviceCaps *out) {
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return set_error(JQ_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    PerDevice &d = g_dev[dev];
+    if (!d.caps_ok) {
+        int major = 0, minor = 0;
+        JQ_CUDA_TRY(cudaDeviceGetAttribute(&d.caps.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        JQ_CUDA_TRY(cudaDeviceGetAttribute(&d.caps.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        JQ_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        JQ_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+        d.caps.cc = major * 10 + minor;
+        d.caps_ok = true;
+    }
+    *out = d.caps;
+    return JQ_OK;
+}
+
+int *device_fault_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    PerDevice &d = g_dev[dev];
+    if (!d.fault_ok) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_fault_word) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        d.fault_ptr = static_cast<int *>(p);
+        d.fault_ok = true;
+    }
+    return d.fault_ptr;
+}
+
+namespace {
+
+int check_order(int order) {
+    if (order != JQ_ORDER_KSUPER_COL && order != JQ_ORDER_COL_KSUPER)
+        return set_error(JQ_ERR_INVALID_ARG, "unknown Q8_1 block order %d", order);
+    return JQ_OK;
+}
+int check_s_mode(int s_mode) {
+    if (s_mode != JQ_S_SUM_X && s_mode != JQ_S_D_SUM_Q)
+        return set_error(JQ_ERR_INVALID_ARG, "unknown s_mode %d", s_mode);
+    return JQ_OK;
+}
+
+int check_mul_mat_shape(int64_t K, int64_t N, int64_t M) {
+    if (K < 0 || N < 0 || M < 0) return set_error(JQ_ERR_INVALID_ARG, "negative size (K=%lld N=%lld M=%lld)", (long long)K, (long long)N, (long long)M);
+    // the two checks of mat_mul_q4_0_q8_1 (mm_q4_0_q8_1.cu:331-340)
+    if (K % QK != 0) return set_error(JQ_ERR_SHAPE, "ncols_k must be multiple of %d", QK);
+    if (K % SUPER != 0) return set_error(JQ_ERR_SHAPE, "ncols_k must be multiple of %d for block_q8_1_mmq", SUPER);
+    if (K > (int64_t)1 << 30 || N > (int64_t)1 << 31 || M > (int64_t)1 << 31)
+        return set_error(JQ_ERR_TOO_LARGE, "shape exceeds 32-bit kernel indexing");
+    return JQ_OK;
+}
+
+int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N,
+                     int64_t M, int order, int kernel) {
+    if (N == 0 || M == 0) return JQ_OK;
+    if (K == 0) {
+        JQ_CUDA_TRY(cudaMemsetAsync(d_y, 0, (size_t)M * N * sizeof(float), st));
+        return JQ_OK;
+    }
+    switch (kernel) {
+        case JQ_KERNEL_GENERIC: return launch_mmq_generic(st, d_w, d_xq, d_y, K, N, M, order);
+        case JQ_KERNEL_GEMV_DP4A: return launch_gemv_dp4a(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
+        case JQ_KERNEL_GEMV_MMA: return launch_gemv_mma(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
+        case JQ_KERNEL_GEMM_MMA: return launch_gemm_mma(st, d_w, d_xq, d_y, K, N, M, order);
+        case JQ_KERNEL_AUTO: break;
+        default: return set_error(JQ_ERR_INVALID_ARG, "unknown kernel family %d", kernel);
+    }
+    int rc = JQ_ERR_UNSUPPORTED;
+    if (M <= 2) rc = launch_gemv_dp4a(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
+    if (rc == JQ_ERR_UNSUPPORTED && M <= 8) rc = launch_gemv_mma(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
+    if (rc == JQ_ERR_UNSUPPORTED && M > 8) rc = launch_gemm_mma(st, d_w, d_xq, d_y, K, N, M, order);
+    if (rc == JQ_ERR_UNSUPPORTED) rc = launch_mmq_generic(st, d_w, d_xq, d_y, K, N, M, order);
+    if (rc == JQ_OK) t_last_error.clear();
+    return rc;
+}
+
+}  // namespace
+}  // namespace jq
+
+using namespace jq;
+
+extern "C" {
+
+const char *jq_status_string(int status) {
+    switch (status) {
+        case JQ_OK: return "ok";
+        case JQ_ERR_INVALID_ARG: return "invalid argument";
+        case JQ_ERR_SHAPE: return "unsupported shape";
+        case JQ_ERR_ALIGN: return "misaligned pointer";
+        case JQ_ERR_CUDA: return "CUDA runtime error";
+        case JQ_ERR_UNSUPPORTED: return "unsupported on this path";
+        case JQ_ERR_TIMEOUT: return "device-side wait timed out";
+        case JQ_ERR_TOO_LARGE: return "request exceeds capacity";
+        default: return "unknown status";
+    }
+}
+
+const char *jq_last_error(void) { return t_last_error.c_str(); }
+
+int jq_version(void) { return 100; }
+
+size_t jq_q8_1_bytes(int64_t K, int64_t M) {
+    if (K <= 0 || M <= 0) return 0;
+    return (size_t)M * (size_t)((K + SUPER - 1) / SUPER) * Q8_BYTES;
+}
+
+size_t jq_q4_0_bytes(int64_t N, int64_t K) {
+    if (K <= 0 || N <= 0) return 0;
+    return (size_t)N * (size_t)(K / QK) * Q4_BYTES;
+}
+
+int jq_quantize_q8_1_device(void *stream, const float *d_x, void *d_xq, int64_t K, int64_t M, int order,
+                            int s_mode) {
+    if (K < 0 || M < 0) return set_error(JQ_ERR_INVALID_ARG, "negative size (K=%lld M=%lld)", (long long)K, (long long)M);
+    if (int rc = check_order(order)) return rc;
+    if (int rc = check_s_mode(s_mode)) return rc;
+    if (K % QK != 0) return set_error(JQ_ERR_SHAPE, "K = %lld is not a multiple of %d", (long long)K, QK);
+    if (K == 0 || M == 0) return JQ_OK;
+    if (d_x == nullptr || d_xq == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (((uintptr_t)d_x & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
+        return set_error(JQ_ERR_ALIGN, "activations and Q8_1 blocks must be 16-byte aligned");
+    return launch_quantize_q8_1(static_cast<cudaStream_t>(stream), d_x, d_xq, K, M, order, s_mode);
+}
+
+int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                                   int64_t N, int64_t M, int order, int kernel) {
+    if (int rc = check_mul_mat_shape(K, N, M)) return rc;
+    if (int rc = check_order(order)) return rc;
+    if (N == 0 || M == 0) return JQ_OK;
+    if (d_y == nullptr || (K > 0 && (d_w == nullptr || d_xq == nullptr)))
+        return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (((uintptr_t)d_w & 1u) != 0) return set_error(JQ_ERR_ALIGN, "Q4_0 blocks must be 2-byte aligned");
+    if (((uintptr_t)d_xq & 15u) != 0) return set_error(JQ_ERR_ALIGN, "Q8_1 blocks must be 16-byte aligned");
+    if (((uintptr_t)d_y & 3u) != 0) return set_error(JQ_ERR_ALIGN, "output must be 4-byte aligned");
+    return dispatch_mul_mat(static_cast<cudaStream_t>(stream), d_w, d_xq, d_y, K, N, M, order, kernel);
+}
+
+int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                                int64_t N, int64_t M, int order) {
+    return jq_mul_mat_q4_0_q8_1_device_ex(stream, d_w, d_xq, d_y, K, N, M, order, JQ_KERNEL_AUTO);
+}
+
+int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y, int64_t K,
+                          int64_t N, int64_t M, int s_mode) {
+    if (int rc = check_mul_mat_shape(K, N, M)) return rc;
+    if (int rc = check_s_mode(s_mode)) return rc;
+    if (M == 0) return JQ_OK;
+    if (K > 0 && (d_x == nullptr || d_ws == nullptr)) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (N > 0 && (d_y == nullptr || (K > 0 && d_w == nullptr))) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (((uintptr_t)d_x & 15u) != 0 || ((uintptr_t)d_ws & 15u) != 0)
+        return set_error(JQ_ERR_ALIGN, "activations and workspace must be 16-byte aligned");
+    if (((uintptr_t)d_w & 1u) != 0) return set_error(JQ_ERR_ALIGN, "Q4_0 blocks must be 2-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K > 0 && N > 0 && M <= 8) {
+        // decode regime: quantization runs in the multiply kernel's prologue
+        int rc = JQ_ERR_UNSUPPORTED;
+        if (M <= 2) rc = launch_gemv_dp4a(st, d_w, nullptr, d_x, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, s_mode);
+        if (rc == JQ_ERR_UNSUPPORTED)
+            rc = launch_gemv_mma(st, d_w, nullptr, d_x, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, s_mode);
+        if (rc != JQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (K > 0) {
+        if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
+    }
+    return dispatch_mul_mat(st, d_w, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO);
+}
+
+int jq_block_sums_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq, int32_t *d_sums, int64_t K,
+                                   int64_t N, int64_t M, int order) {
+    if (int rc = check_mul_mat_shape(K, N, M)) return rc;
+    if (int rc = check_order(order)) return rc;
+    if (N == 0 || M == 0 || K == 0) return JQ_OK;
+    if (d_w == nullptr || d_xq == nullptr || d_sums == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (((uintptr_t)d_xq & 15u) != 0) return set_error(JQ_ERR_ALIGN, "Q8_1 blocks must be 16-byte aligned");
+    return launch_block_sums(static_cast<cudaStream_t>(stream), d_w, d_xq, d_sums, K, N, M, order);
+}
+
+int jq_quantize_q4_0_device(void *stream, const float *d_w, void *d_wq, int64_t N, int64_t K) {
+    if (N < 0 || K < 0) return set_error(JQ_ERR_INVALID_ARG, "negative size");
+    if (K % QK != 0) return set_error(JQ_ERR_SHAPE, "K = %lld is not a multiple of %d", (long long)K, QK);
+    if (N == 0 || K == 0) return JQ_OK;
+    if (d_w == nullptr || d_wq == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_wq & 1u) != 0)
+        return set_error(JQ_ERR_ALIGN, "weights must be 16-byte aligned, Q4_0 output 2-byte aligned");
+    return launch_quantize_q4_0(static_cast<cudaStream_t>(stream), d_w, d_wq, N, K);
+}
+
+int jq_device_fault(int clear, int *fault_out) {
+    int *p = device_fault_ptr();
+    if (p == nullptr) return set_error(JQ_ERR_CUDA, "cannot locate the device fault word");
+    int v = 0;
+    JQ_CUDA_TRY(cudaDeviceSynchronize());
+    JQ_CUDA_TRY(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (clear && v != 0) {
+        const int zero = 0;
+        JQ_CUDA_TRY(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    }
+    if (fault_out) *fault_out = v;
+    return JQ_OK;
+}
+
+// ---- host entry points -----------------------------------------------------------------------
+
+namespace {
+
+struct DeviceScratch {
+    cudaStream_t stream = nullptr;
+    void *ptrs[4] = {nullptr, nullptr, nullptr, nullptr};
+    int n = 0;
+    int alloc(void **out, size_t bytes) {
+        *out = nullptr;
+        if (bytes == 0) return JQ_OK;
+        JQ_CUDA_TRY(cudaMallocAsync(out, bytes, stream));
+        ptrs[n++] = *out;
+        return JQ_OK;
+    }
+    int open() {
+        JQ_CUDA_TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        return JQ_OK;
+    }
+    ~DeviceScratch() {
+        if (stream) {
+            for (int i = 0; i < n; ++i) cudaFreeAsync(ptrs[i], stream);
+            cudaStreamSynchronize(stream);
+            cudaStreamDestroy(stream);
+        }
+    }
+};
+
+}  // namespace
+
+int jq_q8_1_host(const float *input, uint8_t *output, const int *dims, int ndims) {
+    if (dims == nullptr || ndims < 1) return set_error(JQ_ERR_INVALID_ARG, "dims missing");
+    const int64_t ne0 = dims[0];
+    const int64_t ne1 = ndims > 1 ? dims[1] : 1;
+    const int64_t ne2 = ndims > 2 ? dims[2] : 1;
+    const int64_t ne3 = ndims > 3 ? dims[3] : 1;
+    if (ne0 < 0 || ne1 < 0 || ne2 < 0 || ne3 < 0) return set_error(JQ_ERR_INVALID_ARG, "negative dimension");
+    const int64_t M = ne1 * ne2 * ne3;  // every row of length ne0 is one column of the multiply
+    if (ne0 == 0 || M == 0) return JQ_OK;
+    if (input == nullptr || output == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (ne0 % QK != 0) return set_error(JQ_ERR_SHAPE, "dims[0] = %lld is not a multiple of %d", (long long)ne0, QK);
+    DeviceScratch s;
+    if (int rc = s.open()) return rc;
+    void *d_x, *d_y;
+    const size_t in_bytes = (size_t)ne0 * M * sizeof(float), out_bytes = jq_q8_1_bytes(ne0, M);
+    if (int rc = s.alloc(&d_x, in_bytes)) return rc;
+    if (int rc = s.alloc(&d_y, out_bytes)) return rc;
+    JQ_CUDA_TRY(cudaMemcpyAsync(d_x, input, in_bytes, cudaMemcpyHostToDevice, s.stream));
+    if (int rc = launch_quantize_q8_1(s.stream, static_cast<const float *>(d_x), d_y, ne0, M, JQ_ORDER_KSUPER_COL, JQ_S_SUM_X))
+        return rc;
+    JQ_CUDA_TRY(cudaMemcpyAsync(output, d_y, out_bytes, cudaMemcpyDeviceToHost, s.stream));
+    JQ_CUDA_TRY(cudaStreamSynchronize(s.stream));
+    return JQ_OK;
+}
+
+int jq_parse_q8_1_output(const uint8_t *input, int8_t *qs_out, float *scale_out, float *sum_out, int64_t n_blocks) {
+    if (n_blocks < 0) return set_error(JQ_ERR_INVALID_ARG, "negative block count");
+    if (n_blocks == 0) return JQ_OK;
+    if (!input || !qs_out || !scale_out || !sum_out) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    for (int64_t b = 0; b < n_blocks; ++b) {
+        const uint8_t *blk = input + b * Q8_BYTES;
+        std::memcpy(qs_out + b * SUPER, blk + Q8_QS_OFFSET, SUPER);
+        for (int g = 0; g < 4; ++g) {
+            __half h[2];
+            std::memcpy(h, blk + 4 * g, 4);
+            scale_out[b * 4 + g] = __half2float(h[0]);
+            sum_out[b * 4 + g] = __half2float(h[1]);
+        }
+    }
+    return JQ_OK;
+}
+
+int jq_mat_mul_q4_0_q8_1_host_ex(const void *weight_q4_0, const float *input, uint8_t *quant_workspace,
+                                 float *output, const int *input_dims, int ndims, int nrows_out, int ncols_k,
+                                 int s_mode) {
+    if (input_dims == nullptr || ndims < 2) return set_error(JQ_ERR_INVALID_ARG, "input_dims needs at least 2 entries");
+    const int64_t ne0 = input_dims[0], ne1 = input_dims[1];
+    const int64_t ne2 = ndims > 2 ? input_dims[2] : 1, ne3 = ndims > 3 ? input_dims[3] : 1;
+    if (ne0 != ncols_k) return set_error(JQ_ERR_SHAPE, "input_dims[0]=%lld must equal ncols_k=%d", (long long)ne0, ncols_k);
+    if (nrows_out < 0 || ne1 < 0 || ne2 < 0 || ne3 < 0) return set_error(JQ_ERR_INVALID_ARG, "negative dimension");
+    const int64_t K = ncols_k, N = nrows_out, M = ne1 * ne2 * ne3;
+    if (int rc = check_mul_mat_shape(K, N, M)) return rc;
+    if (int rc = check_s_mode(s_mode)) return rc;
+    if (M == 0) return JQ_OK;
+    if ((K > 0 && (input == nullptr || (N > 0 && weight_q4_0 == nullptr))) || (N > 0 && output == nullptr))
+        return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    DeviceScratch s;
+    if (int rc = s.open()) return rc;
+    void *d_w, *d_x, *d_ws, *d_y;
+    const size_t w_bytes = jq_q4_0_bytes(N, K), x_bytes = (size_t)M * K * sizeof(float);
+    const size_t ws_bytes = jq_q8_1_bytes(K, M), y_bytes = (size_t)M * N * sizeof(float);
+    if (int rc = s.alloc(&d_w, w_bytes)) return rc;
+    if (int rc = s.alloc(&d_x, x_bytes)) return rc;
+    if (int rc = s.alloc(&d_ws, ws_bytes)) return rc;
+    if (int rc = s.alloc(&d_y, y_bytes)) return rc;
+    if (w_bytes) JQ_CUDA_TRY(cudaMemcpyAsync(d_w, weight_q4_0, w_bytes, cudaMemcpyHostToDevice, s.stream));
+    if (x_bytes) JQ_CUDA_TRY(cudaMemcpyAsync(d_x, input, x_bytes, cudaMemcpyHostToDevice, s.stream));
+    if (K > 0) {
+        // the workspace keeps the order q8_1() writes (q8_1.cu:84-86) ...
+        if (int rc = launch_quantize_q8_1(s.stream, static_cast<const float *>(d_x), d_ws, K, M, JQ_ORDER_KSUPER_COL, s_mode))
+            return rc;
+        if (quant_workspace) JQ_CUDA_TRY(cudaMemcpyAsync(quant_workspace, d_ws, ws_bytes, cudaMemcpyDeviceToHost, s.stream));
+    }
+    if (N > 0) {
+        // ... and the multiply is told so, which the reference's own kernel is not (it reads
+        // m * (K/128) + k/128, mm_q4_0_q8_1.cu:230) and therefore mixes columns for M > 1.
+        if (int rc = dispatch_mul_mat(s.stream, d_w, d_ws, static_cast<float *>(d_y), K, N, M, JQ_ORDER_KSUPER_COL, JQ_KERNEL_AUTO))
+            return rc;
+        JQ_CUDA_TRY(cudaMemcpyAsync(output, d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
+    }
+    JQ_CUDA_TRY(cudaStreamSynchronize(s.stream));
+    return JQ_OK;
+}
+
+int jq_mat_mul_q4_0_q8_1_host(const void *weight_q4_0, const float *input, uint8_t *quant_workspace, float *output,
+                              const int *input_dims, int ndims, int nrows_out, int ncols_k) {
+    return jq_mat_mul_q4_0_q8_1_host_ex(weight_q4_0, input, quant_workspace, output, input_dims, ndims, nrows_out,
+                                        ncols_k, JQ_S_SUM_X);
+}
+
+// ---- resident weights ----------------------------------------------------------------------------
+
+struct jq_weights {
+    void *d_w = nullptr;
+    int64_t N = 0, K = 0;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    void *d_x = nullptr, *d_ws = nullptr, *d_y = nullptr;
+    int64_t m_cap = 0;
+};
+
+int jq_weights_create(const void *host_w_q4_0, int64_t N, int64_t K, jq_weights **out) {
+    if (out == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null out pointer");
+    *out = nullptr;
+    if (int rc = check_mul_mat_shape(K, N, 0)) return rc;
+    if (host_w_q4_0 == nullptr && N * K > 0) return set_error(JQ_ERR_INVALID_ARG, "null weights");
+    jq_weights *w = new (std::nothrow) jq_weights();
+    if (!w) return set_error(JQ_ERR_CUDA, "out of host memory");
+    w->N = N;
+    w->K = K;
+    cudaError_t e = cudaGetDevice(&w->device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&w->stream, cudaStreamNonBlocking);
+    const size_t bytes = jq_q4_0_bytes(N, K);
+    if (e == cudaSuccess && bytes) e = cudaMalloc(&w->d_w, bytes);
+    if (e == cudaSuccess && bytes) e = cudaMemcpy(w->d_w, host_w_q4_0, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        const int rc = cuda_error(e, "jq_weights_create");
+        jq_weights_destroy(w);
+        return rc;
+    }
+    *out = w;
+    return JQ_OK;
+}
+
+int jq_weights_destroy(jq_weights *w) {
+    if (!w) return JQ_OK;
+    if (w->stream) cudaStreamSynchronize(w->stream);
+    cudaFree(w->d_w);
+    cudaFree(w->d_x);
+    cudaFree(w->d_ws);
+    cudaFree(w->d_y);
+    if (w->stream) cudaStreamDestroy(w->stream);
+    delete w;
+    return JQ_OK;
+}
+
+const void *jq_weights_device_ptr(const jq_weights *w) { return w ? w->d_w : nullptr; }
+
+int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace, float *y, int64_t M, int s_mode) {
+    if (!w) return set_error(JQ_ERR_INVALID_ARG, "null weights handle");
+    if (M < 0) return set_error(JQ_ERR_INVALID_ARG, "negative M");
+    if (M == 0) return JQ_OK;
+    if (!x || !y) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (M > w->m_cap) {  // staging buffers grow, never shrink
+        JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+        cudaFree(w->d_x);
+        cudaFree(w->d_ws);
+        cudaFree(w->d_y);
+        w->d_x = w->d_ws = w->d_y = nullptr;
+        w->m_cap = 0;
+        JQ_CUDA_TRY(cudaMalloc(&w->d_x, (size_t)M * w->K * sizeof(float) + 16));
+        JQ_CUDA_TRY(cudaMalloc(&w->d_ws, jq_q8_1_bytes(w->K, M) + 16));
+        JQ_CUDA_TRY(cudaMalloc(&w->d_y, (size_t)M * w->N * sizeof(float) + 16));
+        w->m_cap = M;
+    }
+    JQ_CUDA_TRY(cudaMemcpyAsync(w->d_x, x, (size_t)M * w->K * sizeof(float), cudaMemcpyHostToDevice, w->stream));
+    if (int rc = jq_linear_q4_0_device(w->stream, w->d_w, static_cast<const float *>(w->d_x), w->d_ws,
+                                       static_cast<float *>(w->d_y), w->K, w->N, M, s_mode))
+        return rc;
+    if (quant_workspace)
+        JQ_CUDA_TRY(cudaMemcpyAsync(quant_workspace, w->d_ws, jq_q8_1_bytes(w->K, M), cudaMemcpyDeviceToHost, w->stream));
+    JQ_CUDA_TRY(cudaMemcpyAsync(y, w->d_y, (size_t)M * w->N * sizeof(float), cudaMemcpyDeviceToHost, w->stream));
+    JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+    return JQ_OK;
+}
+
+// ---- device description -----------------------------------------------------------------------------
+
+int jq_query_device_hw_info(int device, jq_device_hw_info *out) {
+    if (!out) return set_error(JQ_ERR_INVALID_ARG, "null out pointer");
+    std::memset(out, 0, sizeof(*out));
+    cudaDeviceProp prop{};
+    JQ_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    std::strncpy(out->name, prop.name, sizeof(out->name) - 1);
+    out->device_id = device;
+    out->cc_major = prop.major;
+    out->cc_minor = prop.minor;
+    out->sm_count = prop.multiProcessorCount;
+    JQ_CUDA_TRY(cudaDeviceGetAttribute(&out->sm_clock_khz, cudaDevAttrClockRate, device));
+    JQ_CUDA_TRY(cudaDeviceGetAttribute(&out->mem_clock_khz, cudaDevAttrMemoryClockRate, device));
+    JQ_CUDA_TRY(cudaDeviceGetAttribute(&out->mem_bus_width_bits, cudaDevAttrGlobalMemoryBusWidth, device));
+    out->smem_per_sm = prop.sharedMemPerMultiprocessor;
+    out->smem_per_block_optin = prop.sharedMemPerBlockOptin;
+    out->l2_bytes = (size_t)prop.l2CacheSize;
+    out->global_mem_bytes = prop.totalGlobalMem;
+    out->max_warps_per_sm = prop.maxThreadsPerMultiProcessor / (prop.warpSize > 0 ? prop.warpSize : 32);
+    const int cc = prop.major * 10 + prop.minor;
+    // per-SM tables: CUDA cores, schedulers, dense tensor MACs per clock.  The sm_100 tensor rates
+    // are NVIDIA's published dense B200 peaks (2.25 PFLOP/s bf16, 4.5 POP/s int8) divided by
+    // 148 SMs x 1.86 GHz.
+    int tc_bf16_mac = 0, tc_int8_mac = 0;
+    switch (cc) {
+        case 80: out->fp32_cores_per_sm = 64; tc_bf16_mac = 1024; tc_int8_mac = 2048; break;
+        case 86: case 87: case 89: out->fp32_cores_per_sm = 128; tc_bf16_mac = 512; tc_int8_mac = 1024; break;
+        case 90: out->fp32_cores_per_sm = 128; tc_bf16_mac = 2048; tc_int8_mac = 4096; break;
+        case 100: case 103: out->fp32_cores_per_sm = 128; tc_bf16_mac = 4096; tc_int8_mac = 8192; break;
+        default: out->fp32_cores_per_sm = cc >= 100 ? 128 : 0; break;
+    }
+    out->warp_schedulers_per_sm = cc >= 70 ? 4 : 0;
+    const double sm_hz = (double)out->sm_clock_khz * 1e3;
+    out->peak_fp32_tflops = (double)out->sm_count * out->fp32_cores_per_sm * 2.0 * sm_hz / 1e12;
+    out->peak_bf16_dense_tflops = (double)out->sm_count * tc_bf16_mac * 2.0 * sm_hz / 1e12;
+    out->peak_int8_dense_tops = (double)out->sm_count * tc_int8_mac * 2.0 * sm_hz / 1e12;
+    // DDR formula of the reference (device_hw_info.cuh:236-241); right for HBM too when the
+    // runtime reports the data clock and the full bus width.
+    out->peak_dram_gbs = (double)out->mem_clock_khz * 1e3 * (out->mem_bus_width_bits / 8.0) * 2.0 / 1e9;
+    if (out->peak_dram_gbs > 0) out->ridge_int8_ops_per_byte = out->peak_int8_dense_tops * 1e12 / (out->peak_dram_gbs * 1e9);
+    return JQ_OK;
+}
+
+}  // extern "C"

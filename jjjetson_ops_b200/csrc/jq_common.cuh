@@ -1,0 +1,191 @@
+// Shared definitions of the sm_100a Q4_0 x Q8_1 kernels: block layouts, error plumbing and the
+// small PTX wrappers (mbarrier, bulk async copy, int8 mma) the kernels are built from.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/jq_b200.h"
+
+namespace jq {
+
+constexpr int QK = 32;          // values per Q4_0 block and per Q8_1 group
+constexpr int Q4_BYTES = 18;    // block_q4_0: fp16 d + 16 nibble bytes
+constexpr int SUPER = 128;      // values per block_q8_1_mmq
+constexpr int Q8_BYTES = 144;   // 4 x half2 (d, s) + 128 int8
+constexpr int Q8_QS_OFFSET = 16;
+
+// Mirror of the reference's activation block (src/cuda/q8_1.cu:14-18).
+struct __align__(16) BlockQ8_1Mmq {
+    half2 ds4[4];
+    int8_t qs[SUPER];
+};
+static_assert(sizeof(BlockQ8_1Mmq) == Q8_BYTES, "block_q8_1_mmq must be 144 bytes");
+
+// ---- host-side error plumbing ------------------------------------------------------------
+int set_error(int status, const char *fmt, ...);  // records the message, returns `status`
+int cuda_error(cudaError_t e, const char *what);  // JQ_ERR_CUDA with the runtime's message
+
+#define JQ_CUDA_TRY(expr)                                         \
+    do {                                                          \
+        cudaError_t jq_e_ = (expr);                               \
+        if (jq_e_ != cudaSuccess) return ::jq::cuda_error(jq_e_, #expr); \
+    } while (0)
+
+// Per-device facts the launchers need; queried once per device.
+struct DeviceCaps {
+    int sm_count = 0;
+    int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
+    int cc = 0;          // major*10 + minor
+};
+int device_caps(DeviceCaps *out);  // for the current device
+
+// Device address (on the current device) of the word a kernel sets when one of its bounded waits
+// gives up; nullptr if it cannot be obtained.  Kernels receive it as a parameter.
+int *device_fault_ptr();
+
+// ---- launchers implemented in the .cu files ----------------------------------------------
+int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t K, int64_t M,
+                         int order, int s_mode);
+int launch_quantize_q4_0(cudaStream_t st, const float *d_w, void *d_wq, int64_t N, int64_t K);
+int launch_mmq_generic(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                       int64_t N, int64_t M, int order);
+int launch_block_sums(cudaStream_t st, const void *d_w, const void *d_xq, int32_t *d_sums, int64_t K,
+                      int64_t N, int64_t M, int order);
+// Streaming GEMV family.  d_x_f32 != nullptr fuses the activation quantizer into the prologue
+// (d_xq then receives the quantized blocks in JQ_ORDER_COL_KSUPER order, may be nullptr).
+// Returns JQ_ERR_UNSUPPORTED when the shape or alignment rules of the fast path do not hold.
+int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
+                     void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
+                     int s_mode);
+int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
+                    void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
+                    int s_mode);
+int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                    int64_t N, int64_t M, int order);
+
+// ---- device helpers --------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ int64_t q8_block_index(int64_t ksuper, int64_t m, int64_t n_super, int64_t M,
+                                                  int order) {
+    return order == JQ_ORDER_KSUPER_COL ? ksuper * M + m : m * n_super + ksuper;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
+    return __half2float(__ushort_as_half((unsigned short)h16));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- mbarrier -------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls, records the fault and reports false so that the
+// caller can leave the kernel instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *fault,
+                                                  uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (fault != nullptr) atomicExch(fault, 1);
+    return false;
+}
+
+// 1-D bulk async copy global -> shared, completion counted in bytes on an mbarrier.
+// Source, destination and size must all be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes,
+                                         uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Named barrier over a subset of the CTA's warps.
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// D(16x8, s32) = A(16x32, u8 row) * B(32x8, s8 col) + C
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2],
+                                               const int (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(c[0]), "r"(c[1]),
+          "r"(c[2]), "r"(c[3]));
+}
+
+// One 32-value group of the activation quantizer, as 8 lanes x 4 floats, following
+// quantize_q8_1_kernel (src/cuda/q8_1.cu:55-79,101-103) operation by operation so that the int8
+// values, fp16 d and fp16 sum come out bit-identical: max and sum by xor butterflies with
+// offsets 4, 2, 1, d_inv = 127/amax by IEEE division, q = roundf(x * d_inv), d = 1/d_inv.
+// Every lane of the warp must call it.  Returns the packed char4; ds holds (d, s) as fp16 bits.
+__device__ __forceinline__ uint32_t quantize_group_q8_1(float4 xi, int s_mode, uint32_t *ds_bits) {
+    float amax = fmaxf(fabsf(xi.x), fmaxf(fabsf(xi.y), fmaxf(fabsf(xi.z), fabsf(xi.w))));
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off, 32));
+    }
+    float sum = xi.x + xi.y + xi.z + xi.w;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off, 32);
+    }
+    const float d_inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    const int q0 = (int)roundf(xi.x * d_inv);
+    const int q1 = (int)roundf(xi.y * d_inv);
+    const int q2 = (int)roundf(xi.z * d_inv);
+    const int q3 = (int)roundf(xi.w * d_inv);
+    const __half dh = amax > 0.0f ? __float2half(1.0f / d_inv) : __ushort_as_half((unsigned short)0);
+    __half sh;
+    if (s_mode == JQ_S_SUM_X) {
+        sh = __float2half(sum);
+    } else {
+        int isum = q0 + q1 + q2 + q3;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+            isum += __shfl_xor_sync(0xFFFFFFFFu, isum, off, 32);
+        }
+        sh = __float2half(__half2float(dh) * (float)isum);
+    }
+    *ds_bits = (uint32_t)__half_as_ushort(dh) | ((uint32_t)__half_as_ushort(sh) << 16);
+    return (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+           ((uint32_t)(q3 & 0xFF) << 24);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace jq

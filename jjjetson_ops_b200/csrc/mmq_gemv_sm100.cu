@@ -1,0 +1,551 @@
+// Decode-regime multiply (M <= 8): an HBM-streaming kernel for sm_100a.
+//
+// Work to replace: q4_0_q8_1_mat_mul_kernel (reference src/cuda/mm_q4_0_q8_1.cu:164-289) when the
+// batch is a handful of columns.  There the whole cost is reading the Q4_0 weights once, so the
+// kernel is organised around keeping HBM busy:
+//
+//   * one persistent CTA per SM owns a contiguous slab of weight rows;
+//   * a producer thread streams the slab through a ring of shared-memory stages with 1-D bulk
+//     async copies (cp.async.bulk, completion counted on an mbarrier), so many tens of KB per SM
+//     are in flight without costing the compute warps a single load instruction;
+//   * the activations (at most 8 columns) are quantized in the prologue if they arrive as fp32,
+//     and then live in registers for the whole kernel;
+//   * consumer warps read the 18-byte blocks out of shared memory, unpack nibbles in registers
+//     and form the exact int32 block sums, with dp4a (M <= 2, one warp per row) or with one
+//     int8 mma.m16n8k32 per 16 rows x 1 block (M <= 8, K split over the warps);
+//   * per block the epilogue is the reference's: acc += d4 * (sumi * d8 - 8 * s8)
+//     (mm_q4_0_q8_1.cu:92), with fp32 partial sums reduced by shuffles / through shared memory.
+//
+// The 18-byte block is only 2-byte aligned, but 8 blocks are 144 = 9 * 16 bytes, so with
+// K % 256 == 0 and a 16-byte aligned base every row is a legal bulk-copy source.  Other shapes
+// are refused here and fall to the generic kernel.
+#include "jq_common.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int GV_MAX_STAGES = 8;
+constexpr int GV_BAR_BYTES = 128;  // full[8] + empty[8] mbarriers
+constexpr uint32_t MASK4 = 0x0F0F0F0Fu;
+
+struct GemvParams {
+    const uint8_t *w;
+    const uint8_t *xq;     // quantized activations (nullptr when x_f32 is given)
+    const float *x_f32;    // raw activations to quantize in the prologue, or nullptr
+    uint8_t *xq_out;       // where CTA 0 publishes the blocks it quantized, or nullptr
+    float *y;
+    int *fault;
+    int64_t N;
+    int K, M, order, s_mode;
+    int n_super;           // K / 128
+    uint32_t row_bytes;    // K / 32 * 18
+    uint32_t row_stride;   // distance between rows inside a stage (>= row_bytes)
+    uint32_t stage_bytes;
+    uint32_t x_bytes;      // shared bytes reserved for the quantized activations
+    int stages;
+    int rows_per_stage;
+};
+
+__device__ __forceinline__ void cta_row_range(int64_t N, int64_t *begin, int64_t *end) {
+    *begin = (int64_t)blockIdx.x * N / gridDim.x;
+    *end = (int64_t)(blockIdx.x + 1) * N / gridDim.x;
+}
+
+// Producer: one thread walks the CTA's row slab stage by stage.
+template <bool PER_ROW>
+__device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty,
+                                              uint8_t *ring) {
+    int64_t r_begin, r_end;
+    cta_row_range(p.N, &r_begin, &r_end);
+    const int R = p.rows_per_stage;
+    const int n_chunks = (int)((r_end - r_begin + R - 1) / R);
+    for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % p.stages;
+        const uint32_t round = (uint32_t)(c / p.stages);
+        if (round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1u, p.fault)) return;
+        const int64_t r0 = r_begin + (int64_t)c * R;
+        const int rows = (int)min((int64_t)R, r_end - r0);
+        uint8_t *dst = ring + (size_t)s * p.stage_bytes;
+        const uint8_t *src = p.w + r0 * p.row_bytes;
+        mbar_arrive_expect_tx(&full[s], (uint32_t)rows * p.row_bytes);
+        if (PER_ROW) {
+            for (int r = 0; r < rows; ++r) {
+                bulk_g2s(dst + (size_t)r * p.row_stride, src + (size_t)r * p.row_bytes, p.row_bytes, &full[s]);
+            }
+        } else {
+            bulk_g2s(dst, src, (uint32_t)rows * p.row_bytes, &full[s]);
+        }
+    }
+}
+
+// Prologue of the consumer warps: put the quantized activations into shared memory, laid out
+// [m][k/128] as 144-byte blocks.  Either quantize fp32 input (bit-identical to the stand-alone
+// quantizer) or copy already quantized blocks, honouring their order.
+template <int NW>
+__device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, int warp, int lane) {
+    const int total = p.M * p.n_super;
+    if (p.x_f32 != nullptr) {
+        for (int idx = warp; idx < total; idx += NW) {
+            const int m = idx / p.n_super, ks = idx - m * p.n_super;
+            const float4 xi = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
+            uint32_t ds;
+            const uint32_t q = quantize_group_q8_1(xi, p.s_mode, &ds);
+            uint8_t *blk = xs + (size_t)idx * Q8_BYTES;
+            reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+            if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
+            if (p.xq_out != nullptr && blockIdx.x == 0) {
+                uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+                reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = q;
+                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = ds;
+            }
+        }
+    } else {
+        // 9 x 16 bytes per block
+        for (int i = warp * 32 + lane; i < total * 9; i += NW * 32) {
+            const int idx = i / 9, part = i - idx * 9;
+            const int m = idx / p.n_super, ks = idx - m * p.n_super;
+            const uint8_t *g = p.xq + (size_t)q8_block_index(ks, m, p.n_super, p.M, p.order) * Q8_BYTES;
+            reinterpret_cast<uint4 *>(xs + (size_t)idx * Q8_BYTES)[part] =
+                __ldg(reinterpret_cast<const uint4 *>(g) + part);
+        }
+    }
+    named_bar_sync(1, NW * 32);
+}
+
+// ------------------------------------------------------------------------------------------------
+// dp4a variant: one warp per weight row, one lane per 128-value slice (four Q4_0 blocks = 72
+// bytes, read as nine conflict-free 8-byte shared loads), activations of that slice in registers.
+// ------------------------------------------------------------------------------------------------
+template <int M_T, int NSB, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + GV_MAX_STAGES;
+    uint8_t *xs = smem + GV_BAR_BYTES;
+    uint8_t *ring = xs + p.x_bytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NW);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == NW) {
+        if (lane == 0) gemv_producer<false>(p, full, empty, ring);
+        return;
+    }
+
+    stage_activations<NW>(p, xs, warp, lane);
+
+    // This lane's slices of X: slice i covers k in [128*(lane + 32 i), +128).
+    int xq[NSB][M_T][32];
+    float xd[NSB][M_T][4], xms[NSB][M_T][4];
+#pragma unroll
+    for (int i = 0; i < NSB; ++i) {
+        const int sb = lane + 32 * i;
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) {
+            if (sb < p.n_super && m < p.M) {
+                const uint4 *b = reinterpret_cast<const uint4 *>(xs + (size_t)(m * p.n_super + sb) * Q8_BYTES);
+                const uint4 ds = b[0];
+                const uint32_t dsv[4] = {ds.x, ds.y, ds.z, ds.w};
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    xd[i][m][g] = half_bits_to_float(dsv[g] & 0xFFFFu);
+                    xms[i][m][g] = -8.0f * half_bits_to_float(dsv[g] >> 16);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint4 v = b[1 + j];
+                    xq[i][m][4 * j + 0] = (int)v.x;
+                    xq[i][m][4 * j + 1] = (int)v.y;
+                    xq[i][m][4 * j + 2] = (int)v.z;
+                    xq[i][m][4 * j + 3] = (int)v.w;
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) xd[i][m][g] = xms[i][m][g] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) xq[i][m][j] = 0;
+            }
+        }
+    }
+
+    int64_t r_begin, r_end;
+    cta_row_range(p.N, &r_begin, &r_end);
+    const int R = p.rows_per_stage;
+    const int n_chunks = (int)((r_end - r_begin + R - 1) / R);
+
+    for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % p.stages;
+        const uint32_t round = (uint32_t)(c / p.stages);
+        if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
+        const uint8_t *stage = ring + (size_t)s * p.stage_bytes;
+        const int64_t r0 = r_begin + (int64_t)c * R;
+        const int rows = (int)min((int64_t)R, r_end - r0);
+
+        for (int r = warp; r < rows; r += NW) {
+            const uint8_t *rowp = stage + (size_t)r * p.row_bytes;
+            float acc[M_T];
+#pragma unroll
+            for (int m = 0; m < M_T; ++m) acc[m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NSB; ++i) {
+                const int sb = lane + 32 * i;
+                if (sb < p.n_super) {
+                    uint32_t wv[18];
+                    const uint2 *src = reinterpret_cast<const uint2 *>(rowp + sb * 72);
+#pragma unroll
+                    for (int j = 0; j < 9; ++j) {
+                        const uint2 v = src[j];
+                        wv[2 * j] = v.x;
+                        wv[2 * j + 1] = v.y;
+                    }
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        // block b starts at byte 18 b of the 72: word 4.5 b
+                        uint32_t q[4], dbits;
+                        if ((b & 1) == 0) {
+                            const int w0 = (b / 2) * 9;
+                            dbits = wv[w0] & 0xFFFFu;
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) q[t] = __funnelshift_r(wv[w0 + t], wv[w0 + t + 1], 16);
+                        } else {
+                            const int w0 = (b / 2) * 9 + 4;
+                            dbits = wv[w0] >> 16;
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) q[t] = wv[w0 + 1 + t];
+                        }
+                        const float d4 = half_bits_to_float(dbits);
+                        int sumi[M_T];
+#pragma unroll
+                        for (int m = 0; m < M_T; ++m) sumi[m] = 0;
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const int lo = (int)(q[t] & MASK4), hi = (int)((q[t] >> 4) & MASK4);
+#pragma unroll
+                            for (int m = 0; m < M_T; ++m) {
+                                sumi[m] = __dp4a(lo, xq[i][m][8 * b + t], sumi[m]);
+                                sumi[m] = __dp4a(hi, xq[i][m][8 * b + t + 4], sumi[m]);
+                            }
+                        }
+#pragma unroll
+                        for (int m = 0; m < M_T; ++m) {
+                            acc[m] = fmaf(d4, fmaf((float)sumi[m], xd[i][m][b], xms[i][m][b]), acc[m]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < M_T; ++m) {
+                float v = acc[m];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
+                if (lane == 0 && m < p.M) p.y[(size_t)m * p.N + (r0 + r)] = v;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// mma variant (M <= 8): a stage holds 16 weight rows (one m16 tile), each copied separately so that
+// the row distance in shared memory can be padded to an odd multiple of 16 bytes, which makes
+// the fragment loads (8 rows x 4 consecutive words) bank-conflict free.  Warp w owns the K slice
+// [w*KBW, (w+1)*KBW) of 32-wide blocks for all 16 rows: the activation fragments and scales of
+// its slice stay in registers, and per block it issues one mma.m16n8k32 (u8 nibbles x s8
+// activations -> exact s32 block sums for 16 rows x 8 columns).  Thread (g = lane/4, t = lane%4)
+// feeds the tile with word t of the block: its low nibbles are weights 4t..4t+3 (fragment a0/a1),
+// its high nibbles weights 16+4t.. (a2/a3) -- exactly the k ranges the fragment layout asks of it.
+// Partial fp32 sums of the NW warps are added in a fixed order through shared memory.
+// ------------------------------------------------------------------------------------------------
+template <int KBW, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + GV_MAX_STAGES;
+    float *red = reinterpret_cast<float *>(smem + GV_BAR_BYTES);  // [2][NW][128]
+    uint8_t *xs = smem + GV_BAR_BYTES + 2 * NW * 128 * sizeof(float);
+    uint8_t *ring = xs + p.x_bytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NW);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == NW) {
+        if (lane == 0) gemv_producer<true>(p, full, empty, ring);
+        return;
+    }
+
+    stage_activations<NW>(p, xs, warp, lane);
+
+    const int g = lane >> 2, t = lane & 3;
+    const int nb = p.K / QK;
+    const int kb0 = warp * KBW;
+    // B fragments (column g) and scales (columns 2t, 2t+1) of this warp's K slice.
+    uint32_t xb0[KBW], xb1[KBW];
+    float xd0[KBW], xd1[KBW], xm0[KBW], xm1[KBW];
+#pragma unroll
+    for (int j = 0; j < KBW; ++j) {
+        const int kb = kb0 + j;
+        xb0[j] = xb1[j] = 0u;
+        xd0[j] = xd1[j] = xm0[j] = xm1[j] = 0.0f;
+        if (kb < nb) {
+            const int ks = kb >> 2, sub = kb & 3;
+            if (g < p.M) {
+                const uint8_t *b = xs + (size_t)(g * p.n_super + ks) * Q8_BYTES + Q8_QS_OFFSET + sub * QK;
+                xb0[j] = reinterpret_cast<const uint32_t *>(b)[t];
+                xb1[j] = reinterpret_cast<const uint32_t *>(b)[t + 4];
+            }
+            if (2 * t < p.M) {
+                const uint32_t ds = reinterpret_cast<const uint32_t *>(xs + (size_t)((2 * t) * p.n_super + ks) * Q8_BYTES)[sub];
+                xd0[j] = half_bits_to_float(ds & 0xFFFFu);
+                xm0[j] = -8.0f * half_bits_to_float(ds >> 16);
+            }
+            if (2 * t + 1 < p.M) {
+                const uint32_t ds =
+                    reinterpret_cast<const uint32_t *>(xs + (size_t)((2 * t + 1) * p.n_super + ks) * Q8_BYTES)[sub];
+                xd1[j] = half_bits_to_float(ds & 0xFFFFu);
+                xm1[j] = -8.0f * half_bits_to_float(ds >> 16);
+            }
+        }
+    }
+
+    int64_t r_begin, r_end;
+    cta_row_range(p.N, &r_begin, &r_end);
+    const int n_chunks = (int)((r_end - r_begin + 15) / 16);
+    const int zero4[4] = {0, 0, 0, 0};
+
+    for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % p.stages;
+        const uint32_t round = (uint32_t)(c / p.stages);
+        if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
+        const uint8_t *stage = ring + (size_t)s * p.stage_bytes;
+        const int64_t r0 = r_begin + (int64_t)c * 16;
+        const int rows = (int)min((int64_t)16, r_end - r0);
+
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};  // (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+        const uint8_t *row_lo = stage + (size_t)g * p.row_stride;
+        const uint8_t *row_hi = stage + (size_t)(g + 8) * p.row_stride;
+#pragma unroll
+        for (int jp = 0; jp < KBW / 2; ++jp) {
+            const int kbe = kb0 + 2 * jp;  // even block, 4-byte aligned start at byte 18*kbe
+            if (kbe < nb) {
+                uint32_t a_even[4], a_odd[4];
+                float d_even[2], d_odd[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint8_t *pr = (h == 0 ? row_lo : row_hi) + (size_t)kbe * Q4_BYTES;
+                    const uint32_t *pw = reinterpret_cast<const uint32_t *>(pr);
+                    const uint32_t u0 = pw[t], u1 = pw[t + 1], u2 = pw[5 + t];
+                    const uint32_t we = __funnelshift_r(u0, u1, 16);  // word t of the even block
+                    a_even[h] = we & MASK4;              // a0 / a1: weights 4t..4t+3
+                    a_even[2 + h] = (we >> 4) & MASK4;   // a2 / a3: weights 16+4t..
+                    a_odd[h] = u2 & MASK4;
+                    a_odd[2 + h] = (u2 >> 4) & MASK4;
+                    d_even[h] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(pr));
+                    d_odd[h] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(pr + Q4_BYTES));
+                }
+                int ce[4], co[4];
+                {
+                    const uint32_t bfrag[2] = {xb0[2 * jp], xb1[2 * jp]};
+                    mma_u8s8_16832(ce, a_even, bfrag, zero4);
+                }
+                acc[0] = fmaf(d_even[0], fmaf((float)ce[0], xd0[2 * jp], xm0[2 * jp]), acc[0]);
+                acc[1] = fmaf(d_even[0], fmaf((float)ce[1], xd1[2 * jp], xm1[2 * jp]), acc[1]);
+                acc[2] = fmaf(d_even[1], fmaf((float)ce[2], xd0[2 * jp], xm0[2 * jp]), acc[2]);
+                acc[3] = fmaf(d_even[1], fmaf((float)ce[3], xd1[2 * jp], xm1[2 * jp]), acc[3]);
+                if (kbe + 1 < nb) {
+                    const uint32_t bfrag[2] = {xb0[2 * jp + 1], xb1[2 * jp + 1]};
+                    mma_u8s8_16832(co, a_odd, bfrag, zero4);
+                    acc[0] = fmaf(d_odd[0], fmaf((float)co[0], xd0[2 * jp + 1], xm0[2 * jp + 1]), acc[0]);
+                    acc[1] = fmaf(d_odd[0], fmaf((float)co[1], xd1[2 * jp + 1], xm1[2 * jp + 1]), acc[1]);
+                    acc[2] = fmaf(d_odd[1], fmaf((float)co[2], xd0[2 * jp + 1], xm0[2 * jp + 1]), acc[2]);
+                    acc[3] = fmaf(d_odd[1], fmaf((float)co[3], xd1[2 * jp + 1], xm1[2 * jp + 1]), acc[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // the stage's bytes are in registers / consumed
+
+        // Cross-warp reduction, double buffered by tile parity: one barrier per tile.
+        float *mine = red + ((size_t)(c & 1) * NW + warp) * 128;
+        mine[(g)*8 + 2 * t] = acc[0];
+        mine[(g)*8 + 2 * t + 1] = acc[1];
+        mine[(g + 8) * 8 + 2 * t] = acc[2];
+        mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
+        named_bar_sync(2, NW * 32);
+        const int tid = warp * 32 + lane;
+        if (tid < 128) {
+            const int row = tid >> 3, col = tid & 7;
+            if (row < rows && col < p.M) {
+                const float *src = red + (size_t)(c & 1) * NW * 128 + tid;
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) v += src[w * 128];
+                p.y[(size_t)col * p.N + (r0 + row)] = v;
+            }
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device).
+int ensure_smem_attr(void (*kernel)(const GemvParams), int bytes) {
+    struct Entry {
+        const void *fn;
+        int dev, bytes;
+    };
+    static thread_local Entry table[32] = {};
+    static thread_local int used = 0;
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    for (int i = 0; i < used; ++i) {
+        if (table[i].fn == (const void *)kernel && table[i].dev == dev) {
+            if (table[i].bytes >= bytes) return JQ_OK;
+            JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+            table[i].bytes = bytes;
+            return JQ_OK;
+        }
+    }
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (used < 32) table[used++] = Entry{(const void *)kernel, dev, bytes};
+    return JQ_OK;
+}
+
+inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+int fast_path_ok(const void *d_w, const void *d_xq, const float *d_x_f32, int64_t K, int64_t N) {
+    if (K % 256 != 0) return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs K %% 256 == 0 (K = %lld)", (long long)K);
+    if (((uintptr_t)d_w & 15u) != 0) return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs 16-byte aligned weights");
+    if (d_x_f32 != nullptr && ((uintptr_t)d_x_f32 & 15u) != 0)
+        return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs 16-byte aligned activations");
+    if (d_x_f32 == nullptr && ((uintptr_t)d_xq & 15u) != 0)
+        return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs 16-byte aligned Q8_1 blocks");
+    if (K > (1 << 20) || N > (int64_t)1 << 31) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the streaming GEMV");
+    return JQ_OK;
+}
+
+template <int M_T, int NSB, int NW>
+int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
+    p.rows_per_stage = NW;
+    p.row_stride = p.row_bytes;
+    for (;;) {
+        p.stage_bytes = align_up((uint32_t)p.rows_per_stage * p.row_bytes, 128);
+        const int64_t avail = (int64_t)caps.smem_optin - GV_BAR_BYTES - p.x_bytes;
+        p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
+        if (p.stages >= 3 || p.rows_per_stage == 1) break;
+        p.rows_per_stage = p.rows_per_stage > 2 ? p.rows_per_stage / 2 : 1;
+    }
+    if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
+    const int smem = GV_BAR_BYTES + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+    auto kernel = gemv_dp4a_kernel<M_T, NSB, NW>;
+    if (int rc = ensure_smem_attr(kernel, smem)) return rc;
+    const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
+    const int grid = (int)min((int64_t)caps.sm_count, max((int64_t)1, want));
+    kernel<<<grid, (NW + 1) * 32, smem, st>>>(p);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+template <int KBW, int NW>
+int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
+    p.rows_per_stage = 16;
+    // rows 16*odd bytes apart: 8 rows x 4 words hit 32 distinct banks
+    p.row_stride = p.row_bytes + ((p.row_bytes / 16) % 2 == 0 ? 16 : 0);
+    // the last warps may read a few blocks past the row end (their results are discarded)
+    p.stage_bytes = align_up(16 * p.row_stride + KBW * Q4_BYTES + 64, 128);
+    const int red_bytes = 2 * NW * 128 * (int)sizeof(float);
+    const int64_t avail = (int64_t)caps.smem_optin - GV_BAR_BYTES - red_bytes - p.x_bytes;
+    p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
+    if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "16 rows of %u bytes do not fit the shared-memory ring", p.row_bytes);
+    const int smem = GV_BAR_BYTES + red_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+    auto kernel = gemv_mma_kernel<KBW, NW>;
+    if (int rc = ensure_smem_attr(kernel, smem)) return rc;
+    const int64_t want = (p.N + 15) / 16;
+    const int grid = (int)min((int64_t)caps.sm_count, max((int64_t)1, want));
+    kernel<<<grid, (NW + 1) * 32, smem, st>>>(p);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
+                float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+    p.w = static_cast<const uint8_t *>(d_w);
+    p.xq = d_x_f32 ? nullptr : static_cast<const uint8_t *>(d_xq);
+    p.x_f32 = d_x_f32;
+    p.xq_out = d_x_f32 ? static_cast<uint8_t *>(d_xq_out) : nullptr;
+    p.y = d_y;
+    p.fault = device_fault_ptr();
+    p.N = N;
+    p.K = (int)K;
+    p.M = (int)M;
+    p.order = order;
+    p.s_mode = s_mode;
+    p.n_super = (int)(K / SUPER);
+    p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
+    p.x_bytes = align_up((uint32_t)(M * p.n_super * Q8_BYTES), 128);
+    return JQ_OK;
+}
+
+}  // namespace
+
+int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
+                     float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+    if (M < 1 || M > 2) return set_error(JQ_ERR_UNSUPPORTED, "dp4a GEMV handles M <= 2 (M = %lld)", (long long)M);
+    if (int rc = fast_path_ok(d_w, d_xq, d_x_f32, K, N)) return rc;
+    if (N == 0) return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    GemvParams p{};
+    fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
+    const int nsb = (p.n_super + 31) / 32;
+    if (M == 1) {
+        switch (nsb) {
+            case 1: return run_dp4a<1, 1, 16>(st, p, caps);
+            case 2: return run_dp4a<1, 2, 8>(st, p, caps);
+            case 3: return run_dp4a<1, 3, 7>(st, p, caps);  // 7 + 1 warps: 255 registers per thread
+            case 4: return run_dp4a<1, 4, 7>(st, p, caps);
+            default: break;
+        }
+    } else {
+        switch (nsb) {
+            case 1: return run_dp4a<2, 1, 8>(st, p, caps);
+            case 2: return run_dp4a<2, 2, 7>(st, p, caps);
+            default: break;
+        }
+    }
+    return set_error(JQ_ERR_UNSUPPORTED, "dp4a GEMV: K = %lld too long to keep %lld activation columns in registers",
+                     (long long)K, (long long)M);
+}
+
+int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
+                    float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+    if (M < 1 || M > 8) return set_error(JQ_ERR_UNSUPPORTED, "mma GEMV handles M <= 8 (M = %lld)", (long long)M);
+    if (int rc = fast_path_ok(d_w, d_xq, d_x_f32, K, N)) return rc;
+    if (N == 0) return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    GemvParams p{};
+    fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
+    const int nb = (int)(K / QK);
+    if (nb <= 8 * 8) return run_mma<8, 8>(st, p, caps);
+    if (nb <= 16 * 8) return run_mma<8, 16>(st, p, caps);
+    if (nb <= 16 * 12) return run_mma<12, 16>(st, p, caps);
+    return set_error(JQ_ERR_UNSUPPORTED, "mma GEMV: K = %lld too long to keep the activation fragments in registers",
+                     (long long)K);
+}
+
+}  // namespace jq

@@ -1,0 +1,142 @@
+// Quantizers: fp32 activations -> block_q8_1_mmq, fp32 weights -> Q4_0.
+//
+// The activation quantizer replaces quantize_q8_1_kernel (reference src/cuda/q8_1.cu:20-104).
+// It is a pure streaming kernel (reads 4 B, writes 1.125 B per value); one warp owns one
+// 128-value block, one lane four consecutive floats, so a warp reads 512 contiguous bytes and
+// writes 128 + 16 contiguous bytes.
+#include "jq_common.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int QUANT_THREADS = 256;
+constexpr int QUANT_UNROLL = 4;
+
+__global__ void __launch_bounds__(QUANT_THREADS)
+quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq, int64_t K, int64_t M,
+                           int64_t n_super, int order, int s_mode) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = ((int64_t)blockIdx.x * QUANT_THREADS + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * QUANT_THREADS) >> 5;
+    const int64_t total = M * n_super;
+
+    for (int64_t base = warp0; base < total; base += n_warps * QUANT_UNROLL) {
+        float4 xi[QUANT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < QUANT_UNROLL; ++u) {
+            const int64_t b = base + (int64_t)u * n_warps;
+            xi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < total) {
+                const int64_t m = b / n_super, ks = b - m * n_super;
+                const int64_t k = ks * SUPER + lane * 4;
+                if (k < K) xi[u] = __ldg(reinterpret_cast<const float4 *>(x + m * K + k));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QUANT_UNROLL; ++u) {
+            const int64_t b = base + (int64_t)u * n_warps;  // uniform across the warp
+            if (b >= total) break;
+            uint32_t ds;
+            const uint32_t q = quantize_group_q8_1(xi[u], s_mode, &ds);
+            const int64_t m = b / n_super, ks = b - m * n_super;
+            uint8_t *blk = xq + q8_block_index(ks, m, n_super, M, order) * Q8_BYTES;
+            reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+            if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
+        }
+    }
+}
+
+// fp32 [N][K] -> Q4_0.  Eight lanes own one 32-weight block.  The block's scale comes from the
+// element of largest magnitude, the first one on ties, taken with its sign.
+__global__ void __launch_bounds__(256)
+quantize_q4_0_kernel_sm100(const float *__restrict__ w, uint8_t *__restrict__ wq, int64_t n_blocks) {
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & 7;
+    const int64_t group0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    const int64_t n_groups = ((int64_t)gridDim.x * blockDim.x) >> 3;
+    const int64_t iters = (n_blocks + n_groups - 1) / n_groups;
+    for (int64_t it = 0; it < iters; ++it) {
+        const int64_t b = group0 + it * n_groups;
+        const bool live = b < n_blocks;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) v = __ldg(reinterpret_cast<const float4 *>(w + b * QK) + sub);
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        float amax = 0.0f, mx = 0.0f;
+        int idx = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (amax < fabsf(e[j])) {
+                amax = fabsf(e[j]);
+                mx = e[j];
+                idx = sub * 4 + j;
+            }
+        }
+        if (amax == 0.0f) idx = 32;  // "nothing found yet": loses every tie
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+            const float oa = __shfl_xor_sync(0xFFFFFFFFu, amax, off, 32);
+            const float om = __shfl_xor_sync(0xFFFFFFFFu, mx, off, 32);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off, 32);
+            if (oa > amax || (oa == amax && oi < idx)) {
+                amax = oa;
+                mx = om;
+                idx = oi;
+            }
+        }
+        const float d = mx / -8.0f;
+        const float id = d != 0.0f ? 1.0f / d : 0.0f;
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // multiply and add round separately (no fused multiply-add), then truncate
+            int q = (int)__fadd_rn(__fmul_rn(e[j], id), 8.5f);
+            q = q > 15 ? 15 : q;
+            packed |= (uint32_t)q << (8 * j);
+        }
+        const uint32_t hi = __shfl_xor_sync(0xFFFFFFFFu, packed, 4, 32);  // weights j+16 for lanes 0..3
+        if (live && sub < 4) {
+            const uint32_t bytes = packed | (hi << 4);
+            uint8_t *o = wq + b * Q4_BYTES;
+            uint16_t *o16 = reinterpret_cast<uint16_t *>(o + 2 + 4 * sub);  // 2-byte aligned only
+            o16[0] = (uint16_t)(bytes & 0xFFFFu);
+            o16[1] = (uint16_t)(bytes >> 16);
+            if (sub == 0) *reinterpret_cast<uint16_t *>(o) = __half_as_ushort(__float2half(d));
+        }
+    }
+}
+
+}  // namespace
+
+int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t K, int64_t M, int order,
+                         int s_mode) {
+    const int64_t n_super = (K + SUPER - 1) / SUPER;
+    const int64_t total = M * n_super;
+    if (total == 0) return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    const int warps_per_cta = QUANT_THREADS / 32;
+    int64_t ctas = (total + (int64_t)warps_per_cta * QUANT_UNROLL - 1) / ((int64_t)warps_per_cta * QUANT_UNROLL);
+    const int64_t cap = (int64_t)caps.sm_count * 8 * 4;  // a few waves of resident CTAs
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    quantize_q8_1_kernel_sm100<<<(unsigned)ctas, QUANT_THREADS, 0, st>>>(
+        d_x, static_cast<uint8_t *>(d_xq), K, M, n_super, order, s_mode);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+int launch_quantize_q4_0(cudaStream_t st, const float *d_w, void *d_wq, int64_t N, int64_t K) {
+    const int64_t n_blocks = N * (K / QK);
+    if (n_blocks == 0) return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    int64_t ctas = (n_blocks + 31) / 32;  // 32 blocks per 256-thread CTA per pass
+    const int64_t cap = (int64_t)caps.sm_count * 32;
+    if (ctas > cap) ctas = cap;
+    quantize_q4_0_kernel_sm100<<<(unsigned)ctas, 256, 0, st>>>(d_w, static_cast<uint8_t *>(d_wq), n_blocks);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+}  // namespace jq
