@@ -1,0 +1,489 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_0 x Q8_1 quantized-linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A *step* is one pass of the hot path over one batch of synthetic input: quantize the fp32
+activations to Q8_1 and multiply by the resident Q4_0 weights (one fused kernel in the decode
+regime).  The headline workload is the decode GEMV of configuration 2 at M = 1
+(K = 4096, N = 11008, seed 1, 1 % outlier channels).  The metric is achieved GB/s of
+algorithmic bytes (weights + fp32 activations + fp32 outputs) per step.
+
+Between steps the weights rotate through enough distinct copies to exceed L2 several times, so
+every step streams its weights from HBM.  The K steps are captured into CUDA graphs (blocks of
+up to 128 steps) and timed with CUDA events on the launching stream, max over ranks.
+
+With N > 1 ranks (one process per GPU, launched by torchrun) the layer is N-sharded: every rank
+owns an 11008-row shard of an (11008 * N)-row layer (weak scaling), computes its band of the
+output and the bands are all-gathered along N with NCCL inside the step.
+
+``--impl reference`` times the CPU restatement of the path (quantize, dequantise both operands,
+fp32 matmul) on all host threads; the reference project has no CPU implementation of its own.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "Q4_0xQ8_1 GEMV GB/s at M=1 (cfg2: K=4096, N=11008)"
+UNIT = "GB/s"
+L2_BYTES = 126 * 1024 * 1024
+GRAPH_BLOCK = 128
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 0.0)),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)), "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML, read-only)."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
+        self.sm_max = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _poll_once(self):
+        n = self._nvml
+        if n is None:
+            return
+        try:
+            mhz = int(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM))
+            try:
+                reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            except Exception:
+                reasons = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+            self.samples.append((mhz, reasons))
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._poll_once()
+            self._stop.wait(0.004)
+
+    def start(self):
+        if self._nvml is None:
+            return
+        self._poll_once()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._poll_once()
+
+    def summary(self):
+        if self._nvml is None or not self.samples:
+            return self._nvidia_smi_fallback()
+        n = self._nvml
+        names = {
+            getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(n, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        seen = set()
+        for _, r in self.samples:
+            for bit, name in names.items():
+                if r & bit:
+                    seen.add(name)
+        mhz = sorted(m for m, _ in self.samples)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.sm_max, "reasons": sorted(seen),
+                "samples": len(self.samples)}
+
+    def _nvidia_smi_fallback(self):
+        try:
+            out = subprocess.run(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.active",
+                 "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout.strip()
+            a = [v.strip() for v in out.split(",")]
+            return {"sm_mhz": int(a[0]), "sm_max_mhz": int(a[1]), "reasons": [a[2]], "samples": 1,
+                    "note": "single nvidia-smi sample after the timed region"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement, all host threads
+# ------------------------------------------------------------------------------------------------
+def run_reference(args) -> None:
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from jjjetson_ops_b200 import synth
+    from oracle import jq_oracle as O
+
+    O.build()
+    w, x, lin = synth.make_linear_case(2, 0, 1)
+    wq = O.quantize_q4_0(w)
+    K, N, M = lin.K, lin.N, 1
+    alg = synth.algorithmic_bytes(K, N, M, fused_quantize=True)
+    y = np.empty((M, N), dtype=np.float32)
+    ws = np.empty(M * (K // 128) * 144, dtype=np.uint8)
+    for _ in range(max(args.warmup, 1)):
+        O.linear_cpu_baseline(wq, x, K, N, M, y=y, ws=ws)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.linear_cpu_baseline(wq, x, K, N, M, y=y, ws=ws)
+    dt = time.perf_counter() - t0
+    value = alg * args.steps / dt / 1e9
+    cores = O.num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(K, N, M, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "the whole cfg2 M=1 workload per step (quantize X, dequantise W and X, fp32 "
+                                   "matmul), %d OpenMP threads; the reference has no CPU implementation of the multiply"
+                                   % cores},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(K, N, M, world):
+    return {
+        "workload": "cfg2 decode GEMV: quantize_q8_1 + Q4_0xQ8_1 mul_mat, M=%d, K=%d, N=%d per GPU, seed 1, "
+                    "1%% outlier channels x20" % (M, K, N),
+        "M": M, "K": K, "N_per_gpu": N, "N_total": N * world,
+        "parallelism": "single GPU" if world == 1 else "N-sharded x%d, all-gather of outputs (NCCL)" % world,
+        "l2": "weights rotate through distinct copies totalling > 3x L2 between steps (cold L2)",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def time_graph_steps(torch, step_fn, steps, warmup, barrier):
+    """Times exactly `steps` calls of step_fn(i) with CUDA events; the calls are replayed from
+    CUDA graphs of up to GRAPH_BLOCK steps each."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            step_fn(i)
+    stream.synchronize()
+
+    graphs = []  # (graph, count)
+    used_graph = True
+    try:
+        done = 0
+        while done < steps:
+            n = min(GRAPH_BLOCK, steps - done)
+            if graphs and graphs[-1][1] == n:
+                # identical block: replay the same graph again (step index pattern repeats mod R)
+                graphs.append(graphs[-1])
+            else:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(n):
+                        step_fn(i)
+                graphs.append((g, n))
+            done += n
+        with torch.cuda.stream(stream):
+            graphs[0][0].replay()  # one untimed replay: graph upload
+        stream.synchronize()
+    except Exception as ex:  # capture refused (e.g. by a collective): time plain launches
+        used_graph = False
+        graphs = []
+        sys.stderr.write("[bench] CUDA graph capture unavailable (%r); timing direct launches\n" % (ex,))
+        torch.cuda.synchronize()
+
+    barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        start.record(stream)
+        if used_graph:
+            for g, _ in graphs:
+                g.replay()
+        else:
+            for i in range(steps):
+                step_fn(i)
+        end.record(stream)
+    stream.synchronize()
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(end) / 1e3, used_graph
+
+
+def run_ours(args) -> None:
+    import torch
+
+    from jjjetson_ops_b200 import capi, synth
+
+    rank, world, local = dist_env()
+    if args.gpus != world and world > 1:
+        args.gpus = world
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for this path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: WPS440
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    peaks = measured_peaks()
+    M = args.m
+    w, x_all, lin = synth.make_linear_case(2, 0, 8)
+    K, N = lin.K, lin.N
+    x_host = np.ascontiguousarray(x_all[:M])
+    alg = synth.algorithmic_bytes(K, N, M, fused_quantize=True)
+
+    # resident weights: R distinct copies (rotated row blocks, so the bytes differ) > 3x L2
+    wq0 = capi.quantize_q4_0(torch.from_numpy(w).to(dev))
+    copy_bytes = wq0.numel()
+    R = max(2, -(-3 * L2_BYTES // copy_bytes) + 1)
+    weights = [wq0] + [torch.roll(wq0, shifts=32 * r, dims=0).contiguous() for r in range(1, R)]
+    del w
+    d_x = torch.from_numpy(x_host).to(dev)
+    d_ws = torch.zeros(max(capi.q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
+    d_y = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    gather = torch.zeros((world * M, N), dtype=torch.float32, device=dev) if world > 1 else None
+
+    def step(i):
+        capi.linear_q4_0(weights[i % R], d_x, N, capi.S_D_SUM_Q, ws=d_ws, out=d_y)
+        if gather is not None:
+            dist.all_gather_into_tensor(gather, d_y)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    seconds, used_graph = time_graph_steps(torch, step, args.steps, args.warmup, barrier)
+    sampler.stop()
+    if dist is not None:
+        t = torch.tensor([seconds], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seconds = float(t.item())
+    fault = capi.device_fault()
+
+    # ---- end to end through the host-facing C ABI: pinned host buffers, copies inside the timed region
+    e2e = None
+    if rank == 0 or world > 1:
+        e2e = measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    value = alg * world * args.steps / seconds / 1e9
+    per_gpu_gbs = alg * args.steps / seconds / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic", "config": workload_config(K, N, M, world),
+        "roofline": {
+            "bound": "hbm", "achieved": per_gpu_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": load_traffic_note(),
+            "peak_source": peaks["source"], "kernel": "gemv_dp4a_kernel (fused quantize + multiply)",
+            "algorithmic_bytes_per_launch": alg,
+        },
+        "e2e": e2e,
+        "gpu_launches": args.steps,
+        "clocks": sampler.summary(),
+        "cuda_graph": used_graph,
+        "weight_copies": R,
+        "device_fault": fault,
+    }
+    if world == 1 and not args.no_extras:
+        line["cpu_baseline"] = measure_cpu_baseline(K, N, M, alg)
+        line["extras"] = measure_extras(torch, capi, synth, dev, peaks)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def load_traffic_note():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture, if recorded."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f).get("gemv_dp4a_cfg2_m1_dram_bytes_per_launch")
+    except Exception:
+        return None
+
+
+def measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world):
+    """Same steps through jq_linear_q4_0_host: host x -> device, fused kernel, device y -> host."""
+    import ctypes
+
+    lib = capi.lib()
+    R = len(weights)
+
+    class Handle(ctypes.Structure):
+        pass
+
+    # resident-weight handles need host copies once; reuse two of the device copies to bound setup time
+    n_handles = min(R, 16)
+    handles = []
+    for r in range(n_handles):
+        h = ctypes.c_void_p()
+        host_w = weights[r].cpu().numpy()
+        capi.check(lib.jq_weights_create(host_w.ctypes.data, N, K, ctypes.byref(h)))
+        handles.append(h)
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    y_pin = torch.empty((M, N), dtype=torch.float32).pin_memory()
+    xp, yp = x_pin.data_ptr(), y_pin.data_ptr()
+    steps = min(args.steps, 2000)
+    for i in range(5):
+        capi.check(lib.jq_linear_q4_0_host(handles[i % n_handles], xp, None, yp, M, capi.S_D_SUM_Q))
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        capi.check(lib.jq_linear_q4_0_host(handles[i % n_handles], xp, None, yp, M, capi.S_D_SUM_Q))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    barrier()
+    if dist is not None:
+        t = torch.tensor([dt], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    for h in handles:
+        lib.jq_weights_destroy(h)
+    return {
+        "value": alg * world * steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": int(x_pin.numel() * 4),
+        "d2h_bytes_per_step": int(y_pin.numel() * 4), "steps": steps, "ms_per_step": dt / steps * 1e3,
+        "api": "jq_linear_q4_0_host (weights resident, pinned host activations and outputs, synchronous)",
+        "weight_copies": n_handles,
+    }
+
+
+def measure_cpu_baseline(K, N, M, alg):
+    from jjjetson_ops_b200 import synth
+    from oracle import jq_oracle as O
+
+    O.build()
+    w, x, _ = synth.make_linear_case(2, 0, M)
+    wq = O.quantize_q4_0(w)
+    y = np.empty((M, N), dtype=np.float32)
+    ws = np.empty(M * (K // 128) * 144, dtype=np.uint8)
+    O.linear_cpu_baseline(wq, x, K, N, M, y=y, ws=ws)
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 5.0 or reps < 3:
+        O.linear_cpu_baseline(wq, x, K, N, M, y=y, ws=ws)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": alg * reps / dt / 1e9, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+            "sample": "%d passes of the whole cfg2 M=%d workload in %.1f s (quantize X, dequantise W and X to fp32, "
+                      "fp32 matmul; OpenMP)" % (reps, M, dt)}
+
+
+def measure_extras(torch, capi, synth, dev, peaks):
+    """Secondary numbers on the same box: other batch sizes, the prefill GEMM, the large shapes.
+    Each is timed like the headline (cold-L2 weight rotation, CUDA graph, CUDA events)."""
+    out = {}
+
+    def bench_linear(K, N, M, steps=200, fused=True):
+        rng = np.random.default_rng(1234)
+        wq_bytes = capi.q4_0_bytes(N, K)
+        R = max(2, -(-3 * L2_BYTES // wq_bytes) + 1)
+        base = torch.from_numpy(rng.integers(0, 256, size=wq_bytes, dtype=np.uint8)).to(dev).view(N, -1)
+        # random bytes are valid Q4_0 blocks except that a random fp16 scale may be inf/nan: fix the scales
+        blocks = base.view(N, K // 32, 18)
+        blocks[:, :, 0] = 0
+        blocks[:, :, 1] = 0x20  # d = 2^-7
+        ws_ = [base] + [torch.roll(base, shifts=32 * r, dims=0).contiguous() for r in range(1, R)]
+        x = torch.from_numpy(rng.standard_normal((M, K), dtype=np.float32)).to(dev)
+        ws = torch.zeros(max(capi.q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
+        y = torch.zeros((M, N), dtype=torch.float32, device=dev)
+
+        def step(i):
+            capi.linear_q4_0(ws_[i % R], x, N, capi.S_D_SUM_Q, ws=ws, out=y)
+
+        sec, _ = time_graph_steps(torch, step, steps, 3, lambda: None)
+        del ws_, base
+        torch.cuda.empty_cache()
+        return sec / steps
+
+    for M in (2, 4, 8):
+        t = bench_linear(4096, 11008, M)
+        b = synth.algorithmic_bytes(4096, 11008, M)
+        out["cfg2_M%d" % M] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    t = bench_linear(4096, 4096, 1)
+    b = synth.algorithmic_bytes(4096, 4096, 1)
+    out["cfg1_M1"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    t = bench_linear(8192, 28672, 1, steps=100)
+    b = synth.algorithmic_bytes(8192, 28672, 1)
+    out["cfg4_M1"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    t = bench_linear(11008, 4096, 1)
+    b = synth.algorithmic_bytes(11008, 4096, 1)
+    out["cfg5_down_M1"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    t = bench_linear(4096, 4096, 512, steps=50)
+    o = synth.ops(4096, 4096, 512)
+    out["cfg3_M512"] = {"us": t * 1e6, "TOPS": o / t / 1e12, "frac_int8_peak": o / t / 1e12 / int8_peak,
+                        "int8_peak_tops": int8_peak, "int8_peak_note": "2 x cuBLAS bf16 %s burst" % peaks["source"]}
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4096)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--m", type=int, default=1, help="activation rows of the headline workload (1..8)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary shapes and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps == 4096:
+            args.steps = 200
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,323 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars: bit-exact for the int8 activations, the fp16 (d, s) pairs, the Q4_0 bytes and the int32
+block sums; max|y - ref| / max|ref| <= 1e-5 against the oracle's reference-formula multiply on
+the same quantized inputs (only fp32 summation order differs) and <= 1e-3 against
+dequantise-then-matmul in float64 (with s = d * sum(q)).
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL_FORMULA = 1e-5  # same formula, different fp32 summation order
+TOL_DEQUANT = 1e-3  # the accuracy target against dequantise-then-matmul
+
+
+@pytest.fixture(scope="module")
+def env(native_lib, oracle, cuda_device):
+    import torch
+
+    class Env:
+        c = native_lib
+        O = oracle
+        dev = cuda_device
+        t = torch
+
+        def up(self, a):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device)
+
+    e = Env()
+    yield e
+    assert native_lib.device_fault(clear=True) == 0  # no kernel gave up on a bounded wait
+
+
+def _case(rng, K, N, M, sigma=0.02):
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(sigma)).astype(np.float32)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    return w, x
+
+
+# ------------------------------------------------------------------------------- quantizers
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("s_mode", [0, 1])
+@pytest.mark.parametrize("shape", [(1, 128), (1, 4096), (13, 2048), (5, 640), (2, 160), (3, 32), (64, 11008)])
+def test_quantize_q8_1_bit_exact(env, order, s_mode, shape):
+    M, K = shape
+    rng = np.random.default_rng(100 + M + K)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    if K >= 96:
+        x[M // 2, 64:96] = 0.0  # all-zero group: d = 0 (not the reference's +inf)
+    x[0, 0] = 300.0
+    raw = env.c.quantize_q8_1(env.up(x), order, s_mode).cpu().numpy()
+    assert np.array_equal(raw, env.O.quantize_q8_1(x, order, s_mode))
+
+
+def test_quantize_q8_1_reference_golden(env):
+    """The reference's own test case (tests/test_q8_1.py:65-123) on the device entry."""
+    g = np.load(os.path.join(GOLDEN, "q8_1_ref_seed24.npz"))
+    np.random.seed(24)
+    x = np.ascontiguousarray(np.random.randn(2048, 13, 1, 1).astype(np.float32)[:, :, 0, 0].T)
+    raw = env.c.quantize_q8_1(env.up(x), env.c.ORDER_KSUPER_COL, env.c.S_SUM_X).cpu().numpy()
+    qs, d, s = env.O.parse_q8_1(raw, 208)
+    assert np.array_equal(qs, g["a_qs"])
+    assert np.allclose(d, g["a_scale"], atol=1e-5) and np.allclose(s, g["a_sum"], atol=1e-2)
+
+
+def test_quantize_q4_0_bit_exact(env):
+    from tests.golden.make_q4_0_gguf_golden import make_input
+
+    w = make_input()
+    got = env.c.quantize_q4_0(env.up(w)).cpu().numpy()
+    assert np.array_equal(got, np.load(os.path.join(GOLDEN, "q4_0_gguf_seed5.npz"))["q4_0"])
+    rng = np.random.default_rng(12)
+    w2 = (rng.standard_normal((333, 1024), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    w2[7, 96:128] = 0.0
+    assert np.array_equal(env.c.quantize_q4_0(env.up(w2)).cpu().numpy(), env.O.quantize_q4_0(w2))
+
+
+# ------------------------------------------------------------------------------- block sums
+@pytest.mark.parametrize("order", [0, 1])
+def test_block_sums_bit_exact(env, order):
+    rng = np.random.default_rng(13)
+    K, N, M = 512, 100, 5
+    w, x = _case(rng, K, N, M)
+    wq = env.O.quantize_q4_0(w)
+    xq = env.O.quantize_q8_1(x, order, 1)
+    got = env.c.block_sums(env.up(wq), env.up(xq), K, N, M, order).cpu().numpy()
+    assert np.array_equal(got, env.O.block_sums(wq, xq, K, N, M, order))
+
+
+# ------------------------------------------------------------------------------- the multiply
+def _check_mul_mat(env, wq, x, K, N, M, kernel, order, s_mode, rows=None):
+    """Runs the kernel on (wq, quantized x) and compares against the oracle."""
+    xq = env.O.quantize_q8_1(x, order, s_mode)
+    y = env.c.mul_mat_q4_0_q8_1(env.up(wq), env.up(xq), K, N, M, order, kernel).cpu().numpy()
+    assert y.shape == (M, N) and np.isfinite(y).all()
+    if rows is None:
+        ref = env.O.mul_mat_ref(wq, xq, K, N, M, order)
+        deq = env.O.mul_mat_deq_f64(wq, xq, K, N, M, order)
+        ysel = y
+    else:  # full-size case: the oracle checks a sample of weight rows
+        wsel = np.ascontiguousarray(wq.reshape(N, -1)[rows])
+        ref = env.O.mul_mat_ref(wsel, xq, K, len(rows), M, order)
+        deq = env.O.mul_mat_deq_f64(wsel, xq, K, len(rows), M, order)
+        ysel = y[:, rows]
+    e_ref = env.O.err_max_rel(ysel, ref)
+    assert e_ref <= TOL_FORMULA, (e_ref, kernel)
+    if s_mode == env.c.S_D_SUM_Q:
+        e_deq = env.O.err_max_rel(ysel, deq)
+        assert e_deq <= TOL_DEQUANT, (e_deq, kernel)
+    return y
+
+
+SMALL = [(128, 32, 1), (256, 32, 2), (256, 33, 5), (512, 100, 8), (768, 7, 3), (1024, 257, 1), (256, 1, 1),
+         (2048, 130, 4), (4096, 300, 2), (8192, 70, 1), (11008, 50, 1), (16384, 40, 1), (1280, 64, 8)]
+
+
+@pytest.mark.parametrize("K,N,M", SMALL)
+@pytest.mark.parametrize("order", [0, 1])
+def test_mul_mat_small_shapes_all_kernels(env, K, N, M, order):
+    c = env.c
+    rng = np.random.default_rng(K + N + M)
+    w, x = _case(rng, K, N, M)
+    wq = env.O.quantize_q4_0(w)
+    ran = []
+    for kernel in (c.KERNEL_GENERIC, c.KERNEL_GEMV_DP4A, c.KERNEL_GEMV_MMA, c.KERNEL_GEMM_MMA, c.KERNEL_AUTO):
+        try:
+            _check_mul_mat(env, wq, x, K, N, M, kernel, order, c.S_D_SUM_Q)
+            ran.append(kernel)
+        except c.JqError as e:
+            assert e.status == c.ERR_UNSUPPORTED, e  # a family may refuse a shape, never fail on it
+    assert c.KERNEL_GENERIC in ran and c.KERNEL_AUTO in ran
+    if K % 256 == 0 and M <= 2 and K <= 16384 and not (M == 2 and K > 8192):
+        assert c.KERNEL_GEMV_DP4A in ran
+    if K % 256 == 0 and K <= 6144:
+        assert c.KERNEL_GEMV_MMA in ran
+
+
+def test_mul_mat_reference_s_mode(env):
+    """With the reference's s = sum(x) the kernels still follow the reference formula exactly;
+    only the distance to dequantise-then-matmul grows (about 1e-2)."""
+    c = env.c
+    rng = np.random.default_rng(77)
+    K, N, M = 1024, 96, 3
+    w, x = _case(rng, K, N, M)
+    wq = env.O.quantize_q4_0(w)
+    for kernel in (c.KERNEL_GENERIC, c.KERNEL_GEMV_MMA, c.KERNEL_AUTO):
+        _check_mul_mat(env, wq, x, K, N, M, kernel, c.ORDER_COL_KSUPER, c.S_SUM_X)
+
+
+def test_mul_mat_empty_and_degenerate(env):
+    c, t = env.c, env.t
+    w = t.zeros(18 * 4 * 8, dtype=t.uint8, device=env.dev)
+    xq = t.zeros(144, dtype=t.uint8, device=env.dev)
+    assert c.mul_mat_q4_0_q8_1(w, xq, 128, 0, 1).shape == (1, 0)
+    assert c.mul_mat_q4_0_q8_1(w, xq, 128, 8, 0).shape == (0, 8)
+    y = c.mul_mat_q4_0_q8_1(w, xq, 128, 8, 1)  # all-zero blocks: d = 0 everywhere -> exact zeros
+    assert not y.cpu().numpy().any()
+    with pytest.raises(c.JqError) as ei:
+        c.mul_mat_q4_0_q8_1(w, xq, 96, 8, 1)
+    assert ei.value.status == c.ERR_SHAPE
+
+
+def _config_case(env, cfg, linear, M, rows=None):
+    from jjjetson_ops_b200 import synth
+
+    w, x, lin = synth.make_linear_case(cfg, linear, M)
+    wq = env.c.quantize_q4_0(env.up(w)).cpu().numpy()  # the device quantizer is itself checked above
+    check = slice(None) if rows is None and w.shape[0] <= 4096 else rows
+    if check is not None:  # the synthetic weights really are what the oracle's quantizer makes of them
+        assert np.array_equal(wq[check], env.O.quantize_q4_0(np.ascontiguousarray(w[check])))
+    return wq, x, lin
+
+
+def test_config1_decode_gemv(env):
+    c = env.c
+    wq, x, lin = _config_case(env, 1, 0, 1)
+    for kernel in (c.KERNEL_AUTO, c.KERNEL_GEMV_DP4A, c.KERNEL_GEMV_MMA, c.KERNEL_GENERIC):
+        _check_mul_mat(env, wq, x, lin.K, lin.N, 1, kernel, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_config2_decode_batch(env, M):
+    c = env.c
+    wq, x, lin = _config_case(env, 2, 0, M)
+    kernels = [c.KERNEL_AUTO, c.KERNEL_GEMV_MMA] + ([c.KERNEL_GEMV_DP4A] if M <= 2 else [])
+    for kernel in kernels:
+        _check_mul_mat(env, wq, x, lin.K, lin.N, M, kernel, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+
+
+def test_config3_prefill(env):
+    c = env.c
+    wq, x, lin = _config_case(env, 3, 0, 512)
+    _check_mul_mat(env, wq, x, lin.K, lin.N, 512, c.KERNEL_AUTO, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+    _check_mul_mat(env, wq, x, lin.K, lin.N, 512, c.KERNEL_AUTO, c.ORDER_KSUPER_COL, c.S_D_SUM_Q)
+
+
+def test_config4_large_shapes(env):
+    c = env.c
+    rows = np.sort(np.random.default_rng(44).choice(28672, size=96, replace=False))
+    wq, x, lin = _config_case(env, 4, 0, None, rows=rows)
+    _check_mul_mat(env, wq, x[:1], lin.K, lin.N, 1, c.KERNEL_AUTO, c.ORDER_COL_KSUPER, c.S_D_SUM_Q, rows=rows)
+    _check_mul_mat(env, wq, x, lin.K, lin.N, 2048, c.KERNEL_AUTO, c.ORDER_COL_KSUPER, c.S_D_SUM_Q, rows=rows)
+
+
+@pytest.mark.parametrize("M", [1, 128])
+def test_config5_layer_chain(env, M):
+    c = env.c
+    for linear in range(5):
+        rows = np.sort(np.random.default_rng(50 + linear).choice(4096, size=128, replace=False))
+        wq, x, lin = _config_case(env, 5, linear, M, rows=rows)
+        _check_mul_mat(env, wq, x, lin.K, lin.N, M, c.KERNEL_AUTO, c.ORDER_COL_KSUPER, c.S_D_SUM_Q, rows=rows)
+
+
+# ------------------------------------------------------------------------------- fused linear
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 1), (4096, 11008, 2), (4096, 11008, 8), (8192, 2048, 1),
+                                   (11008, 4096, 1), (2048, 100, 5), (4096, 512, 64), (1280, 96, 3)])
+@pytest.mark.parametrize("s_mode", [0, 1])
+def test_linear_fused_equals_two_steps(env, K, N, M, s_mode):
+    c = env.c
+    rng = np.random.default_rng(K * 3 + N + M)
+    w, x = _case(rng, K, N, M)
+    wq = env.O.quantize_q4_0(w)
+    d_w, d_x = env.up(wq), env.up(x)
+    ws = env.t.zeros(c.q8_1_bytes(K, M), dtype=env.t.uint8, device=env.dev)
+    y = c.linear_q4_0(d_w, d_x, N, s_mode, ws=ws).cpu().numpy()
+    xq = env.O.quantize_q8_1(x, c.ORDER_COL_KSUPER, s_mode)
+    assert np.array_equal(ws.cpu().numpy(), xq)  # the workspace holds the quantized activations
+    y2 = c.mul_mat_q4_0_q8_1(d_w, env.up(xq), K, N, M, c.ORDER_COL_KSUPER).cpu().numpy()
+    assert np.array_equal(y, y2)  # same kernels, same arithmetic: identical bits
+    assert env.O.err_max_rel(y, env.O.mul_mat_ref(wq, xq, K, N, M)) <= TOL_FORMULA
+
+
+def test_multiply_is_linear_in_the_integer_activations(env):
+    """Size-independent property at full cfg2 size: block sums of q1 + q2 equal the sum of block
+    sums, checked through the real kernels with unit scales (d = 1, s = 0 -> y = d4 * sumi summed)."""
+    c = env.c
+    from jjjetson_ops_b200 import synth
+
+    w, _, lin = synth.make_linear_case(2, 0, 1)
+    d_w = c.quantize_q4_0(env.up(w))
+    K, N = lin.K, lin.N
+    rng = np.random.default_rng(91)
+    qa = rng.integers(-60, 60, size=K, dtype=np.int8)
+    qb = rng.integers(-60, 60, size=K, dtype=np.int8)
+
+    def blocks(q):
+        b = np.zeros((K // 128, 144), dtype=np.uint8)
+        b[:, :16] = np.tile(np.array([1.0, 0.0], dtype=np.float16).view(np.uint8), 4)
+        b[:, 16:] = q.reshape(K // 128, 128).view(np.uint8)
+        return b.reshape(-1)
+
+    ys = [c.mul_mat_q4_0_q8_1(d_w, env.up(blocks(q)), K, N, 1).cpu().numpy().astype(np.float64)
+          for q in (qa, qb, (qa + qb).astype(np.int8))]
+    scale = np.abs(ys[2]).max()
+    assert np.abs(ys[0] + ys[1] - ys[2]).max() <= 1e-5 * scale
+
+
+# ------------------------------------------------------------------------------- host entry points
+def test_reference_module_flow_q8_1(env):
+    """The reference's tests/test_q8_1.py:65-123, against this library's q8_1_me module."""
+    import jjjetson_ops_b200 as pkg
+
+    q8_1_me, _ = pkg.import_reference_modules()
+    np.random.seed(24)
+    input_np = np.asfortranarray(np.random.randn(2048, 13, 1, 1).astype(np.float32))
+    n_blocks = 13 * ((2048 + 127) // 128)
+    q_output = np.zeros(n_blocks * 144, dtype=np.uint8)
+    q8_1_me.quantize(input_np, q_output, [2048, 13, 1, 1])
+    qs, scale, ssum = q8_1_me.parse(q_output, n_blocks)
+    g = np.load(os.path.join(GOLDEN, "q8_1_ref_seed24.npz"))
+    assert qs.shape == g["a_qs"].shape and np.all(qs == g["a_qs"])
+    assert np.allclose(scale, g["a_scale"], atol=1e-5) and np.allclose(ssum, g["a_sum"], atol=1e-2)
+
+
+@pytest.mark.parametrize("M", [1, 5])
+def test_reference_module_flow_mmq(env, M):
+    import jjjetson_ops_b200 as pkg
+
+    _, mm = pkg.import_reference_modules()
+    rng = np.random.default_rng(5 + M)
+    K, N = 1024, 200
+    w, x = _case(rng, K, N, M)
+    wq = env.O.quantize_q4_0(w)
+    ws = np.zeros(env.c.q8_1_bytes(K, M), dtype=np.uint8)
+    y = np.zeros((M, N), dtype=np.float32)
+    mm.mmq(wq.reshape(-1), x, ws, y, [K, M, 1, 1], N, K)
+    xq = env.O.quantize_q8_1(x, env.c.ORDER_KSUPER_COL, env.c.S_SUM_X)  # what q8_1() writes
+    assert np.array_equal(ws, xq)
+    assert env.O.err_max_rel(y, env.O.mul_mat_ref(wq, xq, K, N, M, env.c.ORDER_KSUPER_COL)) <= TOL_FORMULA
+    y2 = np.zeros_like(y)
+    mm.mmq(wq.reshape(-1), x, ws, y2, [K, M, 1, 1], N, K, s_mode=1)
+    xq1 = env.O.quantize_q8_1(x, env.c.ORDER_KSUPER_COL, env.c.S_D_SUM_Q)
+    assert env.O.err_max_rel(y2, env.O.mul_mat_deq_f64(wq, xq1, K, N, M, env.c.ORDER_KSUPER_COL)) <= TOL_DEQUANT
+
+
+def test_resident_weights_host_linear(env):
+    c = env.c
+    rng = np.random.default_rng(31)
+    K, N = 4096, 1000
+    w, x = _case(rng, K, N, 8)
+    wq = env.O.quantize_q4_0(w)
+    rw = c.ResidentWeights(wq, N, K)
+    try:
+        for M in (1, 8, 3):
+            xin = np.ascontiguousarray(x[:M])
+            y = np.zeros((M, N), dtype=np.float32)
+            ws = np.zeros(c.q8_1_bytes(K, M), dtype=np.uint8)
+            rw.linear(xin.ctypes.data, y.ctypes.data, M, c.S_D_SUM_Q, ws.ctypes.data)
+            xq = env.O.quantize_q8_1(xin, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+            assert np.array_equal(ws, xq)
+            assert env.O.err_max_rel(y, env.O.mul_mat_ref(wq, xq, K, N, M)) <= TOL_FORMULA
+    finally:
+        rw.close()
+
+
+def test_device_hw_info(env):
+    info = env.c.query_device_hw_info(0)
+    assert info["sm_count"] > 0 and info["cc_major"] >= 10, info
+    assert info["peak_dram_gbs"] > 1000 and info["peak_int8_dense_tops"] > 1000

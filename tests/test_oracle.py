@@ -106,8 +106,8 @@ def test_block_sums_and_formulas(oracle):
     xq0 = oracle.quantize_q8_1(x, 1, oracle.S_SUM_X)
     e0 = oracle.err_max_rel(oracle.mul_mat_ref(wq, xq0, K, N, M, 1), oracle.mul_mat_deq_f64(wq, xq0, K, N, M, 1))
     assert 1e-3 < e0 < 5e-2
-    # dequantised weights are close to the originals
-    assert np.abs(oracle.dequantize_q4_0(wq, K) - w).max() <= np.abs(w).max() / 8 * 0.51 + 1e-6
+    # dequantised weights are close to the originals (half a step, a full step where +max clamps to q = 15)
+    assert np.abs(oracle.dequantize_q4_0(wq, K) - w).max() <= np.abs(w).max() / 8 * 1.01 + 1e-6
 
 
 def test_cpu_baseline_path_matches_yardstick(oracle):
