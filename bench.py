@@ -194,6 +194,8 @@ def workload_config(K, N, M, world):
         "M": M, "K": K, "N_per_gpu": N, "N_total": N * world,
         "parallelism": "single GPU" if world == 1 else "N-sharded x%d, all-gather of outputs (NCCL)" % world,
         "l2": "weights rotate through distinct copies totalling > 3x L2 between steps (cold L2)",
+        "overlap": "steps are launched with programmatic dependent launch; JQ_OPT_STATIC_WEIGHTS=1 lets a step "
+                   "prefetch its weights while the previous step drains (activations/outputs stay ordered)",
     }
 
 
@@ -274,6 +276,9 @@ def run_ours(args) -> None:
         if dist is not None:
             dist.barrier()
 
+    # inference setting: weights are uploaded once and never rewritten, so consecutive steps may
+    # overlap the next step's weight stream with the previous step's tail
+    capi.set_option(capi.OPT_STATIC_WEIGHTS, 0 if args.no_overlap else 1)
     peaks = measured_peaks()
     M = args.m
     w, x_all, lin = synth.make_linear_case(2, 0, 8)
@@ -476,6 +481,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--m", type=int, default=1, help="activation rows of the headline workload (1..8)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary shapes and the CPU baseline")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="do not let a step's weight stream start before the previous step has finished")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 4096:

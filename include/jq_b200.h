@@ -67,6 +67,19 @@ typedef enum jq_kernel {
     JQ_KERNEL_GEMM_MMA = 4   /* M > 8: tiled int8 tensor-core GEMM with per-block rescale */
 } jq_kernel;
 
+/* Process-wide switches. */
+typedef enum jq_option {
+    /* 1: the caller promises that weight buffers are never written by work queued just ahead of a
+     * multiply on the same stream (true for inference: weights are uploaded once).  The decode
+     * kernels then start streaming weights while the previous kernel on the stream is still
+     * draining, before they wait for it; activations and outputs are always ordered normally.
+     * 0 (default): the weight stream, too, waits for the previous kernel. */
+    JQ_OPT_STATIC_WEIGHTS = 0,
+    JQ_OPT_COUNT_ = 1
+} jq_option;
+int jq_set_option(int option, int value);
+int jq_get_option(int option, int *value_out);
+
 const char *jq_status_string(int status);
 /* Message of the last failure on the calling thread ("" if none). */
 const char *jq_last_error(void);

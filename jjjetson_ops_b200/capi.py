@@ -50,6 +50,8 @@ _SIGS = {
     "jq_status_string": (ctypes.c_char_p, [_ci]),
     "jq_last_error": (ctypes.c_char_p, []),
     "jq_version": (_ci, []),
+    "jq_set_option": (_ci, [_ci, _ci]),
+    "jq_get_option": (_ci, [_ci, ctypes.POINTER(_ci)]),
     "jq_q8_1_bytes": (_sz, [_i64, _i64]),
     "jq_q4_0_bytes": (_sz, [_i64, _i64]),
     "jq_quantize_q8_1_device": (_ci, [_vp, _vp, _vp, _i64, _i64, _ci, _ci]),
@@ -90,6 +92,19 @@ def last_error() -> str:
 def check(status: int) -> None:
     if status != OK:
         raise JqError(status, last_error())
+
+
+OPT_STATIC_WEIGHTS = 0
+
+
+def set_option(option: int, value: int) -> None:
+    check(_lib.jq_set_option(option, value))
+
+
+def get_option(option: int) -> int:
+    v = ctypes.c_int(0)
+    check(_lib.jq_get_option(option, ctypes.byref(v)))
+    return int(v.value)
 
 
 def q8_1_bytes(K: int, M: int) -> int:

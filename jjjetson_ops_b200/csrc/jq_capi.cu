@@ -1,6 +1,7 @@
 // C ABI of the library: argument checking, kernel selection, the reference-style host wrappers,
 // resident weights, and the device description.  Declarations and the reference lines each entry
 // point replaces are in include/jq_b200.h.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -26,8 +27,13 @@ struct PerDevice {
 };
 PerDevice g_dev[MAX_DEVICES];
 std::mutex g_dev_mutex;
+std::atomic<int> g_options[JQ_OPT_COUNT_];
 
 }  // namespace
+
+int option_value(int option) {
+    return option >= 0 && option < JQ_OPT_COUNT_ ? g_options[option].load(std::memory_order_relaxed) : 0;
+}
 
 int set_error(int status, const char *fmt, ...) {
     char buf[512];
@@ -53,6 +59,7 @@ int device_caps(DeviceCaps *out) {
         int major = 0, minor = 0;
         JQ_CUDA_TRY(cudaDeviceGetAttribute(&d.caps.sm_count, cudaDevAttrMultiProcessorCount, dev));
         JQ_CUDA_TRY(cudaDeviceGetAttribute(&d.caps.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        JQ_CUDA_TRY(cudaDeviceGetAttribute(&d.caps.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
         JQ_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         JQ_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
         d.caps.cc = major * 10 + minor;
@@ -151,6 +158,18 @@ const char *jq_last_error(void) { return t_last_error.c_str(); }
 
 int jq_version(void) { return 100; }
 
+int jq_set_option(int option, int value) {
+    if (option < 0 || option >= JQ_OPT_COUNT_) return set_error(JQ_ERR_INVALID_ARG, "unknown option %d", option);
+    g_options[option].store(value, std::memory_order_relaxed);
+    return JQ_OK;
+}
+
+int jq_get_option(int option, int *value_out) {
+    if (option < 0 || option >= JQ_OPT_COUNT_ || !value_out) return set_error(JQ_ERR_INVALID_ARG, "unknown option %d", option);
+    *value_out = option_value(option);
+    return JQ_OK;
+}
+
 size_t jq_q8_1_bytes(int64_t K, int64_t M) {
     if (K <= 0 || M <= 0) return 0;
     return (size_t)M * (size_t)((K + SUPER - 1) / SUPER) * Q8_BYTES;
@@ -203,8 +222,9 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
         return set_error(JQ_ERR_ALIGN, "activations and workspace must be 16-byte aligned");
     if (((uintptr_t)d_w & 1u) != 0) return set_error(JQ_ERR_ALIGN, "Q4_0 blocks must be 2-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (K > 0 && N > 0 && M <= 8) {
-        // decode regime: quantization runs in the multiply kernel's prologue
+    // Decode regime: with few activation blocks the quantizer runs in the multiply kernel's own
+    // prologue (every CTA redoes it, which only pays while it is a handful of blocks per warp).
+    if (K > 0 && N > 0 && M <= 8 && M * (K / SUPER) <= 64) {
         int rc = JQ_ERR_UNSUPPORTED;
         if (M <= 2) rc = launch_gemv_dp4a(st, d_w, nullptr, d_x, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, s_mode);
         if (rc == JQ_ERR_UNSUPPORTED)

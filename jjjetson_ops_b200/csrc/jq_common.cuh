@@ -40,9 +40,12 @@ int cuda_error(cudaError_t e, const char *what);  // JQ_ERR_CUDA with the runtim
 struct DeviceCaps {
     int sm_count = 0;
     int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
+    int smem_per_sm = 0; // shared memory per multiprocessor
     int cc = 0;          // major*10 + minor
 };
 int device_caps(DeviceCaps *out);  // for the current device
+
+int option_value(int option);       // process-wide settings of jq_set_option()
 
 // Device address (on the current device) of the word a kernel sets when one of its bounded waits
 // gives up; nullptr if it cannot be obtained.  Kernels receive it as a parameter.
@@ -82,6 +85,29 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// Shared-memory loads by 32-bit shared address: keeps address arithmetic in 32 bits and the load in
+// the shared state space whatever the compiler can prove about the pointer.
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return (uint32_t)v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // ---- mbarrier -------------------------------------------------------------------------------

@@ -26,7 +26,8 @@ namespace jq {
 namespace {
 
 constexpr int GV_MAX_STAGES = 8;
-constexpr int GV_BAR_BYTES = 128;  // full[8] + empty[8] mbarriers
+constexpr int GV_BAR_BYTES = 256;  // full[8] + empty[8] ring mbarriers, red_full[4] + red_empty[4] (+ spare)
+constexpr int GV_RED_SLOTS = 4;
 constexpr uint32_t MASK4 = 0x0F0F0F0Fu;
 
 struct GemvParams {
@@ -43,9 +44,16 @@ struct GemvParams {
     uint32_t row_stride;   // distance between rows inside a stage (>= row_bytes)
     uint32_t stage_bytes;
     uint32_t x_bytes;      // shared bytes reserved for the quantized activations
+    uint32_t x_pitch;      // bytes between two activation rows there (padded against bank conflicts)
     int stages;
     int rows_per_stage;
+    int prefetch_early;    // the weight stream may start before the preceding kernel in the stream has finished
 };
+
+// Programmatic dependent launch: let the next kernel in the stream be scheduled early, and wait
+// for the previous one (and its memory operations) before touching anything it may have written.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ void cta_row_range(int64_t N, int64_t *begin, int64_t *end) {
     *begin = (int64_t)blockIdx.x * N / gridDim.x;
@@ -86,18 +94,33 @@ template <int NW>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, int warp, int lane) {
     const int total = p.M * p.n_super;
     if (p.x_f32 != nullptr) {
-        for (int idx = warp; idx < total; idx += NW) {
-            const int m = idx / p.n_super, ks = idx - m * p.n_super;
-            const float4 xi = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
-            uint32_t ds;
-            const uint32_t q = quantize_group_q8_1(xi, p.s_mode, &ds);
-            uint8_t *blk = xs + (size_t)idx * Q8_BYTES;
-            reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
-            if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
-            if (p.xq_out != nullptr && blockIdx.x == 0) {
-                uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-                reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = q;
-                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = ds;
+        constexpr int U = 8;  // loads in flight per warp: the prologue is latency-, not bandwidth-bound
+        for (int base = warp; base < total; base += NW * U) {
+            float4 xi[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * NW;
+                xi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < total) {
+                    const int m = idx / p.n_super, ks = idx - m * p.n_super;
+                    xi[u] = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * NW;  // uniform across the warp
+                if (idx >= total) break;
+                uint32_t ds;
+                const uint32_t q = quantize_group_q8_1(xi[u], p.s_mode, &ds);
+                const int m = idx / p.n_super, ks = idx - m * p.n_super;
+                uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+                reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
+                if (p.xq_out != nullptr && blockIdx.x == 0) {
+                    uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+                    reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = q;
+                    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = ds;
+                }
             }
         }
     } else {
@@ -106,7 +129,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
             const int idx = i / 9, part = i - idx * 9;
             const int m = idx / p.n_super, ks = idx - m * p.n_super;
             const uint8_t *g = p.xq + (size_t)q8_block_index(ks, m, p.n_super, p.M, p.order) * Q8_BYTES;
-            reinterpret_cast<uint4 *>(xs + (size_t)idx * Q8_BYTES)[part] =
+            reinterpret_cast<uint4 *>(xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES)[part] =
                 __ldg(reinterpret_cast<const uint4 *>(g) + part);
         }
     }
@@ -117,8 +140,8 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
 // dp4a variant: one warp per weight row, one lane per 128-value slice (four Q4_0 blocks = 72
 // bytes, read as nine conflict-free 8-byte shared loads), activations of that slice in registers.
 // ------------------------------------------------------------------------------------------------
-template <int M_T, int NSB, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvParams p) {
+template <int M_T, int NSB, int NW, int MINB>
+__global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + GV_MAX_STAGES;
@@ -135,10 +158,15 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvP
     }
     __syncthreads();
 
+    griddep_launch_dependents();
     if (warp == NW) {
-        if (lane == 0) gemv_producer<false>(p, full, empty, ring);
+        if (lane == 0) {
+            if (!p.prefetch_early) griddep_wait();
+            gemv_producer<false>(p, full, empty, ring);
+        }
         return;
     }
+    griddep_wait();  // activations may come from, and outputs may be read by, the previous kernel
 
     stage_activations<NW>(p, xs, warp, lane);
 
@@ -151,7 +179,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvP
 #pragma unroll
         for (int m = 0; m < M_T; ++m) {
             if (sb < p.n_super && m < p.M) {
-                const uint4 *b = reinterpret_cast<const uint4 *>(xs + (size_t)(m * p.n_super + sb) * Q8_BYTES);
+                const uint4 *b = reinterpret_cast<const uint4 *>(xs + (size_t)m * p.x_pitch + (size_t)sb * Q8_BYTES);
                 const uint4 ds = b[0];
                 const uint32_t dsv[4] = {ds.x, ds.y, ds.z, ds.w};
 #pragma unroll
@@ -180,17 +208,18 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvP
     cta_row_range(p.N, &r_begin, &r_end);
     const int R = p.rows_per_stage;
     const int n_chunks = (int)((r_end - r_begin + R - 1) / R);
+    const uint32_t ring_addr = smem_u32(ring);
 
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % p.stages;
         const uint32_t round = (uint32_t)(c / p.stages);
         if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
-        const uint8_t *stage = ring + (size_t)s * p.stage_bytes;
+        const uint32_t stage = ring_addr + (uint32_t)s * p.stage_bytes;
         const int64_t r0 = r_begin + (int64_t)c * R;
         const int rows = (int)min((int64_t)R, r_end - r0);
 
         for (int r = warp; r < rows; r += NW) {
-            const uint8_t *rowp = stage + (size_t)r * p.row_bytes;
+            const uint32_t rowp = stage + (uint32_t)r * p.row_bytes;
             float acc[M_T];
 #pragma unroll
             for (int m = 0; m < M_T; ++m) acc[m] = 0.0f;
@@ -199,10 +228,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvP
                 const int sb = lane + 32 * i;
                 if (sb < p.n_super) {
                     uint32_t wv[18];
-                    const uint2 *src = reinterpret_cast<const uint2 *>(rowp + sb * 72);
 #pragma unroll
                     for (int j = 0; j < 9; ++j) {
-                        const uint2 v = src[j];
+                        const uint2 v = lds_v2(rowp + (uint32_t)sb * 72u + 8u * j);
                         wv[2 * j] = v.x;
                         wv[2 * j + 1] = v.y;
                     }
@@ -266,12 +294,14 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_dp4a_kernel(const GemvP
 // Partial fp32 sums of the NW warps are added in a fixed order through shared memory.
 // ------------------------------------------------------------------------------------------------
 template <int KBW, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + GV_MAX_STAGES;
-    float *red = reinterpret_cast<float *>(smem + GV_BAR_BYTES);  // [2][NW][128]
-    uint8_t *xs = smem + GV_BAR_BYTES + 2 * NW * 128 * sizeof(float);
+    uint64_t *red_full = empty + GV_MAX_STAGES;
+    uint64_t *red_empty = red_full + GV_RED_SLOTS;
+    float *red = reinterpret_cast<float *>(smem + GV_BAR_BYTES);  // [GV_RED_SLOTS][NW][128]
+    uint8_t *xs = smem + GV_BAR_BYTES + GV_RED_SLOTS * NW * 128 * sizeof(float);
     uint8_t *ring = xs + p.x_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -280,12 +310,49 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvPa
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NW);
         }
+        for (int s = 0; s < GV_RED_SLOTS; ++s) {
+            mbar_init(&red_full[s], NW);
+            mbar_init(&red_empty[s], 1);
+        }
         fence_mbar_init();
     }
     __syncthreads();
 
-    if (warp == NW) {
-        if (lane == 0) gemv_producer<true>(p, full, empty, ring);
+    int64_t r_begin, r_end;
+    cta_row_range(p.N, &r_begin, &r_end);
+    const int n_chunks = (int)((r_end - r_begin + 15) / 16);
+
+    griddep_launch_dependents();
+    if (warp == NW) {  // weight stream
+        if (lane == 0) {
+            if (!p.prefetch_early) griddep_wait();
+            gemv_producer<true>(p, full, empty, ring);
+        }
+        return;
+    }
+    griddep_wait();
+    if (warp == NW + 1) {
+        // Reducer: adds the NW partial tiles in a fixed order and writes the outputs, so that the
+        // compute warps never wait for one another.
+        for (int c = 0; c < n_chunks; ++c) {
+            const int slot = c % GV_RED_SLOTS;
+            const uint32_t round = (uint32_t)(c / GV_RED_SLOTS);
+            if (!mbar_wait_bounded(&red_full[slot], round & 1u, p.fault)) return;
+            const int64_t r0 = r_begin + (int64_t)c * 16;
+            const int rows = (int)min((int64_t)16, r_end - r0);
+            const float *src = red + (size_t)slot * NW * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = lane + 32 * j;  // idx = row * 8 + col
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) v += src[w * 128 + idx];
+                const int row = idx >> 3, col = idx & 7;
+                if (row < rows && col < p.M) p.y[(size_t)col * p.N + (r0 + row)] = v;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_empty[slot]);
+        }
         return;
     }
 
@@ -294,6 +361,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvPa
     const int g = lane >> 2, t = lane & 3;
     const int nb = p.K / QK;
     const int kb0 = warp * KBW;
+    const uint32_t xs_addr = smem_u32(xs);
+    const uint32_t ring_addr = smem_u32(ring);
     // B fragments (column g) and scales (columns 2t, 2t+1) of this warp's K slice.
     uint32_t xb0[KBW], xb1[KBW];
     float xd0[KBW], xd1[KBW], xm0[KBW], xm1[KBW];
@@ -305,40 +374,34 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvPa
         if (kb < nb) {
             const int ks = kb >> 2, sub = kb & 3;
             if (g < p.M) {
-                const uint8_t *b = xs + (size_t)(g * p.n_super + ks) * Q8_BYTES + Q8_QS_OFFSET + sub * QK;
-                xb0[j] = reinterpret_cast<const uint32_t *>(b)[t];
-                xb1[j] = reinterpret_cast<const uint32_t *>(b)[t + 4];
+                const uint32_t b = xs_addr + (uint32_t)g * p.x_pitch + (uint32_t)ks * Q8_BYTES + Q8_QS_OFFSET + sub * QK;
+                xb0[j] = lds_u32(b + 4u * t);
+                xb1[j] = lds_u32(b + 4u * (t + 4));
             }
             if (2 * t < p.M) {
-                const uint32_t ds = reinterpret_cast<const uint32_t *>(xs + (size_t)((2 * t) * p.n_super + ks) * Q8_BYTES)[sub];
+                const uint32_t ds = lds_u32(xs_addr + (uint32_t)(2 * t) * p.x_pitch + (uint32_t)ks * Q8_BYTES + 4u * sub);
                 xd0[j] = half_bits_to_float(ds & 0xFFFFu);
                 xm0[j] = -8.0f * half_bits_to_float(ds >> 16);
             }
             if (2 * t + 1 < p.M) {
-                const uint32_t ds =
-                    reinterpret_cast<const uint32_t *>(xs + (size_t)((2 * t + 1) * p.n_super + ks) * Q8_BYTES)[sub];
+                const uint32_t ds = lds_u32(xs_addr + (uint32_t)(2 * t + 1) * p.x_pitch + (uint32_t)ks * Q8_BYTES + 4u * sub);
                 xd1[j] = half_bits_to_float(ds & 0xFFFFu);
                 xm1[j] = -8.0f * half_bits_to_float(ds >> 16);
             }
         }
     }
 
-    int64_t r_begin, r_end;
-    cta_row_range(p.N, &r_begin, &r_end);
-    const int n_chunks = (int)((r_end - r_begin + 15) / 16);
     const int zero4[4] = {0, 0, 0, 0};
 
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % p.stages;
         const uint32_t round = (uint32_t)(c / p.stages);
         if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
-        const uint8_t *stage = ring + (size_t)s * p.stage_bytes;
-        const int64_t r0 = r_begin + (int64_t)c * 16;
-        const int rows = (int)min((int64_t)16, r_end - r0);
+        const uint32_t stage = ring_addr + (uint32_t)s * p.stage_bytes;
 
         float acc[4] = {0.f, 0.f, 0.f, 0.f};  // (row g, col 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
-        const uint8_t *row_lo = stage + (size_t)g * p.row_stride;
-        const uint8_t *row_hi = stage + (size_t)(g + 8) * p.row_stride;
+        const uint32_t row_lo = stage + (uint32_t)g * p.row_stride;
+        const uint32_t row_hi = stage + (uint32_t)(g + 8) * p.row_stride;
 #pragma unroll
         for (int jp = 0; jp < KBW / 2; ++jp) {
             const int kbe = kb0 + 2 * jp;  // even block, 4-byte aligned start at byte 18*kbe
@@ -347,16 +410,15 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvPa
                 float d_even[2], d_odd[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint8_t *pr = (h == 0 ? row_lo : row_hi) + (size_t)kbe * Q4_BYTES;
-                    const uint32_t *pw = reinterpret_cast<const uint32_t *>(pr);
-                    const uint32_t u0 = pw[t], u1 = pw[t + 1], u2 = pw[5 + t];
+                    const uint32_t pr = (h == 0 ? row_lo : row_hi) + (uint32_t)kbe * Q4_BYTES;
+                    const uint32_t u0 = lds_u32(pr + 4u * t), u1 = lds_u32(pr + 4u * t + 4u), u2 = lds_u32(pr + 4u * t + 20u);
                     const uint32_t we = __funnelshift_r(u0, u1, 16);  // word t of the even block
                     a_even[h] = we & MASK4;              // a0 / a1: weights 4t..4t+3
                     a_even[2 + h] = (we >> 4) & MASK4;   // a2 / a3: weights 16+4t..
                     a_odd[h] = u2 & MASK4;
                     a_odd[2 + h] = (u2 >> 4) & MASK4;
-                    d_even[h] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(pr));
-                    d_odd[h] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(pr + Q4_BYTES));
+                    d_even[h] = half_bits_to_float(lds_u16(pr));
+                    d_odd[h] = half_bits_to_float(lds_u16(pr + Q4_BYTES));
                 }
                 int ce[4], co[4];
                 {
@@ -378,26 +440,17 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) gemv_mma_kernel(const GemvPa
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);  // the stage's bytes are in registers / consumed
+        if (lane == 0) mbar_arrive(&empty[s]);  // the stage's bytes have been consumed
 
-        // Cross-warp reduction, double buffered by tile parity: one barrier per tile.
-        float *mine = red + ((size_t)(c & 1) * NW + warp) * 128;
-        mine[(g)*8 + 2 * t] = acc[0];
-        mine[(g)*8 + 2 * t + 1] = acc[1];
-        mine[(g + 8) * 8 + 2 * t] = acc[2];
-        mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-        named_bar_sync(2, NW * 32);
-        const int tid = warp * 32 + lane;
-        if (tid < 128) {
-            const int row = tid >> 3, col = tid & 7;
-            if (row < rows && col < p.M) {
-                const float *src = red + (size_t)(c & 1) * NW * 128 + tid;
-                float v = 0.0f;
-#pragma unroll
-                for (int w = 0; w < NW; ++w) v += src[w * 128];
-                p.y[(size_t)col * p.N + (r0 + row)] = v;
-            }
-        }
+        // hand the partial 16 x 8 tile to the reducer warp
+        const int slot = c % GV_RED_SLOTS;
+        const uint32_t rround = (uint32_t)(c / GV_RED_SLOTS);
+        if (rround > 0 && !mbar_wait_bounded(&red_empty[slot], (rround - 1) & 1u, p.fault)) return;
+        float *mine = red + ((size_t)slot * NW + warp) * 128;
+        *reinterpret_cast<float2 *>(&mine[g * 8 + 2 * t]) = make_float2(acc[0], acc[1]);
+        *reinterpret_cast<float2 *>(&mine[(g + 8) * 8 + 2 * t]) = make_float2(acc[2], acc[3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&red_full[slot]);
     }
 }
 
@@ -421,11 +474,30 @@ int ensure_smem_attr(void (*kernel)(const GemvParams), int bytes) {
         }
     }
     JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    // ask for the largest shared-memory carve-out so that two CTAs of ~110 KB fit one SM
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     if (used < 32) table[used++] = Entry{(const void *)kernel, dev, bytes};
     return JQ_OK;
 }
 
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while its
+// predecessor in the stream drains; it orders itself with griddepcontrol.wait.
+int launch_pdl(void (*kernel)(const GemvParams), int grid, int block, int smem, cudaStream_t st, const GemvParams &p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+    return JQ_OK;
+}
 
 int fast_path_ok(const void *d_w, const void *d_xq, const float *d_x_f32, int64_t K, int64_t N) {
     if (K % 256 != 0) return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs K %% 256 == 0 (K = %lld)", (long long)K);
@@ -438,26 +510,26 @@ int fast_path_ok(const void *d_w, const void *d_xq, const float *d_x_f32, int64_
     return JQ_OK;
 }
 
-template <int M_T, int NSB, int NW>
+template <int M_T, int NSB, int NW, int MINB>
 int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
-    p.rows_per_stage = NW;
+    // MINB CTAs share an SM: each gets an equal slice of its shared memory (1 KB per CTA is reserved)
+    const int64_t budget = min((int64_t)caps.smem_optin, (int64_t)caps.smem_per_sm / MINB - 1024);
+    p.rows_per_stage = MINB > 1 ? 8 : NW;
     p.row_stride = p.row_bytes;
     for (;;) {
         p.stage_bytes = align_up((uint32_t)p.rows_per_stage * p.row_bytes, 128);
-        const int64_t avail = (int64_t)caps.smem_optin - GV_BAR_BYTES - p.x_bytes;
+        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes;
         p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
         if (p.stages >= 3 || p.rows_per_stage == 1) break;
         p.rows_per_stage = p.rows_per_stage > 2 ? p.rows_per_stage / 2 : 1;
     }
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
     const int smem = GV_BAR_BYTES + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
-    auto kernel = gemv_dp4a_kernel<M_T, NSB, NW>;
+    auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
-    const int grid = (int)min((int64_t)caps.sm_count, max((int64_t)1, want));
-    kernel<<<grid, (NW + 1) * 32, smem, st>>>(p);
-    JQ_CUDA_TRY(cudaGetLastError());
-    return JQ_OK;
+    const int grid = (int)min((int64_t)caps.sm_count * MINB, max((int64_t)1, want));
+    return launch_pdl(kernel, grid, (NW + 1) * 32, smem, st, p);
 }
 
 template <int KBW, int NW>
@@ -467,7 +539,7 @@ int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     p.row_stride = p.row_bytes + ((p.row_bytes / 16) % 2 == 0 ? 16 : 0);
     // the last warps may read a few blocks past the row end (their results are discarded)
     p.stage_bytes = align_up(16 * p.row_stride + KBW * Q4_BYTES + 64, 128);
-    const int red_bytes = 2 * NW * 128 * (int)sizeof(float);
+    const int red_bytes = GV_RED_SLOTS * NW * 128 * (int)sizeof(float);
     const int64_t avail = (int64_t)caps.smem_optin - GV_BAR_BYTES - red_bytes - p.x_bytes;
     p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "16 rows of %u bytes do not fit the shared-memory ring", p.row_bytes);
@@ -476,9 +548,7 @@ int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + 15) / 16;
     const int grid = (int)min((int64_t)caps.sm_count, max((int64_t)1, want));
-    kernel<<<grid, (NW + 1) * 32, smem, st>>>(p);
-    JQ_CUDA_TRY(cudaGetLastError());
-    return JQ_OK;
+    return launch_pdl(kernel, grid, (NW + 2) * 32, smem, st, p);
 }
 
 int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
@@ -496,7 +566,10 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
     p.s_mode = s_mode;
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
-    p.x_bytes = align_up((uint32_t)(M * p.n_super * Q8_BYTES), 128);
+    // activation rows 16*odd bytes apart in shared memory: 8 columns x 4 consecutive words hit 32 banks
+    p.x_pitch = (uint32_t)p.n_super * Q8_BYTES + (p.n_super % 2 == 0 ? 16u : 0u);
+    p.x_bytes = align_up((uint32_t)M * p.x_pitch, 128);
+    p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
     return JQ_OK;
 }
 
@@ -514,16 +587,16 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {
-            case 1: return run_dp4a<1, 1, 16>(st, p, caps);
-            case 2: return run_dp4a<1, 2, 8>(st, p, caps);
-            case 3: return run_dp4a<1, 3, 7>(st, p, caps);  // 7 + 1 warps: 255 registers per thread
-            case 4: return run_dp4a<1, 4, 7>(st, p, caps);
+            case 1: return run_dp4a<1, 1, 8, 2>(st, p, caps);  // two CTAs per SM: consecutive kernels overlap
+            case 2: return run_dp4a<1, 2, 8, 1>(st, p, caps);
+            case 3: return run_dp4a<1, 3, 7, 1>(st, p, caps);  // 7 + 1 warps: 255 registers per thread
+            case 4: return run_dp4a<1, 4, 7, 1>(st, p, caps);
             default: break;
         }
     } else {
         switch (nsb) {
-            case 1: return run_dp4a<2, 1, 8>(st, p, caps);
-            case 2: return run_dp4a<2, 2, 7>(st, p, caps);
+            case 1: return run_dp4a<2, 1, 8, 1>(st, p, caps);
+            case 2: return run_dp4a<2, 2, 7, 1>(st, p, caps);
             default: break;
         }
     }

@@ -16,6 +16,10 @@ constexpr int QUANT_UNROLL = 4;
 __global__ void __launch_bounds__(QUANT_THREADS)
 quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq, int64_t K, int64_t M,
                            int64_t n_super, int order, int s_mode) {
+    // let the multiply that follows on the stream start its weight stream right away; wait for
+    // whatever produced x before reading it
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = ((int64_t)blockIdx.x * QUANT_THREADS + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * QUANT_THREADS) >> 5;
@@ -120,9 +124,17 @@ int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t 
     const int64_t cap = (int64_t)caps.sm_count * 8 * 4;  // a few waves of resident CTAs
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
-    quantize_q8_1_kernel_sm100<<<(unsigned)ctas, QUANT_THREADS, 0, st>>>(
-        d_x, static_cast<uint8_t *>(d_xq), K, M, n_super, order, s_mode);
-    JQ_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(QUANT_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100, d_x, static_cast<uint8_t *>(d_xq), K, M, n_super,
+                                   order, s_mode));
     return JQ_OK;
 }
 

@@ -115,7 +115,8 @@ def _check_mul_mat(env, wq, x, K, N, M, kernel, order, s_mode, rows=None):
 
 
 SMALL = [(128, 32, 1), (256, 32, 2), (256, 33, 5), (512, 100, 8), (768, 7, 3), (1024, 257, 1), (256, 1, 1),
-         (2048, 130, 4), (4096, 300, 2), (8192, 70, 1), (11008, 50, 1), (16384, 40, 1), (1280, 64, 8)]
+         (2048, 130, 4), (4096, 300, 2), (8192, 70, 1), (11008, 50, 1), (16384, 40, 1), (1280, 64, 8),
+         (512, 200, 33), (1024, 129, 130), (256, 64, 300), (768, 256, 128), (4096, 384, 17)]
 
 
 @pytest.mark.parametrize("K,N,M", SMALL)
@@ -135,8 +136,10 @@ def test_mul_mat_small_shapes_all_kernels(env, K, N, M, order):
     assert c.KERNEL_GENERIC in ran and c.KERNEL_AUTO in ran
     if K % 256 == 0 and M <= 2 and K <= 16384 and not (M == 2 and K > 8192):
         assert c.KERNEL_GEMV_DP4A in ran
-    if K % 256 == 0 and K <= 6144:
+    if K % 256 == 0 and K <= 6144 and M <= 8:
         assert c.KERNEL_GEMV_MMA in ran
+    if K % 256 == 0:
+        assert c.KERNEL_GEMM_MMA in ran
 
 
 def test_mul_mat_reference_s_mode(env):
@@ -232,6 +235,46 @@ def test_linear_fused_equals_two_steps(env, K, N, M, s_mode):
     y2 = c.mul_mat_q4_0_q8_1(d_w, env.up(xq), K, N, M, c.ORDER_COL_KSUPER).cpu().numpy()
     assert np.array_equal(y, y2)  # same kernels, same arithmetic: identical bits
     assert env.O.err_max_rel(y, env.O.mul_mat_ref(wq, xq, K, N, M)) <= TOL_FORMULA
+
+
+@pytest.mark.parametrize("static_weights", [0, 1])
+@pytest.mark.parametrize("M", [1, 4])
+def test_dependent_chain_back_to_back(env, static_weights, M):
+    """Three linears queued without any synchronisation, each consuming the previous output.  With
+    JQ_OPT_STATIC_WEIGHTS the kernels overlap their weight stream with the predecessor's tail; the
+    activations must still be ordered, so the chain has to equal the step-by-step oracle chain."""
+    c = env.c
+    rng = np.random.default_rng(300 + M)
+    dims = [(4096, 4096), (4096, 2048), (2048, 512)]  # (K, N)
+    ws_host = [env.O.quantize_q4_0((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.03)).astype(np.float32))
+               for k, n in dims]
+    x0 = rng.standard_normal((M, dims[0][0]), dtype=np.float32)
+    d_ws = [env.up(w) for w in ws_host]
+    d_x = env.up(x0)
+    scratch = [env.t.zeros(c.q8_1_bytes(k, M), dtype=env.t.uint8, device=env.dev) for k, _ in dims]
+    c.set_option(c.OPT_STATIC_WEIGHTS, static_weights)
+    try:
+        assert c.get_option(c.OPT_STATIC_WEIGHTS) == static_weights
+        for _ in range(3):  # repeat so that kernels of different rounds overlap too
+            h = d_x
+            for (k, n), d_w, ws in zip(dims, d_ws, scratch):
+                h = c.linear_q4_0(d_w, h, n, c.S_D_SUM_Q, ws=ws)
+        got = h.cpu().numpy()
+    finally:
+        c.set_option(c.OPT_STATIC_WEIGHTS, 0)
+    ref = x0
+    for (k, n), w in zip(dims, ws_host):
+        xq = env.O.quantize_q8_1(ref, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+        ref = env.O.mul_mat_ref(w, xq, k, n, M)
+    # fp32 summation order differs per layer and requantization can flip a rounding: loose bound
+    assert env.O.err_max_rel(got, ref) <= 2e-2
+    # the last layer, fed the GPU's own input to it, must match tightly
+    h2 = d_x
+    for (k, n), d_w, ws in zip(dims[:2], d_ws[:2], scratch[:2]):
+        h2 = c.linear_q4_0(d_w, h2, n, c.S_D_SUM_Q, ws=ws)
+    x_last = h2.cpu().numpy()
+    xq = env.O.quantize_q8_1(x_last, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+    assert env.O.err_max_rel(got, env.O.mul_mat_ref(ws_host[2], xq, dims[2][0], dims[2][1], M)) <= TOL_FORMULA
 
 
 def test_multiply_is_linear_in_the_integer_activations(env):
