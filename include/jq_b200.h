@@ -118,6 +118,24 @@ int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y,
                           int64_t K, int64_t N, int64_t M, int s_mode);
 
+/* No counterpart in the reference.  jq_linear_q4_0_device() without the d_ws argument, for callers
+ * that must not allocate device memory and have no spare buffer to lend: an inference server that
+ * handed the whole device to its own arena at start-up (a later cudaMalloc fails or fragments),
+ * or a latency-critical decode loop that cannot afford cudaMalloc's device-wide synchronisation.
+ * The Q8_1 scratch lives in a fixed array inside the library image: JQ_NOALLOC_WS_BYTES bytes of
+ * device memory on every GPU that loads the library, held until the process exits.
+ *  - Capacity: jq_q8_1_bytes(K, M) <= JQ_NOALLOC_WS_BYTES (e.g. M = 512 at K = 4096, M = 128 at
+ *    K = 11008); larger requests return JQ_ERR_TOO_LARGE and launch nothing.
+ *  - The first call on each device looks up the array's device address (with that device current);
+ *    make that first call outside any stream capture.  No call allocates or frees anything.
+ *  - Every call on a device shares the one array and overwrites the part it uses, so nothing has to
+ *    be cleared between calls; two calls whose kernels can overlap on the GPU (different streams
+ *    without an ordering between them) race on it - order them, or use jq_linear_q4_0_device().
+ *  - The quantized activations are not returned to the caller. */
+#define JQ_NOALLOC_WS_BYTES (4u << 20)
+int jq_linear_q4_0_device_noalloc(void *stream, const void *d_w, const float *d_x, float *d_y, int64_t K,
+                                  int64_t N, int64_t M, int s_mode);
+
 /* Parity aid: the exact int32 dot product of every (row n, 32-wide block kb, column m),
  * d_sums[(m*N + n)*(K/32) + kb], i.e. `sumi` of q4_0_q8_1_vec_dot_impl (mm_q4_0_q8_1.cu:71-93)
  * before any scale is applied.  The reference never exposes it. */

@@ -58,6 +58,7 @@ _SIGS = {
     "jq_mul_mat_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_mul_mat_q4_0_q8_1_device_ex": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, _ci]),
     "jq_linear_q4_0_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_linear_q4_0_device_noalloc": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_block_sums_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_quantize_q4_0_device": (_ci, [_vp, _vp, _vp, _i64, _i64]),
     "jq_device_fault": (_ci, [_ci, ctypes.POINTER(_ci)]),
@@ -160,6 +161,22 @@ def linear_q4_0(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = S_D_SUM_
     with torch.cuda.device(x.device):
         check(_lib.jq_linear_q4_0_device(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
                                          _dev(ws, torch.uint8, "ws"), _dev(out, torch.float32, "out"), K, N, M, s_mode))
+    return out
+
+
+NOALLOC_WS_BYTES = 4 << 20
+
+
+def linear_q4_0_noalloc(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = S_D_SUM_Q,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``linear_q4_0`` through the entry point that owns its scratch (no workspace argument, no
+    allocation inside the library; ``out`` is allocated here by torch only if not given)."""
+    M, K = x.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.jq_linear_q4_0_device_noalloc(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
+                                                 _dev(out, torch.float32, "out"), K, N, M, s_mode))
     return out
 
 

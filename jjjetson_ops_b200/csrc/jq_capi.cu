@@ -237,6 +237,54 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
     return dispatch_mul_mat(st, d_w, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO);
 }
 
+// ---- the entry point that allocates nothing ---------------------------------------------------------
+// Scratch for the quantized activations, part of the library image (see include/jq_b200.h).  In host
+// code this name is only a handle for the runtime: the kernels must be given the device address that
+// cudaGetSymbolAddress() returns for the device that is current at the time.
+static __device__ __align__(256) uint8_t g_noalloc_ws[JQ_NOALLOC_WS_BYTES];
+
+namespace {
+struct NoAllocSlot {
+    bool ready = false;
+    void *ws = nullptr;
+};
+NoAllocSlot g_noalloc[jq::MAX_DEVICES];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: resolve the array's address on that device.
+int noalloc_workspace(void **out) {
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= jq::MAX_DEVICES) return set_error(JQ_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocSlot &slot = g_noalloc[dev];
+    if (!slot.ready) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_ws);
+        if (e != cudaSuccess) return cuda_error(e, "cudaGetSymbolAddress(g_noalloc_ws)");
+        if (ptr == nullptr) return set_error(JQ_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        slot.ws = ptr;
+        slot.ready = true;
+    }
+    *out = slot.ws;
+    return JQ_OK;
+}
+}  // namespace
+
+int jq_linear_q4_0_device_noalloc(void *stream, const void *d_w, const float *d_x, float *d_y, int64_t K, int64_t N,
+                                  int64_t M, int s_mode) {
+    if (int rc = check_mul_mat_shape(K, N, M)) return rc;
+    const size_t need = jq_q8_1_bytes(K, M);
+    if (need > (size_t)JQ_NOALLOC_WS_BYTES)
+        return set_error(JQ_ERR_TOO_LARGE,
+                         "jq_linear_q4_0_device_noalloc: M = %lld, K = %lld need %zu bytes of Q8_1 scratch, the built-in "
+                         "array holds %u; use jq_linear_q4_0_device with a caller-owned workspace",
+                         (long long)M, (long long)K, need, (unsigned)JQ_NOALLOC_WS_BYTES);
+    void *ws = nullptr;
+    if (int rc = noalloc_workspace(&ws)) return rc;
+    return jq_linear_q4_0_device(stream, d_w, d_x, ws, d_y, K, N, M, s_mode);
+}
+
 int jq_block_sums_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq, int32_t *d_sums, int64_t K,
                                    int64_t N, int64_t M, int order) {
     if (int rc = check_mul_mat_shape(K, N, M)) return rc;
