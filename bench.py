@@ -158,6 +158,7 @@ def run_reference(args) -> None:
     from oracle import jq_oracle as O
 
     O.build()
+    O.use_all_host_threads()  # torchrun exports OMP_NUM_THREADS=1
     w, x, lin = synth.make_linear_case(2, 0, 1)
     wq = O.quantize_q4_0(w)
     K, N, M = lin.K, lin.N, 1
@@ -406,6 +407,7 @@ def measure_cpu_baseline(K, N, M, alg):
     from oracle import jq_oracle as O
 
     O.build()
+    O.use_all_host_threads()
     w, x, _ = synth.make_linear_case(2, 0, M)
     wq = O.quantize_q4_0(w)
     y = np.empty((M, N), dtype=np.float32)

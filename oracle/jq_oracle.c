@@ -391,6 +391,15 @@ void jqo_linear_cpu_baseline(const uint8_t *wq, const float *x, uint8_t *xq_ws, 
     free(xf);
 }
 
+/* Thread count for the OpenMP loops above (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void jqo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int jqo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

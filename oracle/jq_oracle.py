@@ -57,6 +57,8 @@ def lib() -> ctypes.CDLL:
         L.jqo_mul_mat_deq_f64.argtypes = [p, p, i64, i64, i64, ci, p]
         L.jqo_linear_cpu_baseline.argtypes = [p, p, p, i64, i64, i64, ci, p]
         L.jqo_num_threads.restype = ci
+        L.jqo_set_num_threads.argtypes = [ci]
+        L.jqo_set_num_threads.restype = None
         L.jqo_f32_to_f16.argtypes = [ctypes.c_float]
         L.jqo_f32_to_f16.restype = ctypes.c_uint16
         L.jqo_f16_to_f32.argtypes = [ctypes.c_uint16]
@@ -78,6 +80,16 @@ def _ptr(a: np.ndarray) -> ctypes.c_void_p:
 
 def num_threads() -> int:
     return int(lib().jqo_num_threads())
+
+
+def use_all_host_threads() -> int:
+    """Let the OpenMP loops use every core this process may run on; returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().jqo_set_num_threads(n)
+    return num_threads()
 
 
 # ----------------------------------------------------------------------------- C wrappers

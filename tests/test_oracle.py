@@ -28,6 +28,25 @@ def test_q8_1_matches_reference_numpy_golden(oracle, tag):
         assert np.allclose(s, g[f"{tag}_sum"], atol=1e-2)
 
 
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
+def test_oracle_matches_reference_kernels_run_on_b200(oracle, tag):
+    """Outputs of the reference's own CUDA operators, rebuilt unmodified for sm_100a and run on a
+    B200 (tests/golden/make_ref_gpu_golden.py): the quantized blocks and the fp32 products of
+    mat_mul_q4_0_q8_1_device must come out of the oracle bit for bit."""
+    from tests.golden.make_ref_gpu_golden import case_inputs, reorder_ksuper_col_to_col_ksuper
+
+    g = np.load(os.path.join(GOLDEN, "ref_gpu_sm100.npz"))
+    K, N, M, w, x = case_inputs(tag)
+    xq = oracle.quantize_q8_1(x, oracle.ORDER_KSUPER_COL, oracle.S_SUM_X)
+    assert np.array_equal(xq, g[tag + "_xq"])
+    assert np.array_equal(oracle.np_quantize_q8_1(x, oracle.ORDER_KSUPER_COL, oracle.S_SUM_X), g[tag + "_xq"])
+    wq = oracle.quantize_q4_0(w)
+    xq_mm = reorder_ksuper_col_to_col_ksuper(xq, K, M)
+    assert np.array_equal(xq_mm, oracle.quantize_q8_1(x, oracle.ORDER_COL_KSUPER, oracle.S_SUM_X))
+    y = oracle.mul_mat_ref(wq, xq_mm, K, N, M, oracle.ORDER_COL_KSUPER)
+    assert np.array_equal(y, g[tag + "_y"])
+
+
 def test_q4_0_matches_gguf_golden(oracle):
     from tests.golden.make_q4_0_gguf_golden import make_input
 
