@@ -442,8 +442,13 @@ def measure_extras(torch, capi, synth, dev, peaks):
         ws = torch.zeros(max(capi.q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
         y = torch.zeros((M, N), dtype=torch.float32, device=dev)
 
+        xq = capi.quantize_q8_1(x, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q)
+
         def step(i):
-            capi.linear_q4_0(ws_[i % R], x, N, capi.S_D_SUM_Q, ws=ws, out=y)
+            if fused:
+                capi.linear_q4_0(ws_[i % R], x, N, capi.S_D_SUM_Q, ws=ws, out=y)
+            else:  # the multiply alone, activations already in Q8_1 form
+                capi.mul_mat_q4_0_q8_1(ws_[i % R], xq, K, N, M, capi.ORDER_COL_KSUPER, out=y)
 
         sec, _ = time_graph_steps(torch, step, steps, 3, lambda: None)
         del ws_, base
@@ -454,6 +459,10 @@ def measure_extras(torch, capi, synth, dev, peaks):
         t = bench_linear(4096, 11008, M)
         b = synth.algorithmic_bytes(4096, 11008, M)
         out["cfg2_M%d" % M] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    for M in (1, 8):
+        t = bench_linear(4096, 11008, M, fused=False)
+        b = synth.algorithmic_bytes(4096, 11008, M, fused_quantize=False)
+        out["cfg2_M%d_mul_mat_only" % M] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
     t = bench_linear(4096, 4096, 1)
     b = synth.algorithmic_bytes(4096, 4096, 1)
     out["cfg1_M1"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}

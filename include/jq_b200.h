@@ -80,6 +80,13 @@ typedef enum jq_option {
 int jq_set_option(int option, int value);
 int jq_get_option(int option, int *value_out);
 
+/* Tracing aid for the decode kernels: after jq_trace_enable(d_buf, n), each of the next n launches
+ * of a streaming GEMV writes 8 device-clock timestamps (ns, %globaltimer) per CTA into its own
+ * 512 x 8 x uint64 slice of d_buf (CTA start, weight stream begins, last copy issued, predecessor
+ * finished, activations staged, first stage landed, last stage landed, done).  d_buf must hold
+ * n * 32768 bytes and be zeroed by the caller.  jq_trace_enable(NULL, 0) switches it off. */
+int jq_trace_enable(void *d_buf, int64_t n_launches);
+
 const char *jq_status_string(int status);
 /* Message of the last failure on the calling thread ("" if none). */
 const char *jq_last_error(void);

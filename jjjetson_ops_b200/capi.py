@@ -51,6 +51,7 @@ _SIGS = {
     "jq_last_error": (ctypes.c_char_p, []),
     "jq_version": (_ci, []),
     "jq_set_option": (_ci, [_ci, _ci]),
+    "jq_trace_enable": (_ci, [_vp, _i64]),
     "jq_get_option": (_ci, [_ci, ctypes.POINTER(_ci)]),
     "jq_q8_1_bytes": (_sz, [_i64, _i64]),
     "jq_q4_0_bytes": (_sz, [_i64, _i64]),

@@ -31,6 +31,19 @@ std::atomic<int> g_options[JQ_OPT_COUNT_];
 
 }  // namespace
 
+namespace {
+std::atomic<unsigned long long *> g_trace_buf{nullptr};
+std::atomic<long long> g_trace_slots{0}, g_trace_next{0};
+constexpr int TRACE_CTAS = 512;  // CTAs recorded per launch, 8 stamps of 8 bytes each
+}
+void *next_trace_slot() {
+    unsigned long long *buf = g_trace_buf.load();
+    if (buf == nullptr) return nullptr;
+    const long long i = g_trace_next.fetch_add(1);
+    if (i >= g_trace_slots.load()) return nullptr;
+    return buf + (size_t)i * TRACE_CTAS * 8;
+}
+
 int option_value(int option) {
     return option >= 0 && option < JQ_OPT_COUNT_ ? g_options[option].load(std::memory_order_relaxed) : 0;
 }
@@ -161,6 +174,13 @@ int jq_version(void) { return 100; }
 int jq_set_option(int option, int value) {
     if (option < 0 || option >= JQ_OPT_COUNT_) return set_error(JQ_ERR_INVALID_ARG, "unknown option %d", option);
     g_options[option].store(value, std::memory_order_relaxed);
+    return JQ_OK;
+}
+
+int jq_trace_enable(void *d_buf, int64_t n_launches) {
+    g_trace_next.store(0);
+    g_trace_slots.store(d_buf ? n_launches : 0);
+    g_trace_buf.store(static_cast<unsigned long long *>(d_buf));
     return JQ_OK;
 }
 

@@ -46,6 +46,9 @@ struct DeviceCaps {
 int device_caps(DeviceCaps *out);  // for the current device
 
 int option_value(int option);       // process-wide settings of jq_set_option()
+// Tracing aid (jq_trace_enable): device address where the next traced launch may write its
+// per-CTA timestamps, or nullptr when tracing is off or the buffer is full.
+void *next_trace_slot();
 
 // Device address (on the current device) of the word a kernel sets when one of its bounded waits
 // gives up; nullptr if it cannot be obtained.  Kernels receive it as a parameter.

@@ -48,7 +48,18 @@ struct GemvParams {
     int stages;
     int rows_per_stage;
     int prefetch_early;    // the weight stream may start before the preceding kernel in the stream has finished
+    int early_stages;      // stages the producer may request before the activations are staged
+    unsigned long long *trace;  // 8 timestamps per CTA of this launch (tracing aid), or nullptr
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_stamp(const GemvParams &p, int slot) {
+    if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
+}
 
 // Programmatic dependent launch: let the next kernel in the stream be scheduled early, and wait
 // for the previous one (and its memory operations) before touching anything it may have written.
@@ -61,9 +72,12 @@ __device__ __forceinline__ void cta_row_range(int64_t N, int64_t *begin, int64_t
 }
 
 // Producer: one thread walks the CTA's row slab stage by stage.
+// When the stream starts ahead of the previous kernel's end (static weights), only `early_stages`
+// stages are requested up front: the activation loads that follow the wait would otherwise queue
+// behind the whole ring's worth of weight traffic on this SM's path to L2.
 template <bool PER_ROW>
 __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty,
-                                              uint8_t *ring) {
+                                              uint64_t *x_ready, uint8_t *ring) {
     int64_t r_begin, r_end;
     cta_row_range(p.N, &r_begin, &r_end);
     const int R = p.rows_per_stage;
@@ -71,6 +85,7 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % p.stages;
         const uint32_t round = (uint32_t)(c / p.stages);
+        if (c == p.early_stages && !mbar_wait_bounded(x_ready, 0u, p.fault)) return;
         if (round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1u, p.fault)) return;
         const int64_t r0 = r_begin + (int64_t)c * R;
         const int rows = (int)min((int64_t)R, r_end - r0);
@@ -91,10 +106,11 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
 // [m][k/128] as 144-byte blocks.  Either quantize fp32 input (bit-identical to the stand-alone
 // quantizer) or copy already quantized blocks, honouring their order.
 template <int NW>
-__device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, int warp, int lane) {
+__device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, uint64_t *x_ready, int warp,
+                                                  int lane) {
     const int total = p.M * p.n_super;
     if (p.x_f32 != nullptr) {
-        constexpr int U = 8;  // loads in flight per warp: the prologue is latency-, not bandwidth-bound
+        constexpr int U = 4;  // groups per warp in flight: the prologue is latency-, not bandwidth-bound
         for (int base = warp; base < total; base += NW * U) {
             float4 xi[U];
 #pragma unroll
@@ -106,20 +122,34 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
                     xi[u] = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
                 }
             }
+            if (base == warp) {
+                // this warp's first (usually only) batch of loads has landed: let the weight stream go on
+                float touch = 0.0f;
+#pragma unroll
+                for (int u = 0; u < U; ++u) touch += xi[u].x;
+                touch = __shfl_xor_sync(0xFFFFFFFFu, touch, 1, 32);
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // after %1" ::"r"(smem_u32(x_ready)), "f"(touch)
+                                 : "memory");
+                }
+            }
+            // all U groups are quantized together (no early exit), so that their shuffle chains overlap
+            uint32_t qv[U], dsv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) qv[u] = quantize_group_q8_1(xi[u], p.s_mode, &dsv[u]);
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int idx = base + u * NW;  // uniform across the warp
-                if (idx >= total) break;
-                uint32_t ds;
-                const uint32_t q = quantize_group_q8_1(xi[u], p.s_mode, &ds);
-                const int m = idx / p.n_super, ks = idx - m * p.n_super;
-                uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-                reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
-                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
-                if (p.xq_out != nullptr && blockIdx.x == 0) {
-                    uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-                    reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = q;
-                    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = ds;
+                if (idx < total) {
+                    const int m = idx / p.n_super, ks = idx - m * p.n_super;
+                    uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+                    reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = qv[u];
+                    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = dsv[u];
+                    if (p.xq_out != nullptr && blockIdx.x == 0) {
+                        uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+                        reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = qv[u];
+                        if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = dsv[u];
+                    }
                 }
             }
         }
@@ -133,6 +163,11 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
                 __ldg(reinterpret_cast<const uint4 *>(g) + part);
         }
     }
+    if (p.x_f32 == nullptr || warp >= total) {
+        // copies issued above were consumed by their stores; warps without a group arrive at once
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x_ready);
+    }
     named_bar_sync(1, NW * 32);
 }
 
@@ -145,6 +180,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + GV_MAX_STAGES;
+    uint64_t *x_ready = full + 24;
     uint8_t *xs = smem + GV_BAR_BYTES;
     uint8_t *ring = xs + p.x_bytes;
 
@@ -154,21 +190,27 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NW);
         }
+        mbar_init(x_ready, NW);
         fence_mbar_init();
     }
     __syncthreads();
 
+    if (threadIdx.x == 0) trace_stamp(p, 0);  // CTA started
     griddep_launch_dependents();
     if (warp == NW) {
         if (lane == 0) {
             if (!p.prefetch_early) griddep_wait();
-            gemv_producer<false>(p, full, empty, ring);
+            trace_stamp(p, 1);  // weight stream begins
+            gemv_producer<false>(p, full, empty, x_ready, ring);
+            trace_stamp(p, 2);  // last copy issued
         }
         return;
     }
     griddep_wait();  // activations may come from, and outputs may be read by, the previous kernel
+    if (threadIdx.x == 0) trace_stamp(p, 3);  // predecessor finished
 
-    stage_activations<NW>(p, xs, warp, lane);
+    stage_activations<NW>(p, xs, x_ready, warp, lane);
+    if (threadIdx.x == 0) trace_stamp(p, 4);  // activations staged
 
     // This lane's slices of X: slice i covers k in [128*(lane + 32 i), +128).
     int xq[NSB][M_T][32];
@@ -214,6 +256,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         const int s = c % p.stages;
         const uint32_t round = (uint32_t)(c / p.stages);
         if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
+        if (threadIdx.x == 0 && c == 0) trace_stamp(p, 5);  // first stage landed
+        if (threadIdx.x == 0 && c == n_chunks - 1) trace_stamp(p, 6);  // last stage landed
         const uint32_t stage = ring_addr + (uint32_t)s * p.stage_bytes;
         const int64_t r0 = r_begin + (int64_t)c * R;
         const int rows = (int)min((int64_t)R, r_end - r0);
@@ -280,6 +324,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
+    if (threadIdx.x == 0) trace_stamp(p, 7);  // warp 0 done
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -300,6 +345,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
     uint64_t *empty = full + GV_MAX_STAGES;
     uint64_t *red_full = empty + GV_MAX_STAGES;
     uint64_t *red_empty = red_full + GV_RED_SLOTS;
+    uint64_t *x_ready = full + 24;
     float *red = reinterpret_cast<float *>(smem + GV_BAR_BYTES);  // [GV_RED_SLOTS][NW][128]
     uint8_t *xs = smem + GV_BAR_BYTES + GV_RED_SLOTS * NW * 128 * sizeof(float);
     uint8_t *ring = xs + p.x_bytes;
@@ -314,6 +360,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
             mbar_init(&red_full[s], NW);
             mbar_init(&red_empty[s], 1);
         }
+        mbar_init(x_ready, NW);
         fence_mbar_init();
     }
     __syncthreads();
@@ -326,7 +373,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
     if (warp == NW) {  // weight stream
         if (lane == 0) {
             if (!p.prefetch_early) griddep_wait();
-            gemv_producer<true>(p, full, empty, ring);
+            gemv_producer<true>(p, full, empty, x_ready, ring);
         }
         return;
     }
@@ -356,7 +403,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
         return;
     }
 
-    stage_activations<NW>(p, xs, warp, lane);
+    stage_activations<NW>(p, xs, x_ready, warp, lane);
 
     const int g = lane >> 2, t = lane & 3;
     const int nb = p.K / QK;
@@ -570,6 +617,12 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
     p.x_pitch = (uint32_t)p.n_super * Q8_BYTES + (p.n_super % 2 == 0 ? 16u : 0u);
     p.x_bytes = align_up((uint32_t)M * p.x_pitch, 128);
     p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
+    p.trace = static_cast<unsigned long long *>(next_trace_slot());
+    // Ahead of the previous kernel's end only two stages are requested (more would delay the
+    // activation loads that follow the wait); a kernel that quantizes in its prologue starts its
+    // stream at the wait instead, where it overlaps the quantization.
+    if (d_x_f32 != nullptr) p.prefetch_early = 0;
+    p.early_stages = p.prefetch_early ? 2 : (1 << 30);
     return JQ_OK;
 }
 
@@ -587,7 +640,11 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {
-            case 1: return run_dp4a<1, 1, 8, 2>(st, p, caps);  // two CTAs per SM: consecutive kernels overlap
+            case 1:
+                // Quantizing in the prologue is repeated by every CTA: one CTA of 16 warps per SM halves
+                // that cost.  With ready-made Q8_1 input two CTAs of 8 warps per SM overlap better.
+                if (p.x_f32 != nullptr) return run_dp4a<1, 1, 16, 1>(st, p, caps);
+                return run_dp4a<1, 1, 8, 2>(st, p, caps);
             case 2: return run_dp4a<1, 2, 8, 1>(st, p, caps);
             case 3: return run_dp4a<1, 3, 7, 1>(st, p, caps);  // 7 + 1 warps: 255 registers per thread
             case 4: return run_dp4a<1, 4, 7, 1>(st, p, caps);
