@@ -193,7 +193,7 @@ def workload_config(K, N, M, world):
         "workload": "cfg2 decode GEMV: quantize_q8_1 + Q4_0xQ8_1 mul_mat, M=%d, K=%d, N=%d per GPU, seed 1, "
                     "1%% outlier channels x20" % (M, K, N),
         "M": M, "K": K, "N_per_gpu": N, "N_total": N * world,
-        "parallelism": "single GPU" if world == 1 else "N-sharded x%d, all-gather of outputs (NCCL)" % world,
+        "parallelism": "single GPU" if world == 1 else "N-sharded x%d, outputs all-gathered along N" % world,
         "l2": "weights rotate through distinct copies totalling > 3x L2 between steps (cold L2)",
         "overlap": "steps are launched with programmatic dependent launch; JQ_OPT_STATIC_WEIGHTS=1 lets a step "
                    "prefetch its weights while the previous step drains (activations/outputs stay ordered)",
@@ -203,7 +203,7 @@ def workload_config(K, N, M, world):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
-def time_graph_steps(torch, step_fn, steps, warmup, barrier):
+def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None):
     """Times exactly `steps` calls of step_fn(i) with CUDA events; the calls are replayed from
     CUDA graphs of up to GRAPH_BLOCK steps each."""
     stream = torch.cuda.Stream()
@@ -248,6 +248,8 @@ def time_graph_steps(torch, step_fn, steps, warmup, barrier):
         else:
             for i in range(steps):
                 step_fn(i)
+        if finalize is not None:
+            finalize()  # e.g. wait for the last step's bands from every rank
         end.record(stream)
     stream.synchronize()
     torch.cuda.synchronize()
@@ -297,15 +299,28 @@ def run_ours(args) -> None:
     d_ws = torch.zeros(max(capi.q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
     d_y = torch.zeros((M, N), dtype=torch.float32, device=dev)
     gather = torch.zeros((world * M, N), dtype=torch.float32, device=dev) if world > 1 else None
+    bands = None
+    collective = "none"
+    if world > 1:
+        collective = args.collective if M <= 2 else "nccl"
+    if collective == "fused":
+        from jjjetson_ops_b200.sharded import PeerBands
+
+        bands = PeerBands(M, N * world, dev)
 
     def step(i):
+        if bands is not None:
+            # multiply + all-gather in one kernel: the band goes straight into every rank's buffer
+            bands.linear(weights[i % R], d_x, d_ws, rank * N, N)
+            return
         capi.linear_q4_0(weights[i % R], d_x, N, capi.S_D_SUM_Q, ws=d_ws, out=d_y)
         if gather is not None:
             dist.all_gather_into_tensor(gather, d_y)
 
     sampler = ClockSampler(local)
     sampler.start()
-    seconds, used_graph = time_graph_steps(torch, step, args.steps, args.warmup, barrier)
+    seconds, used_graph = time_graph_steps(torch, step, args.steps, args.warmup, barrier,
+                                           finalize=bands.wait if bands is not None else None)
     sampler.stop()
     if dist is not None:
         t = torch.tensor([seconds], dtype=torch.float64, device=dev)
@@ -318,6 +333,8 @@ def run_ours(args) -> None:
     if rank == 0 or world > 1:
         e2e = measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world)
 
+    if bands is not None:
+        bands.close()
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -328,7 +345,7 @@ def run_ours(args) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8", "data": "synthetic", "config": workload_config(K, N, M, world),
+        "dtype": "int8", "data": "synthetic", "config": dict(workload_config(K, N, M, world), collective=collective),
         "roofline": {
             "bound": "hbm", "achieved": per_gpu_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": per_gpu_gbs / peaks["hbm_gbs"], "traffic": load_traffic_note(),
@@ -488,6 +505,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--m", type=int, default=1, help="activation rows of the headline workload (1..8)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary shapes and the CPU baseline")
+    ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: all-gather fused into the multiply kernel (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-overlap", action="store_true",
                     help="do not let a step's weight stream start before the previous step has finished")
     args = ap.parse_args()

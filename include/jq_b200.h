@@ -125,6 +125,44 @@ int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y,
                           int64_t K, int64_t N, int64_t M, int s_mode);
 
+/* ---- N-sharded decode (no counterpart in the reference, which is single-GPU) -------------------
+ * One process per GPU owns a contiguous band of weight rows.  jq_linear_q4_0_allgather_device
+ * runs this rank's quantize + multiply (M <= 2) and writes its band of the output directly into
+ * every rank's [M][N_total] buffer through peer-mapped pointers (plain stores over NVLink), then
+ * raises its arrival flag on every rank.  The kernel does not wait for the other ranks at its end:
+ * whoever consumes the gathered output waits for the flags - the next sharded layer by passing
+ * wait_epoch (its prologue then waits, while its weight stream is already running), anything
+ * else by queueing jq_allgather_wait_device first.  All ranks must make the same sequence of calls.
+ *   y_peers[q]     : rank q's pair of output buffers as mapped on this device (q == rank: local);
+ *                    the second buffer starts y_stride_bytes after the first
+ *   flag_peers[q]  : rank q's uint32[world] flag array, likewise; zero before the first call
+ *   d_epoch        : a local uint32, zero before the first call: how many all-gathers this rank has
+ *                    finished.  Call number e = *d_epoch + 1 stores into buffer (e & 1), raises the
+ *                    flags to e and sets *d_epoch = e (on the device, so CUDA graphs can be replayed)
+ *   wait_previous  : non-zero: the activations are the output of all-gather number *d_epoch; the
+ *                    kernel waits for all its bands before reading them
+ *   d_counter      : a local int, zero before the first call
+ * The two buffers alternate, and with wait_previous (or a jq_allgather_wait_device between calls) a
+ * fast rank cannot overwrite a band that a slow rank still has to read.
+ * Every wait inside the kernels is bounded; if one runs out jq_device_fault() reports 2.  Other
+ * shapes return JQ_ERR_UNSUPPORTED: multiply locally and all-gather with NCCL.
+ * jq_peer_alloc / jq_peer_open: device memory that other processes on the node can map
+ * (cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle); the 64-byte handle travels through any
+ * host channel (e.g. torch.distributed all_gather_object). */
+#define JQ_PEER_HANDLE_BYTES 64
+int jq_peer_alloc(size_t bytes, void **d_ptr, unsigned char *handle_out);
+int jq_peer_open(const unsigned char *handle, void **d_ptr);
+int jq_peer_close(void *d_ptr);
+int jq_peer_free(void *d_ptr);
+int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *d_x, void *d_ws, int64_t K,
+                                    int64_t N_local, int64_t M, int s_mode, void *const *y_peers,
+                                    void *const *flag_peers, int world, int rank, int64_t n_offset,
+                                    int64_t N_total, size_t y_stride_bytes, int wait_previous,
+                                    unsigned *d_epoch, int *d_counter);
+/* Blocks the stream (bounded) until all `world` flags at d_flags have reached *d_epoch, i.e. until
+ * the bands of this rank's latest all-gather have arrived from every rank. */
+int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const unsigned *d_epoch);
+
 /* No counterpart in the reference.  jq_linear_q4_0_device() without the d_ws argument, for callers
  * that must not allocate device memory and have no spare buffer to lend: an inference server that
  * handed the whole device to its own arena at start-up (a later cudaMalloc fails or fragments),

@@ -59,6 +59,13 @@ _SIGS = {
     "jq_mul_mat_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_mul_mat_q4_0_q8_1_device_ex": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, _ci]),
     "jq_linear_q4_0_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_peer_alloc": (_ci, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    "jq_peer_open": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "jq_peer_close": (_ci, [_vp]),
+    "jq_peer_free": (_ci, [_vp]),
+    "jq_linear_q4_0_allgather_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, ctypes.POINTER(_vp),
+                                              ctypes.POINTER(_vp), _ci, _ci, _i64, _i64, _sz, _ci, _vp, _vp]),
+    "jq_allgather_wait_device": (_ci, [_vp, _vp, _ci, _vp]),
     "jq_linear_q4_0_device_noalloc": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_block_sums_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_quantize_q4_0_device": (_ci, [_vp, _vp, _vp, _i64, _i64]),
@@ -179,6 +186,60 @@ def linear_q4_0_noalloc(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = 
         check(_lib.jq_linear_q4_0_device_noalloc(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
                                                  _dev(out, torch.float32, "out"), K, N, M, s_mode))
     return out
+
+
+def peer_alloc(nbytes: int):
+    """Zeroed device memory that other processes of the node can map -> (device pointer, 64-byte handle)."""
+    ptr = _vp()
+    handle = ctypes.create_string_buffer(64)
+    check(_lib.jq_peer_alloc(nbytes, ctypes.byref(ptr), handle))
+    return int(ptr.value), handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    ptr = _vp()
+    check(_lib.jq_peer_open(handle, ctypes.byref(ptr)))
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    check(_lib.jq_peer_close(ptr))
+
+
+def peer_free(ptr: int) -> None:
+    check(_lib.jq_peer_free(ptr))
+
+
+class _RawDeviceMemory:
+    """Lets torch view memory this library allocated (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    typestr = {torch.float32: "<f4", torch.uint8: "|u1", torch.int32: "<i4"}[dtype]
+    return torch.as_tensor(_RawDeviceMemory(ptr, shape, typestr), device=device)
+
+
+def linear_q4_0_allgather(w: torch.Tensor, x: torch.Tensor, ws: torch.Tensor, N_local: int, s_mode: int,
+                          y_peers, flag_peers, world: int, rank: int, n_offset: int, N_total: int,
+                          y_stride_bytes: int, wait_previous: bool, epoch: torch.Tensor, counter: torch.Tensor) -> None:
+    """This rank's quantize + multiply with its output band stored into every rank's buffer."""
+    M, K = x.shape
+    yp = (_vp * world)(*y_peers)
+    fp = (_vp * world)(*flag_peers)
+    with torch.cuda.device(x.device):
+        check(_lib.jq_linear_q4_0_allgather_device(
+            _stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"), _dev(ws, torch.uint8, "ws"), K, N_local, M,
+            s_mode, yp, fp, world, rank, n_offset, N_total, y_stride_bytes, 1 if wait_previous else 0,
+            _dev(epoch, torch.int32, "epoch"), _dev(counter, torch.int32, "counter")))
+
+
+def allgather_wait(device: torch.device, flags_ptr: int, world: int, epoch: torch.Tensor) -> None:
+    with torch.cuda.device(device):
+        check(_lib.jq_allgather_wait_device(torch.cuda.current_stream(device).cuda_stream, flags_ptr, world,
+                                            _dev(epoch, torch.int32, "epoch")))
 
 
 def block_sums(w: torch.Tensor, xq: torch.Tensor, K: int, N: int, M: int,

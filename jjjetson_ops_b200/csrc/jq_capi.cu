@@ -257,6 +257,81 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
     return dispatch_mul_mat(st, d_w, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO);
 }
 
+// ---- N-sharded decode: multiply + all-gather in one kernel -----------------------------------------
+
+int jq_peer_alloc(size_t bytes, void **d_ptr, unsigned char *handle_out) {
+    if (!d_ptr || !handle_out || bytes == 0) return set_error(JQ_ERR_INVALID_ARG, "jq_peer_alloc: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == JQ_PEER_HANDLE_BYTES, "handle size");
+    void *p = nullptr;
+    JQ_CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_error(e, "jq_peer_alloc");
+    }
+    std::memcpy(handle_out, &h, sizeof(h));
+    *d_ptr = p;
+    return JQ_OK;
+}
+
+int jq_peer_open(const unsigned char *handle, void **d_ptr) {
+    if (!d_ptr || !handle) return set_error(JQ_ERR_INVALID_ARG, "jq_peer_open: bad argument");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    JQ_CUDA_TRY(cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return JQ_OK;
+}
+
+int jq_peer_close(void *d_ptr) {
+    if (d_ptr) JQ_CUDA_TRY(cudaIpcCloseMemHandle(d_ptr));
+    return JQ_OK;
+}
+
+int jq_peer_free(void *d_ptr) {
+    if (d_ptr) JQ_CUDA_TRY(cudaFree(d_ptr));
+    return JQ_OK;
+}
+
+int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *d_x, void *d_ws, int64_t K,
+                                    int64_t N_local, int64_t M, int s_mode, void *const *y_peers,
+                                    void *const *flag_peers, int world, int rank, int64_t n_offset, int64_t N_total,
+                                    size_t y_stride_bytes, int wait_previous, unsigned *d_epoch, int *d_counter) {
+    if (int rc = check_mul_mat_shape(K, N_local, M)) return rc;
+    if (int rc = check_s_mode(s_mode)) return rc;
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return set_error(JQ_ERR_INVALID_ARG, "world must be 1..%d and rank inside it (world=%d rank=%d)", MAX_PEERS, world, rank);
+    if (!y_peers || !flag_peers || !d_counter || !d_epoch || !d_w || !d_x) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (n_offset < 0 || n_offset + N_local > N_total) return set_error(JQ_ERR_INVALID_ARG, "band [%lld, %lld) outside N_total = %lld",
+                                                                       (long long)n_offset, (long long)(n_offset + N_local), (long long)N_total);
+    if (M < 1 || M > 2 || N_local < 1 || K < 1)
+        return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather covers M <= 2 (M = %lld); gather with NCCL instead", (long long)M);
+    if (((uintptr_t)d_x & 15u) != 0 || (d_ws && ((uintptr_t)d_ws & 15u) != 0))
+        return set_error(JQ_ERR_ALIGN, "activations and workspace must be 16-byte aligned");
+    GatherArgs ga;
+    for (int q = 0; q < MAX_PEERS; ++q) {
+        ga.y_peer[q] = q < world ? static_cast<float *>(y_peers[q]) : nullptr;
+        ga.flag_peer[q] = q < world ? static_cast<uint32_t *>(flag_peers[q]) : nullptr;
+        if (q < world && (!ga.y_peer[q] || !ga.flag_peer[q])) return set_error(JQ_ERR_INVALID_ARG, "null peer pointer %d", q);
+    }
+    ga.world = world;
+    ga.rank = rank;
+    ga.n_offset = n_offset;
+    ga.N_total = N_total;
+    ga.epoch_ptr = d_epoch;
+    ga.y_stride_bytes = y_stride_bytes;
+    ga.wait_previous = wait_previous;
+    ga.counter = d_counter;
+    return launch_gemv_dp4a(static_cast<cudaStream_t>(stream), d_w, nullptr, d_x, d_ws, nullptr, K, N_local, M,
+                            JQ_ORDER_COL_KSUPER, s_mode, &ga);
+}
+
+int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const unsigned *d_epoch) {
+    if (!d_flags || !d_epoch || world < 1 || world > MAX_PEERS) return set_error(JQ_ERR_INVALID_ARG, "bad pointer or world size");
+    return launch_allgather_wait(static_cast<cudaStream_t>(stream), static_cast<const uint32_t *>(d_flags), world, d_epoch);
+}
+
 // ---- the entry point that allocates nothing ---------------------------------------------------------
 // Scratch for the quantized activations, part of the library image (see include/jq_b200.h).  In host
 // code this name is only a handle for the runtime: the kernels must be given the device address that

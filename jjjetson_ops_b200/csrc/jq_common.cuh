@@ -62,12 +62,32 @@ int launch_mmq_generic(cudaStream_t st, const void *d_w, const void *d_xq, float
                        int64_t N, int64_t M, int order);
 int launch_block_sums(cudaStream_t st, const void *d_w, const void *d_xq, int32_t *d_sums, int64_t K,
                       int64_t N, int64_t M, int order);
+// Optional epilogue of the dp4a GEMV for N-sharded layers: every rank stores its band of the output
+// straight into all ranks' [M][N_total] buffers (peer-mapped memory, plain stores over NVLink) and
+// the kernel ends only when every rank's band has arrived everywhere.
+constexpr int MAX_PEERS = 8;
+struct GatherArgs {
+    float *y_peer[MAX_PEERS];        // base of each rank's output buffer, as mapped on this device
+    uint32_t *flag_peer[MAX_PEERS];  // base of each rank's arrival flags (uint32[world])
+    int world = 0, rank = 0;
+    int64_t n_offset = 0, N_total = 0;
+    uint32_t *epoch_ptr = nullptr;   // local device counter of finished all-gathers (zero before the first call).
+                                     // This call is number *epoch_ptr + 1: it stores into buffer (number & 1),
+                                     // raises the peers' flags to its number and then increments the counter.
+    uint64_t y_stride_bytes = 0;     // distance between the two output buffers of a rank
+    int wait_previous = 0;           // wait until all flags here have reached *epoch_ptr before reading x
+    int *counter = nullptr;          // local int, zero before the first call (the kernel re-zeroes it)
+};
+
+// Waits (bounded) on the stream until all `world` flags have reached *d_epoch.
+int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, const uint32_t *d_epoch);
+
 // Streaming GEMV family.  d_x_f32 != nullptr fuses the activation quantizer into the prologue
 // (d_xq then receives the quantized blocks in JQ_ORDER_COL_KSUPER order, may be nullptr).
 // Returns JQ_ERR_UNSUPPORTED when the shape or alignment rules of the fast path do not hold.
 int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
                      void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
-                     int s_mode);
+                     int s_mode, const GatherArgs *gather = nullptr);
 int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
                     void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
                     int s_mode);

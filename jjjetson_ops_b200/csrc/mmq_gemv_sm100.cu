@@ -49,6 +49,9 @@ struct GemvParams {
     int rows_per_stage;
     int prefetch_early;    // the weight stream may start before the preceding kernel in the stream has finished
     int early_stages;      // stages the producer may request before the activations are staged
+    GatherArgs gather;     // all-gather epilogue (world == 0: plain store to y)
+    uint32_t y_bytes;      // shared bytes of the band staging buffer [M][y_rows] (gather only)
+    uint32_t y_rows;
     unsigned long long *trace;  // 8 timestamps per CTA of this launch (tracing aid), or nullptr
 };
 
@@ -69,6 +72,26 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void cta_row_range(int64_t N, int64_t *begin, int64_t *end) {
     *begin = (int64_t)blockIdx.x * N / gridDim.x;
     *end = (int64_t)(blockIdx.x + 1) * N / gridDim.x;
+}
+
+// Lanes 0..world-1 of one warp poll this rank's arrival flags until each has reached `epoch`.
+__device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uint32_t epoch, int lane, int *fault) {
+    if (lane < world) {
+        bool seen = false;
+        for (uint32_t spin = 0; spin < (1u << 22) && !seen; ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+            seen = (int32_t)(v - epoch) >= 0;
+        }
+        if (!seen && fault != nullptr) atomicExch(fault, 2);
+    }
+    __syncwarp();
+}
+
+__global__ void allgather_wait_kernel(const uint32_t *flags, int world, const uint32_t *epoch_ptr, int *fault) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(epoch_ptr);
+    if (epoch != 0) wait_flags(flags, world, epoch, (int)threadIdx.x, fault);
 }
 
 // Producer: one thread walks the CTA's row slab stage by stage.
@@ -181,7 +204,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + GV_MAX_STAGES;
     uint64_t *x_ready = full + 24;
-    uint8_t *xs = smem + GV_BAR_BYTES;
+    float *ybuf = reinterpret_cast<float *>(smem + GV_BAR_BYTES);
+    uint8_t *xs = smem + GV_BAR_BYTES + p.y_bytes;
     uint8_t *ring = xs + p.x_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -207,6 +231,16 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         return;
     }
     griddep_wait();  // activations may come from, and outputs may be read by, the previous kernel
+    uint32_t gather_epoch = 0;  // number of this all-gather (previous ones finished: *epoch_ptr)
+    if (p.gather.world > 0) {
+        const uint32_t done = *reinterpret_cast<const volatile uint32_t *>(p.gather.epoch_ptr);
+        gather_epoch = done + 1;
+        if (p.gather.wait_previous && done != 0) {
+            // the activations are the output of the previous sharded layer: all its bands must be here
+            if (warp == 0) wait_flags(p.gather.flag_peer[p.gather.rank], p.gather.world, done, lane, p.fault);
+            named_bar_sync(1, NW * 32);
+        }
+    }
     if (threadIdx.x == 0) trace_stamp(p, 3);  // predecessor finished
 
     stage_activations<NW>(p, xs, x_ready, warp, lane);
@@ -318,13 +352,58 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                 float v = acc[m];
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
-                if (lane == 0 && m < p.M) p.y[(size_t)m * p.N + (r0 + r)] = v;
+                if (lane == 0 && m < p.M) {
+                    if (p.gather.world > 0) {
+                        ybuf[(size_t)m * p.y_rows + (size_t)(r0 + r - r_begin)] = v;
+                    } else {
+                        p.y[(size_t)m * p.N + (r0 + r)] = v;
+                    }
+                }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
     if (threadIdx.x == 0) trace_stamp(p, 7);  // warp 0 done
+
+    if (p.gather.world > 0) {
+        // ---- all-gather epilogue: this CTA's rows of the band go to every rank's buffer ----------
+        const GatherArgs &ga = p.gather;
+        named_bar_sync(1, NW * 32);  // the band of this CTA is complete in shared memory
+        const int rows_cta = (int)(r_end - r_begin);
+        for (int idx = warp; idx < ga.world * p.M; idx += NW) {
+            const int q = idx / p.M, m = idx - q * p.M;
+            float *dst = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ga.y_peer[q]) +
+                                                   (size_t)(gather_epoch & 1u) * ga.y_stride_bytes) +
+                         (size_t)m * ga.N_total + ga.n_offset + r_begin;
+            const float *src = ybuf + (size_t)m * p.y_rows;
+            for (int i = lane; i < rows_cta; i += 32) dst[i] = src[i];  // 128 contiguous bytes per warp store
+        }
+        named_bar_sync(1, NW * 32);  // all of this CTA's peer stores have been issued
+        if (warp == 0) {
+            int last = 0;
+            if (lane == 0) {
+                __threadfence_system();  // cumulative over the stores ordered before it by the barrier
+                const int prev = atomicAdd(ga.counter, 1);
+                last = (prev == (int)gridDim.x - 1);
+            }
+            last = __shfl_sync(0xFFFFFFFFu, last, 0);
+            if (last) {
+                // every CTA of this rank has made its band visible system-wide: tell every rank.
+                // Nobody waits here; the consumer of the gathered output waits for the flags.
+                __threadfence_system();
+                if (lane == 0) {
+                    *ga.counter = 0;
+                    *ga.epoch_ptr = gather_epoch;
+                    __threadfence();
+                }
+                if (lane < ga.world) {
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ga.flag_peer[lane] + ga.rank), "r"(gather_epoch)
+                                 : "memory");
+                }
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -563,15 +642,23 @@ int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     const int64_t budget = min((int64_t)caps.smem_optin, (int64_t)caps.smem_per_sm / MINB - 1024);
     p.rows_per_stage = MINB > 1 ? 8 : NW;
     p.row_stride = p.row_bytes;
+    p.y_bytes = 0;
+    p.y_rows = 0;
+    if (p.gather.world > 0) {
+        // rows per CTA are at most ceil(N / grid) + 1 and the grid is at least min(SMs * MINB, N / rows_per_stage)
+        const int64_t min_grid = max((int64_t)1, min((int64_t)caps.sm_count * MINB, (p.N + p.rows_per_stage - 1) / p.rows_per_stage));
+        p.y_rows = (uint32_t)((p.N + min_grid - 1) / min_grid + 1);
+        p.y_bytes = align_up((uint32_t)p.M * p.y_rows * 4u, 128);
+    }
     for (;;) {
         p.stage_bytes = align_up((uint32_t)p.rows_per_stage * p.row_bytes, 128);
-        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes;
+        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes - p.y_bytes;
         p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
         if (p.stages >= 3 || p.rows_per_stage == 1) break;
         p.rows_per_stage = p.rows_per_stage > 2 ? p.rows_per_stage / 2 : 1;
     }
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
-    const int smem = GV_BAR_BYTES + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+    const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
     auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
@@ -628,8 +715,22 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
 
 }  // namespace
 
+int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, const uint32_t *d_epoch) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_wait_kernel, d_flags, world, d_epoch, device_fault_ptr()));
+    return JQ_OK;
+}
+
 int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
-                     float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+                     float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode, const GatherArgs *gather) {
     if (M < 1 || M > 2) return set_error(JQ_ERR_UNSUPPORTED, "dp4a GEMV handles M <= 2 (M = %lld)", (long long)M);
     if (int rc = fast_path_ok(d_w, d_xq, d_x_f32, K, N)) return rc;
     if (N == 0) return JQ_OK;
@@ -637,6 +738,7 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     if (int rc = device_caps(&caps)) return rc;
     GemvParams p{};
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
+    if (gather != nullptr) p.gather = *gather;
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {

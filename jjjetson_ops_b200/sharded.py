@@ -76,3 +76,83 @@ class ShardedLinearQ4_0:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         return self.gather(self.local(x))
+
+
+class PeerBands:
+    """Output buffers of the fused multiply + all-gather (``jq_linear_q4_0_allgather_device``).
+
+    Every rank allocates one block of peer-mappable memory holding two ``[M_max, N_total]`` fp32
+    output buffers (used alternately, so that a fast rank never overwrites what a slow rank's
+    consumer still reads) and its arrival flags, and maps the blocks of all other ranks.  The
+    64-byte handles travel through ``all_gather_object``.
+    """
+
+    FLAG_BYTES = 256
+
+    def __init__(self, M_max: int, N_total: int, device: torch.device, group=None):
+        from . import capi
+
+        self._capi = capi
+        self.group = group
+        self.device = device
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("the fused all-gather handles up to 8 ranks")
+        self.M_max, self.N_total = M_max, N_total
+        self.y_bytes = (M_max * N_total * 4 + 255) // 256 * 256
+        with torch.cuda.device(device):
+            self.local_ptr, handle = capi.peer_alloc(2 * self.y_bytes + self.FLAG_BYTES)
+        handles = [handle]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+        self.ptrs = []
+        with torch.cuda.device(device):
+            for q in range(self.world):
+                self.ptrs.append(self.local_ptr if q == self.rank else capi.peer_open(handles[q]))
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)  # finished all-gathers, kept on the device
+        self._views = [capi.tensor_from_ptr(self.local_ptr + b * self.y_bytes, (M_max, N_total), torch.float32, device)
+                       for b in range(2)]
+        if self.world > 1:
+            dist.barrier(group=group)  # everyone has mapped everyone before the first store
+
+    def linear(self, w_shard: torch.Tensor, x: torch.Tensor, ws: torch.Tensor, n_offset: int, N_local: int,
+               s_mode: Optional[int] = None) -> None:
+        """Queue one fused step.  The step first waits (on the device) for the previous step's bands;
+        call ``wait()`` and then ``latest()`` to read the gathered output."""
+        capi = self._capi
+        M = x.shape[0]
+        if M != self.M_max:
+            raise ValueError("PeerBands was sized for M = %d" % self.M_max)
+        y_peers = list(self.ptrs)
+        flag_peers = [p + 2 * self.y_bytes for p in self.ptrs]
+        capi.linear_q4_0_allgather(w_shard, x, ws, N_local, capi.S_D_SUM_Q if s_mode is None else s_mode, y_peers,
+                                   flag_peers, self.world, self.rank, n_offset, self.N_total, self.y_bytes, True,
+                                   self.epoch, self.counter)
+
+    def wait(self) -> None:
+        """Queue a wait (on the current stream) for the bands of the latest step from every rank."""
+        self._capi.allgather_wait(self.device, self.local_ptr + 2 * self.y_bytes, self.world, self.epoch)
+
+    def latest(self) -> torch.Tensor:
+        """After ``wait()``: the gathered ``[M, N_total]`` output of the latest step (synchronises to
+        read the device-side step counter, which picks the buffer)."""
+        return self._views[int(self.epoch.item()) & 1]
+
+    def close(self) -> None:
+        if self.local_ptr is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody is still storing into anybody
+        with torch.cuda.device(self.device):
+            for q, p in enumerate(self.ptrs):
+                if q != self.rank:
+                    self._capi.peer_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            self._capi.peer_free(self.local_ptr)
+        self.local_ptr = None

@@ -1,0 +1,129 @@
+"""GPU tests of the fused multiply + all-gather (``jq_linear_q4_0_allgather_device``).
+
+On one GPU the kernel runs with world = 1 (its band staging, peer-store loop, completion counter
+and flag logic all execute, with itself as the only peer).  With two or more GPUs a two-rank run
+(one process per GPU, NCCL only for the rendezvous of the IPC handles) checks real peer stores.
+No test makes a rank wait for a peer that never arrives.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 11008, 1), (4096, 1000, 2), (8192, 4096, 1), (2048, 37, 1)])
+def test_fused_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M):
+    import torch
+
+    from jjjetson_ops_b200.sharded import PeerBands
+
+    c = native_lib
+    rng = np.random.default_rng(K + N + M)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    wq = oracle.quantize_q4_0(w)
+    d_w = torch.from_numpy(wq).to(cuda_device)
+    ws = torch.zeros(c.q8_1_bytes(K, M), dtype=torch.uint8, device=cuda_device)
+    bands = PeerBands(M, N, cuda_device)
+    try:
+        for step in range(3):  # alternates the two output buffers and advances the epoch
+            x = rng.standard_normal((M, K), dtype=np.float32)
+            bands.linear(d_w, torch.from_numpy(x).to(cuda_device), ws, 0, N)
+            bands.wait()
+            y = bands.latest().cpu().numpy()
+            assert int(bands.epoch.item()) == step + 1
+            xq = oracle.quantize_q8_1(x, oracle.ORDER_COL_KSUPER, oracle.S_D_SUM_Q)
+            assert np.array_equal(ws.cpu().numpy(), xq)
+            assert oracle.err_max_rel(y, oracle.mul_mat_ref(wq, xq, K, N, M)) <= 1e-5
+            assert int(bands.counter.item()) == 0  # the completion counter re-arms itself
+        assert c.device_fault() == 0
+    finally:
+        bands.close()
+
+
+def test_fused_allgather_refuses_other_shapes(native_lib, cuda_device):
+    import torch
+
+    from jjjetson_ops_b200.sharded import PeerBands
+
+    c = native_lib
+    bands = PeerBands(4, 64, cuda_device)
+    try:
+        d_w = torch.zeros(c.q4_0_bytes(64, 256), dtype=torch.uint8, device=cuda_device)
+        x = torch.zeros((4, 256), dtype=torch.float32, device=cuda_device)
+        ws = torch.zeros(c.q8_1_bytes(256, 4), dtype=torch.uint8, device=cuda_device)
+        with pytest.raises(c.JqError) as ei:
+            bands.linear(d_w, x, ws, 0, 64)
+        assert ei.value.status == c.ERR_UNSUPPORTED  # M = 4: gather with NCCL instead
+    finally:
+        bands.close()
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_rank_worker(rank: int, world: int, port: int, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+
+    from jjjetson_ops_b200 import capi, synth
+    from jjjetson_ops_b200.sharded import PeerBands
+    from oracle import jq_oracle as O
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        K, N, M = 4096, 4096 + 64, 1
+        rng = np.random.default_rng(77)
+        w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        wq = O.quantize_q4_0(w)
+        b, e = synth.shard_rows(N, world, rank)
+        d_w = torch.from_numpy(np.ascontiguousarray(wq[b:e])).to(dev)
+        ws = torch.zeros(capi.q8_1_bytes(K, M), dtype=torch.uint8, device=dev)
+        bands = PeerBands(M, N, dev)
+        ok = True
+        for step in range(4):
+            x = rng.standard_normal((M, K), dtype=np.float32)  # same stream of inputs on every rank
+            bands.linear(d_w, torch.from_numpy(x).to(dev), ws, b, e - b)
+            bands.wait()  # every rank's band has arrived before the buffer is read
+            y = bands.latest().cpu().numpy()
+            xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+            ok = ok and O.err_max_rel(y, O.mul_mat_ref(wq, xq, K, N, M)) <= 1e-5  # all bands, not just ours
+        ok = ok and capi.device_fault() == 0
+        bands.close()
+        q.put((rank, bool(ok)))
+    except Exception as ex:
+        q.put((rank, repr(ex)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_allgather_two_ranks(native_lib, oracle):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert results == [(0, True), (1, True)], results
