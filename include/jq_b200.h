@@ -64,7 +64,8 @@ typedef enum jq_kernel {
     JQ_KERNEL_GENERIC = 1,   /* any shape, plain loads; the safety net */
     JQ_KERNEL_GEMV_DP4A = 2, /* M <= 2: bulk-copy ring, dp4a, warp per row */
     JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
-    JQ_KERNEL_GEMM_MMA = 4   /* M > 8: tiled int8 tensor-core GEMM with per-block rescale */
+    JQ_KERNEL_GEMM_MMA = 4,  /* M > 8: tiled int8 mma.sync GEMM with per-block rescale */
+    JQ_KERNEL_GEMM_TC = 5    /* M > 8: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
 } jq_kernel;
 
 /* Process-wide switches. */

@@ -27,6 +27,7 @@ CUDA_SOURCES = [
     "mmq_generic.cu",
     "mmq_gemv_sm100.cu",
     "mmq_gemm_sm100.cu",
+    "mmq_gemm_tc_sm100.cu",
     "jq_capi.cu",
     "ref_compat.cpp",
 ]

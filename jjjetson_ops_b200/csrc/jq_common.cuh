@@ -93,6 +93,8 @@ int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const fl
                     int s_mode);
 int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                     int64_t N, int64_t M, int order);
+int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                   int64_t N, int64_t M, int order);
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__

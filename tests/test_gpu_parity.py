@@ -127,7 +127,7 @@ def test_mul_mat_small_shapes_all_kernels(env, K, N, M, order):
     w, x = _case(rng, K, N, M)
     wq = env.O.quantize_q4_0(w)
     ran = []
-    for kernel in (c.KERNEL_GENERIC, c.KERNEL_GEMV_DP4A, c.KERNEL_GEMV_MMA, c.KERNEL_GEMM_MMA, c.KERNEL_AUTO):
+    for kernel in (c.KERNEL_GENERIC, c.KERNEL_GEMV_DP4A, c.KERNEL_GEMV_MMA, c.KERNEL_GEMM_MMA, c.KERNEL_GEMM_TC, c.KERNEL_AUTO):
         try:
             _check_mul_mat(env, wq, x, K, N, M, kernel, order, c.S_D_SUM_Q)
             ran.append(kernel)
@@ -139,7 +139,7 @@ def test_mul_mat_small_shapes_all_kernels(env, K, N, M, order):
     if K % 256 == 0 and K <= 6144 and M <= 8:
         assert c.KERNEL_GEMV_MMA in ran
     if K % 256 == 0:
-        assert c.KERNEL_GEMM_MMA in ran
+        assert c.KERNEL_GEMM_MMA in ran and c.KERNEL_GEMM_TC in ran
 
 
 def test_mul_mat_reference_s_mode(env):
@@ -199,6 +199,8 @@ def test_config3_prefill(env):
     wq, x, lin = _config_case(env, 3, 0, 512)
     _check_mul_mat(env, wq, x, lin.K, lin.N, 512, c.KERNEL_AUTO, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
     _check_mul_mat(env, wq, x, lin.K, lin.N, 512, c.KERNEL_AUTO, c.ORDER_KSUPER_COL, c.S_D_SUM_Q)
+    for kernel in (c.KERNEL_GEMM_TC, c.KERNEL_GEMM_MMA):
+        _check_mul_mat(env, wq, x, lin.K, lin.N, 512, kernel, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
 
 
 def test_config4_large_shapes(env):
