@@ -489,12 +489,77 @@ def measure_extras(torch, capi, synth, dev, peaks):
     t = bench_linear(11008, 4096, 1)
     b = synth.algorithmic_bytes(11008, 4096, 1)
     out["cfg5_down_M1"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    # the activation quantizer alone (HBM-bound streaming kernel), prefill-sized input
+    Mq, Kq = 2048, 8192
+    xq_in = torch.from_numpy(np.random.default_rng(7).standard_normal((Mq, Kq), dtype=np.float32)).to(dev)
+    xq_out = torch.zeros(capi.q8_1_bytes(Kq, Mq), dtype=torch.uint8, device=dev)
+    sec, _ = time_graph_steps(torch, lambda i: capi.quantize_q8_1(xq_in, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q, out=xq_out),
+                              50, 3, lambda: None)
+    qb = Mq * Kq * 4 + Mq * (Kq // 128) * 144
+    out["quantize_q8_1_M2048_K8192"] = {"us": sec / 50 * 1e6, "GB/s": qb * 50 / sec / 1e9,
+                                        "frac_hbm": qb * 50 / sec / 1e9 / peaks["hbm_gbs"],
+                                        "note": "85 MB per launch, below L2 size: partly L2-resident"}
+    del xq_in, xq_out
+
+    # cfg5: the five projections of one Llama-7B decoder layer as one dependent chain in one graph
+    for Mc in (1, 128):
+        out["cfg5_chain_M%d" % Mc] = bench_layer_chain(torch, capi, synth, dev, peaks, Mc)
+
     int8_peak = 2.0 * peaks["bf16_tflops"]
     t = bench_linear(4096, 4096, 512, steps=50)
     o = synth.ops(4096, 4096, 512)
     out["cfg3_M512"] = {"us": t * 1e6, "TOPS": o / t / 1e12, "frac_int8_peak": o / t / 1e12 / int8_peak,
                         "int8_peak_tops": int8_peak, "int8_peak_note": "2 x cuBLAS bf16 %s burst" % peaks["source"]}
     return out
+
+
+def bench_layer_chain(torch, capi, synth, dev, peaks, M):
+    """QKV 4096->12288, O 4096->4096 (fed the first 4096 columns of the QKV output), gate and up
+    4096->11008 (fed the O output), down 11008->4096 (fed a synthetic N(0,1) tensor, as configuration 5
+    says).  Every step quantizes its own input.  Several independent layers' worth of weights rotate
+    so that each pass streams its weights from HBM."""
+    rng = np.random.default_rng(4)
+    shapes = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096)]
+    layer_bytes = sum(capi.q4_0_bytes(n, k) for _, k, n in shapes)
+    R = max(2, -(-3 * L2_BYTES // layer_bytes) + 1)
+    layers = []
+    for _ in range(R):
+        ws = []
+        for _, k, n in shapes:
+            b = torch.from_numpy(rng.integers(0, 256, size=capi.q4_0_bytes(n, k), dtype=np.uint8)).to(dev).view(n, -1)
+            blk = b.view(n, k // 32, 18)
+            blk[:, :, 0] = 0
+            blk[:, :, 1] = 0x20  # d = 2^-7 everywhere: random nibbles, finite scales
+            ws.append(b)
+        layers.append(ws)
+    x0 = torch.from_numpy(rng.standard_normal((M, 4096), dtype=np.float32)).to(dev)
+    xdown = torch.from_numpy(rng.standard_normal((M, 11008), dtype=np.float32)).to(dev)
+    scratch = torch.zeros(max(capi.q8_1_bytes(11008, M), 16), dtype=torch.uint8, device=dev)
+    y_qkv = torch.zeros((M, 12288), dtype=torch.float32, device=dev)
+    y_o = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
+    y_gate = torch.zeros((M, 11008), dtype=torch.float32, device=dev)
+    y_up = torch.zeros((M, 11008), dtype=torch.float32, device=dev)
+    y_down = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
+    o_in = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
+
+    def step(i):
+        w = layers[i % R]
+        capi.linear_q4_0(w[0], x0, 12288, capi.S_D_SUM_Q, ws=scratch, out=y_qkv)
+        o_in.copy_(y_qkv[:, :4096])
+        capi.linear_q4_0(w[1], o_in, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_o)
+        capi.linear_q4_0(w[2], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_gate)
+        capi.linear_q4_0(w[3], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_up)
+        capi.linear_q4_0(w[4], xdown, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_down)
+
+    steps = 40 if M == 1 else 10
+    sec, _ = time_graph_steps(torch, step, steps, 3, lambda: None)
+    t = sec / steps
+    alg = sum(synth.algorithmic_bytes(k, n, M) for _, k, n in shapes)
+    ops = sum(synth.ops(k, n, M) for _, k, n in shapes)
+    del layers
+    torch.cuda.empty_cache()
+    return {"us": t * 1e6, "GB/s": alg / t / 1e9, "frac_hbm": alg / t / 1e9 / peaks["hbm_gbs"], "TOPS": ops / t / 1e12,
+            "launches_per_pass": "5 linears (+1 slice copy)", "weight_copies": R}
 
 
 def main() -> None:
