@@ -414,7 +414,8 @@ def measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, 
     return {
         "value": alg * world * steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": int(x_pin.numel() * 4),
         "d2h_bytes_per_step": int(y_pin.numel() * 4), "steps": steps, "ms_per_step": dt / steps * 1e3,
-        "api": "jq_linear_q4_0_host (weights resident, pinned host activations and outputs, synchronous)",
+        "api": "jq_linear_q4_0_host (weights resident; pinned, mapped host activations and outputs; synchronous; "
+               "the quantizer reads x over the bus and a copy kernel writes y back, no copy-engine transfers)",
         "weight_copies": n_handles,
     }
 

@@ -1,6 +1,7 @@
 // C ABI of the library: argument checking, kernel selection, the reference-style host wrappers,
 // resident weights, and the device description.  Declarations and the reference lines each entry
 // point replaces are in include/jq_b200.h.
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -146,6 +147,46 @@ int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *
     if (rc == JQ_OK) t_last_error.clear();
     return rc;
 }
+
+
+// Device-side alias of a pinned, mapped host buffer (nullptr for pageable memory).
+void *mapped_alias(const void *host_ptr) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) return nullptr;
+    return attr.devicePointer;
+}
+
+// Coalesced copy, used to write a small result straight into mapped host memory: for tens of KB
+// one kernel is much quicker than a separate copy-engine transfer.
+// With a single block it can also publish a completion ticket in mapped host memory, which the
+// host polls instead of paying a stream synchronisation's wake-up latency.
+__global__ void copy_f32_kernel(float *__restrict__ dst, const float *__restrict__ src, int64_t n,
+                                volatile unsigned *done_flag, unsigned ticket) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
+    for (int64_t i = i0; i < n; i += stride) {
+        if (i + 4 <= n) {
+            *reinterpret_cast<float4 *>(dst + i) = *reinterpret_cast<const float4 *>(src + i);
+        } else {
+            for (int64_t j = i; j < n; ++j) dst[j] = src[j];
+        }
+    }
+    if (done_flag != nullptr) {  // single-block launches only
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // ticket == 0: count completions on the device (lets a captured graph be replayed)
+            *done_flag = ticket != 0 ? ticket : *done_flag + 1;
+            __threadfence_system();
+        }
+    }
+}
+
 
 }  // namespace
 }  // namespace jq
@@ -544,7 +585,26 @@ struct jq_weights {
     cudaStream_t stream = nullptr;
     void *d_x = nullptr, *d_ws = nullptr, *d_y = nullptr;
     int64_t m_cap = 0;
+    // last host buffers seen and their device aliases (non-null when the buffer is pinned and mapped)
+    const void *seen_x = nullptr;
+    const void *seen_y = nullptr;
+    const float *x_alias = nullptr;
+    float *y_alias = nullptr;
+    // completion ticket in pinned, mapped host memory (written by the copy kernel, polled by the host)
+    unsigned *h_done = nullptr;
+    unsigned *d_done = nullptr;
+    unsigned ticket = 0;
+    // the three launches of a zero-copy call (quantize, multiply, copy back) as one graph, built the
+    // second time the same buffers and batch size are seen
+    cudaGraphExec_t graph = nullptr;
+    const void *graph_x = nullptr;
+    const void *graph_y = nullptr;
+    int64_t graph_m = 0;
+    int graph_s_mode = 0;
+    int graph_hits = 0;
 };
+
+
 
 int jq_weights_create(const void *host_w_q4_0, int64_t N, int64_t K, jq_weights **out) {
     if (out == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null out pointer");
@@ -560,6 +620,12 @@ int jq_weights_create(const void *host_w_q4_0, int64_t N, int64_t K, jq_weights 
     const size_t bytes = jq_q4_0_bytes(N, K);
     if (e == cudaSuccess && bytes) e = cudaMalloc(&w->d_w, bytes);
     if (e == cudaSuccess && bytes) e = cudaMemcpy(w->d_w, host_w_q4_0, bytes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && cudaHostAlloc(reinterpret_cast<void **>(&w->h_done), 64, cudaHostAllocMapped) == cudaSuccess) {
+        *w->h_done = 0;
+        if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&w->d_done), w->h_done, 0) != cudaSuccess) w->d_done = nullptr;
+    } else {
+        (void)cudaGetLastError();  // no ticket: completion falls back to stream synchronisation
+    }
     if (e != cudaSuccess) {
         const int rc = cuda_error(e, "jq_weights_create");
         jq_weights_destroy(w);
@@ -576,6 +642,8 @@ int jq_weights_destroy(jq_weights *w) {
     cudaFree(w->d_x);
     cudaFree(w->d_ws);
     cudaFree(w->d_y);
+    if (w->graph) cudaGraphExecDestroy(w->graph);
+    if (w->h_done) cudaFreeHost(w->h_done);
     if (w->stream) cudaStreamDestroy(w->stream);
     delete w;
     return JQ_OK;
@@ -600,14 +668,104 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
         JQ_CUDA_TRY(cudaMalloc(&w->d_y, (size_t)M * w->N * sizeof(float) + 16));
         w->m_cap = M;
     }
-    JQ_CUDA_TRY(cudaMemcpyAsync(w->d_x, x, (size_t)M * w->K * sizeof(float), cudaMemcpyHostToDevice, w->stream));
-    if (int rc = jq_linear_q4_0_device(w->stream, w->d_w, static_cast<const float *>(w->d_x), w->d_ws,
-                                       static_cast<float *>(w->d_y), w->K, w->N, M, s_mode))
-        return rc;
-    if (quant_workspace)
-        JQ_CUDA_TRY(cudaMemcpyAsync(quant_workspace, w->d_ws, jq_q8_1_bytes(w->K, M), cudaMemcpyDeviceToHost, w->stream));
-    JQ_CUDA_TRY(cudaMemcpyAsync(y, w->d_y, (size_t)M * w->N * sizeof(float), cudaMemcpyDeviceToHost, w->stream));
-    JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+    if (x != w->seen_x) {
+        w->seen_x = x;
+        w->x_alias = static_cast<const float *>(mapped_alias(x));
+    }
+    if (y != w->seen_y) {
+        w->seen_y = y;
+        w->y_alias = static_cast<float *>(mapped_alias(y));
+    }
+    const size_t y_count = (size_t)M * w->N;
+    // Small decode batches from pinned, mapped host memory skip the copy engines: the quantizer
+    // reads the activations over the bus itself and a copy kernel writes the result back.
+    const bool zero_copy_in = w->x_alias != nullptr && M <= 8 && ((uintptr_t)w->x_alias & 15u) == 0 && w->K % SUPER == 0;
+    const bool zero_copy_out = w->y_alias != nullptr && y_count * sizeof(float) <= (1u << 20) && ((uintptr_t)w->y_alias & 15u) == 0;
+    const bool ticketed = zero_copy_in && zero_copy_out && y_count <= 65536 && w->d_done != nullptr && quant_workspace == nullptr;
+
+    auto enqueue = [&](unsigned ticket) -> int {
+        if (zero_copy_in) {
+            if (int rc = launch_quantize_q8_1(w->stream, w->x_alias, w->d_ws, w->K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
+            if (int rc = dispatch_mul_mat(w->stream, w->d_w, w->d_ws, static_cast<float *>(w->d_y), w->K, w->N, M,
+                                          JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO))
+                return rc;
+        } else {
+            JQ_CUDA_TRY(cudaMemcpyAsync(w->d_x, x, (size_t)M * w->K * sizeof(float), cudaMemcpyHostToDevice, w->stream));
+            if (int rc = jq_linear_q4_0_device(w->stream, w->d_w, static_cast<const float *>(w->d_x), w->d_ws,
+                                               static_cast<float *>(w->d_y), w->K, w->N, M, s_mode))
+                return rc;
+        }
+        if (quant_workspace)
+            JQ_CUDA_TRY(cudaMemcpyAsync(quant_workspace, w->d_ws, jq_q8_1_bytes(w->K, M), cudaMemcpyDeviceToHost, w->stream));
+        if (zero_copy_out) {
+            const int threads = ticketed ? 1024 : 256;
+            const int blocks = ticketed ? 1 : (int)std::min<size_t>(8, (y_count / 4 + threads - 1) / threads + 1);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)blocks);
+            cfg.blockDim = dim3(threads);
+            cfg.stream = w->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            volatile unsigned *flag = ticketed ? w->d_done : nullptr;
+            JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, copy_f32_kernel, w->y_alias, static_cast<const float *>(w->d_y),
+                                           (int64_t)y_count, flag, ticket));
+        } else {
+            JQ_CUDA_TRY(cudaMemcpyAsync(y, w->d_y, y_count * sizeof(float), cudaMemcpyDeviceToHost, w->stream));
+        }
+        return JQ_OK;
+    };
+
+    bool launched = false;
+    if (ticketed) {
+        const bool same = w->graph_x == x && w->graph_y == y && w->graph_m == M && w->graph_s_mode == s_mode;
+        if (!same) {
+            if (w->graph) {
+                JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+                cudaGraphExecDestroy(w->graph);
+                w->graph = nullptr;
+            }
+            w->graph_x = x;
+            w->graph_y = y;
+            w->graph_m = M;
+            w->graph_s_mode = s_mode;
+            w->graph_hits = 0;
+        } else if (w->graph == nullptr && ++w->graph_hits >= 2) {
+            // third call with the same buffers: record the three launches once, replay them from now on
+            cudaGraph_t g = nullptr;
+            if (cudaStreamBeginCapture(w->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                const int rc = enqueue(0u);
+                const cudaError_t e = cudaStreamEndCapture(w->stream, &g);
+                if (rc == JQ_OK && e == cudaSuccess && g != nullptr) {
+                    if (cudaGraphInstantiate(&w->graph, g, 0) != cudaSuccess) w->graph = nullptr;
+                }
+                if (g) cudaGraphDestroy(g);
+            }
+            (void)cudaGetLastError();
+        }
+        if (w->graph != nullptr) {
+            JQ_CUDA_TRY(cudaGraphLaunch(w->graph, w->stream));
+            launched = true;
+        }
+    }
+    unsigned expect = 0;
+    if (ticketed) expect = ++w->ticket;  // the flag counts completed ticketed calls
+    if (!launched) {
+        if (int rc = enqueue(0u)) return rc;
+    }
+    bool polled = false;
+    if (ticketed) {
+        volatile unsigned *h = w->h_done;
+        for (long spin = 0; spin < 20000000L; ++spin) {
+            if (*h == expect) {
+                polled = true;
+                break;
+            }
+        }
+    }
+    if (!polled) JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
     return JQ_OK;
 }
 

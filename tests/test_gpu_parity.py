@@ -362,6 +362,36 @@ def test_resident_weights_host_linear(env):
         rw.close()
 
 
+def test_resident_weights_host_linear_pinned_buffers(env):
+    """Pinned (mapped) host buffers take the path without copy-engine transfers: the quantizer reads
+    x over the bus, a copy kernel writes y back.  Same results as with pageable buffers."""
+    c, t = env.c, env.t
+    rng = np.random.default_rng(32)
+    K, N = 4096, 11008
+    w, x = _case(rng, K, N, 8)
+    wq = env.O.quantize_q4_0(w)
+    rw = c.ResidentWeights(wq, N, K)
+    try:
+        for M in (1, 8, 2):
+            x_pin = t.from_numpy(np.ascontiguousarray(x[:M])).pin_memory()
+            y_pin = t.zeros((M, N), dtype=t.float32).pin_memory()
+            for _ in range(2):  # second call reuses the cached buffer attributes
+                y_pin.zero_()
+                rw.linear(x_pin.data_ptr(), y_pin.data_ptr(), M, c.S_D_SUM_Q)
+                xq = env.O.quantize_q8_1(x[:M], c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+                assert env.O.err_max_rel(y_pin.numpy(), env.O.mul_mat_ref(wq, xq, K, N, M)) <= TOL_FORMULA
+            # pageable output with pinned input, and the other way round
+            y_page = np.zeros((M, N), dtype=np.float32)
+            rw.linear(x_pin.data_ptr(), y_page.ctypes.data, M, c.S_D_SUM_Q)
+            assert np.array_equal(y_page, y_pin.numpy())
+            x_page = np.ascontiguousarray(x[:M])
+            y_pin.zero_()
+            rw.linear(x_page.ctypes.data, y_pin.data_ptr(), M, c.S_D_SUM_Q)
+            assert env.O.err_max_rel(y_pin.numpy(), y_page) <= TOL_FORMULA
+    finally:
+        rw.close()
+
+
 def test_device_hw_info(env):
     info = env.c.query_device_hw_info(0)
     assert info["sm_count"] > 0 and info["cc_major"] >= 10, info
