@@ -65,7 +65,7 @@ typedef enum jq_kernel {
     JQ_KERNEL_GEMV_DP4A = 2, /* M <= 2: bulk-copy ring, dp4a, warp per row */
     JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
     JQ_KERNEL_GEMM_MMA = 4,  /* M > 8: tiled int8 mma.sync GEMM with per-block rescale */
-    JQ_KERNEL_GEMM_TC = 5    /* M > 8: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
+    JQ_KERNEL_GEMM_TC = 5    /* M > 8, K % 128 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
 } jq_kernel;
 
 /* Process-wide switches. */
@@ -85,7 +85,11 @@ int jq_get_option(int option, int *value_out);
  * of a streaming GEMV writes 8 device-clock timestamps (ns, %globaltimer) per CTA into its own
  * 512 x 8 x uint64 slice of d_buf (CTA start, weight stream begins, last copy issued, predecessor
  * finished, activations staged, first stage landed, last stage landed, done).  d_buf must hold
- * n * 32768 bytes and be zeroed by the caller.  jq_trace_enable(NULL, 0) switches it off. */
+ * n * 32768 bytes and be zeroed by the caller.  jq_trace_enable(NULL, 0) switches it off.
+ * The tcgen05 GEMM uses its slice differently: SM clock stamps of CTA (0,0) for the first 128
+ * blocks of K, four groups of 128 rows x 8 columns (accumulator seen complete / previous block
+ * accumulated / buffer handed back, one column per drain warp; then MMA issue time in column 0
+ * and stage publication per producer warp in columns 1-3). */
 int jq_trace_enable(void *d_buf, int64_t n_launches);
 
 const char *jq_status_string(int status);
