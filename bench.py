@@ -506,12 +506,126 @@ def measure_extras(torch, capi, synth, dev, peaks):
     for Mc in (1, 128):
         out["cfg5_chain_M%d" % Mc] = bench_layer_chain(torch, capi, synth, dev, peaks, Mc)
 
+    # the layer's own data flow around the linears, fp32 hand-offs against Q8_1 hand-offs
+    for Mc in (1, 128):
+        out["layer_dataflow_M%d" % Mc] = bench_layer_dataflow(torch, capi, synth, dev, peaks, Mc)
+    out.update(bench_producers(torch, capi, dev, peaks))
+
     int8_peak = 2.0 * peaks["bf16_tflops"]
     t = bench_linear(4096, 4096, 512, steps=50)
     o = synth.ops(4096, 4096, 512)
     out["cfg3_M512"] = {"us": t * 1e6, "TOPS": o / t / 1e12, "frac_int8_peak": o / t / 1e12 / int8_peak,
                         "int8_peak_tops": int8_peak, "int8_peak_note": "2 x cuBLAS bf16 %s burst" % peaks["source"]}
     return out
+
+
+def bench_producers(torch, capi, dev, peaks):
+    """The two producer kernels alone on prefill-sized inputs (HBM-bound streaming kernels)."""
+    out = {}
+    rng = np.random.default_rng(8)
+    T, H, I = 4096, 4096, 11008
+    x = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
+    res = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
+    w = torch.ones(H, dtype=torch.float32, device=dev)
+    xq = torch.zeros(capi.q8_1_bytes(H, T), dtype=torch.uint8, device=dev)
+    sec, _ = time_graph_steps(torch, lambda i: capi.rms_norm_q8_1(x, w, 1e-6, residual=res, xq=xq), 20, 3, lambda: None)
+    b = T * H * 4 * 3 + H * 4 + T * (H // 128) * 144  # read input and residual, write residual and the blocks
+    out["rms_norm_fused_add_q8_1_T4096_H4096"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
+                                                  "frac_hbm": b * 20 / sec / 1e9 / peaks["hbm_gbs"],
+                                                  "bytes": b, "note": "201 MB per launch: larger than L2"}
+    del x, res, xq
+    Ts = 2048
+    g = torch.from_numpy(rng.standard_normal((Ts, I), dtype=np.float32)).to(dev)
+    u = torch.from_numpy(rng.standard_normal((Ts, I), dtype=np.float32)).to(dev)
+    mq = torch.zeros(capi.q8_1_bytes(I, Ts), dtype=torch.uint8, device=dev)
+    sec, _ = time_graph_steps(torch, lambda i: capi.swiglu_q8_1(g, u, xq=mq), 20, 3, lambda: None)
+    b = Ts * I * 4 * 2 + Ts * (I // 128) * 144
+    out["swiglu_q8_1_T2048_I11008"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
+                                       "frac_hbm": b * 20 / sec / 1e9 / peaks["hbm_gbs"], "bytes": b,
+                                       "note": "206 MB per launch: larger than L2"}
+    del g, u, mq
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_layer_dataflow(torch, capi, synth, dev, peaks, M):
+    """One decoder layer's linears with the kernels that feed them (the reference's layer,
+    src/engine/transformer_runner.cpp:208-328, without attention, which is not on this path): RMSNorm with
+    residual add -> QKV -> (first 4096 columns) -> O -> RMSNorm with residual add -> gate, up -> SwiGLU -> down.
+    Timed twice: fp32 hand-offs (every linear quantizes its input itself) and Q8_1 hand-offs (the producers
+    write the blocks; gate and up share them)."""
+    rng = np.random.default_rng(4)
+    shapes = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096)]
+    layer_bytes = sum(capi.q4_0_bytes(n, k) for _, k, n in shapes)
+    R = max(2, -(-3 * L2_BYTES // layer_bytes) + 1)
+    layers = []
+    for _ in range(R):
+        ws = []
+        for _, k, n in shapes:
+            b = torch.from_numpy(rng.integers(0, 256, size=capi.q4_0_bytes(n, k), dtype=np.uint8)).to(dev).view(n, -1)
+            blk = b.view(n, k // 32, 18)
+            blk[:, :, 0] = 0
+            blk[:, :, 1] = 0x20
+            ws.append(b)
+        layers.append(ws)
+    H, I = 4096, 11008
+    h0 = torch.from_numpy(rng.standard_normal((M, H), dtype=np.float32)).to(dev)
+    hidden = torch.zeros((M, H), dtype=torch.float32, device=dev)
+    residual = torch.zeros((M, H), dtype=torch.float32, device=dev)
+    wn = torch.ones(H, dtype=torch.float32, device=dev)
+    scratch = torch.zeros(max(capi.q8_1_bytes(I, M), 16), dtype=torch.uint8, device=dev)
+    hq = torch.zeros(max(capi.q8_1_bytes(H, M), 16), dtype=torch.uint8, device=dev)
+    mq = torch.zeros(max(capi.q8_1_bytes(I, M), 16), dtype=torch.uint8, device=dev)
+    y_qkv = torch.zeros((M, 12288), dtype=torch.float32, device=dev)
+    attn = torch.zeros((M, H), dtype=torch.float32, device=dev)
+    mid_h = torch.zeros((M, H), dtype=torch.float32, device=dev)
+    y_gate = torch.zeros((M, I), dtype=torch.float32, device=dev)
+    y_up = torch.zeros((M, I), dtype=torch.float32, device=dev)
+    ffn_mid = torch.zeros((M, I), dtype=torch.float32, device=dev)
+    y_down = torch.zeros((M, H), dtype=torch.float32, device=dev)
+    D, KS = capi.S_D_SUM_Q, capi.ORDER_COL_KSUPER
+
+    def step_fp32(i):
+        w = layers[i % R]
+        hidden.copy_(h0)
+        residual.zero_()
+        capi.rms_norm_q8_1(hidden, wn, 1e-6, residual=residual, normed=hidden, want_q8=False)
+        capi.linear_q4_0(w[0], hidden, 12288, D, ws=scratch, out=y_qkv)
+        attn.copy_(y_qkv[:, :H])
+        capi.linear_q4_0(w[1], attn, H, D, ws=scratch, out=mid_h)
+        capi.rms_norm_q8_1(mid_h, wn, 1e-6, residual=residual, normed=mid_h, want_q8=False)
+        capi.linear_q4_0(w[2], mid_h, I, D, ws=scratch, out=y_gate)
+        capi.linear_q4_0(w[3], mid_h, I, D, ws=scratch, out=y_up)
+        capi.swiglu_q8_1(y_gate, y_up, mid=ffn_mid, want_q8=False)
+        capi.linear_q4_0(w[4], ffn_mid, H, D, ws=scratch, out=y_down)
+
+    def step_q8(i):
+        w = layers[i % R]
+        hidden.copy_(h0)
+        residual.zero_()
+        capi.rms_norm_q8_1(hidden, wn, 1e-6, residual=residual, xq=hq)
+        capi.mul_mat_q4_0_q8_1(w[0], hq, H, 12288, M, KS, out=y_qkv)
+        attn.copy_(y_qkv[:, :H])
+        capi.linear_q4_0(w[1], attn, H, D, ws=scratch, out=mid_h)  # its producer (attention) is not on this path
+        capi.rms_norm_q8_1(mid_h, wn, 1e-6, residual=residual, xq=hq)
+        capi.mul_mat_q4_0_q8_1(w[2], hq, H, I, M, KS, out=y_gate)
+        capi.mul_mat_q4_0_q8_1(w[3], hq, H, I, M, KS, out=y_up)
+        capi.swiglu_q8_1(y_gate, y_up, xq=mq)
+        capi.mul_mat_q4_0_q8_1(w[4], mq, I, H, M, KS, out=y_down)
+
+    steps = 40 if M == 1 else 10
+    res = {}
+    for name, fn in (("fp32_handoffs", step_fp32), ("q8_1_handoffs", step_q8)):
+        sec, _ = time_graph_steps(torch, fn, steps, 3, lambda: None)
+        res[name + "_us"] = sec / steps * 1e6
+    alg = sum(synth.algorithmic_bytes(k, n, M) for _, k, n in shapes)
+    res["GB/s_q8_1_handoffs"] = alg / (res["q8_1_handoffs_us"] * 1e-6) / 1e9
+    res["frac_hbm_q8_1_handoffs"] = res["GB/s_q8_1_handoffs"] / peaks["hbm_gbs"]
+    res["kernels_per_layer"] = "5 multiplies + 2 RMSNorm + SwiGLU (+3 small copies/fills); attention not included"
+    res["weight_copies"] = R
+    del layers
+    torch.cuda.empty_cache()
+    return res
 
 
 def bench_layer_chain(torch, capi, synth, dev, peaks, M):

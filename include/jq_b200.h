@@ -130,6 +130,31 @@ int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y,
                           int64_t K, int64_t N, int64_t M, int s_mode);
 
+/* ---- producers of the quantized linear's input ---------------------------------------------
+ * The two kernels that run just ahead of a linear in the reference's transformer layer
+ * (src/engine/transformer_runner.cpp:208-216, 311-328), with the Q8_1 quantizer folded in: the
+ * linear that follows then takes d_xq through jq_mul_mat_q4_0_q8_1_device and no fp32
+ * activation has to be written, re-read and quantized by a launch of its own.  The fp32 values
+ * are computed in the reference's own operation order, so both the fp32 outputs and the blocks
+ * equal "reference kernel, then quantize_q8_1" bit for bit.
+ *
+ * jq_rms_norm_q8_1_device: rms_norm_fused_add_forward_device (src/cuda/rms_norm_fused_add.cu:
+ * 85-105; z = input + residual, residual <- z, normed = z * rsqrt(mean(z^2) + eps) * weight)
+ * when d_residual is given, rms_norm_forward_device (src/cuda/rms_norm.cu) when it is NULL.
+ * Layout as there: [hidden_size] contiguous per token.  d_normed receives the fp32 result when
+ * not NULL (pass d_input for the reference's in-place behaviour); d_xq receives
+ * jq_q8_1_bytes(hidden_size, num_tokens) bytes of blocks when not NULL (hidden_size % 128 == 0).
+ * d_input itself is only read unless it is also d_normed. */
+int jq_rms_norm_q8_1_device(void *stream, float *d_input, float *d_residual, const float *d_weight,
+                            float *d_normed, void *d_xq, int64_t hidden_size, int64_t num_tokens,
+                            float epsilon, int order, int s_mode);
+
+/* swiglu_silu_mul_launch_device (src/cuda/swiglu.cu:18-29): mid = silu(gate) * up over
+ * [intermediate_size] contiguous values per token.  d_mid (fp32) and d_xq (Q8_1 blocks,
+ * intermediate_size % 128 == 0) are each optional, at least one is required. */
+int jq_swiglu_q8_1_device(void *stream, const float *d_gate, const float *d_up, float *d_mid, void *d_xq,
+                          int64_t intermediate_size, int64_t num_tokens, int order, int s_mode);
+
 /* ---- N-sharded decode (no counterpart in the reference, which is single-GPU) -------------------
  * One process per GPU owns a contiguous band of weight rows.  jq_linear_q4_0_allgather_device
  * runs this rank's quantize + multiply (M <= 2) and writes its band of the output directly into

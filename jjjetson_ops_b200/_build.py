@@ -24,6 +24,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 
 CUDA_SOURCES = [
     "quantize.cu",
+    "producers.cu",
     "mmq_generic.cu",
     "mmq_gemv_sm100.cu",
     "mmq_gemm_sm100.cu",

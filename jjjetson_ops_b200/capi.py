@@ -60,6 +60,12 @@ _SIGS = {
     "jq_mul_mat_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_mul_mat_q4_0_q8_1_device_ex": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, _ci]),
     "jq_linear_q4_0_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
+    "jq_rms_norm_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _ci, _ci]),
+    "jq_swiglu_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _ci, _ci]),
+    "rms_norm_fused_add_forward_device": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float]),
+    "rms_norm_forward_device": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float]),
+    "swiglu_silu_mul_launch_device": (None, [_vp, _vp, _vp, _vp, _ci]),
+    "linear_q4_0_forward_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci]),
     "jq_peer_alloc": (_ci, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
     "jq_peer_open": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "jq_peer_close": (_ci, [_vp]),
@@ -171,6 +177,41 @@ def linear_q4_0(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = S_D_SUM_
         check(_lib.jq_linear_q4_0_device(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
                                          _dev(ws, torch.uint8, "ws"), _dev(out, torch.float32, "out"), K, N, M, s_mode))
     return out
+
+
+def rms_norm_q8_1(x: torch.Tensor, weight: torch.Tensor, epsilon: float, residual: Optional[torch.Tensor] = None,
+                  normed: Optional[torch.Tensor] = None, want_q8: bool = True, order: int = ORDER_COL_KSUPER,
+                  s_mode: int = S_D_SUM_Q, xq: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """RMSNorm of ``x`` ``[T, H]`` (with ``residual`` given: z = x + residual, residual <- z first) with the
+    Q8_1 quantizer folded in.  ``normed`` (may be ``x`` itself) receives the fp32 result; the returned uint8
+    tensor holds the Q8_1 blocks of it (``None`` when ``want_q8`` is false)."""
+    T, H = x.shape
+    if want_q8 and xq is None:
+        xq = torch.empty(max(q8_1_bytes(H, T), 16), dtype=torch.uint8, device=x.device)
+    if not want_q8:
+        xq = None
+    with torch.cuda.device(x.device):
+        check(_lib.jq_rms_norm_q8_1_device(
+            _stream(x), _dev(x, torch.float32, "x"), None if residual is None else _dev(residual, torch.float32, "residual"),
+            _dev(weight, torch.float32, "weight"), None if normed is None else _dev(normed, torch.float32, "normed"),
+            None if xq is None else xq.data_ptr(), H, T, float(epsilon), order, s_mode))
+    return xq
+
+
+def swiglu_q8_1(gate: torch.Tensor, up: torch.Tensor, mid: Optional[torch.Tensor] = None, want_q8: bool = True,
+                order: int = ORDER_COL_KSUPER, s_mode: int = S_D_SUM_Q,
+                xq: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """silu(gate) * up over ``[T, I]`` with the Q8_1 quantizer folded in; ``mid`` receives the fp32 result."""
+    T, I = gate.shape
+    if want_q8 and xq is None:
+        xq = torch.empty(max(q8_1_bytes(I, T), 16), dtype=torch.uint8, device=gate.device)
+    if not want_q8:
+        xq = None
+    with torch.cuda.device(gate.device):
+        check(_lib.jq_swiglu_q8_1_device(
+            _stream(gate), _dev(gate, torch.float32, "gate"), _dev(up, torch.float32, "up"),
+            None if mid is None else _dev(mid, torch.float32, "mid"), None if xq is None else xq.data_ptr(), I, T, order, s_mode))
+    return xq
 
 
 NOALLOC_WS_BYTES = 4 << 20

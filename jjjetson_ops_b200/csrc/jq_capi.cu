@@ -255,6 +255,37 @@ int jq_quantize_q8_1_device(void *stream, const float *d_x, void *d_xq, int64_t 
     return launch_quantize_q8_1(static_cast<cudaStream_t>(stream), d_x, d_xq, K, M, order, s_mode);
 }
 
+int jq_rms_norm_q8_1_device(void *stream, float *d_input, float *d_residual, const float *d_weight, float *d_normed,
+                            void *d_xq, int64_t hidden_size, int64_t num_tokens, float epsilon, int order, int s_mode) {
+    if (hidden_size <= 0 || num_tokens <= 0)
+        return set_error(JQ_ERR_INVALID_ARG, "invalid hidden_size=%lld num_tokens=%lld", (long long)hidden_size, (long long)num_tokens);
+    if (d_xq != nullptr) {
+        if (int rc = check_order(order)) return rc;
+        if (int rc = check_s_mode(s_mode)) return rc;
+        if (((uintptr_t)d_xq & 15u) != 0) return set_error(JQ_ERR_ALIGN, "Q8_1 blocks must be 16-byte aligned");
+    }
+    if (d_input == nullptr || d_weight == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (d_normed == nullptr && d_xq == nullptr && d_residual == nullptr)
+        return set_error(JQ_ERR_INVALID_ARG, "no output requested");
+    return launch_rms_norm_q8_1(static_cast<cudaStream_t>(stream), d_input, d_residual, d_weight, d_normed, d_xq, hidden_size,
+                                num_tokens, epsilon, order, s_mode);
+}
+
+int jq_swiglu_q8_1_device(void *stream, const float *d_gate, const float *d_up, float *d_mid, void *d_xq,
+                          int64_t intermediate_size, int64_t num_tokens, int order, int s_mode) {
+    if (intermediate_size < 0 || num_tokens < 0) return set_error(JQ_ERR_INVALID_ARG, "negative size");
+    if (intermediate_size == 0 || num_tokens == 0) return JQ_OK;
+    if (d_xq != nullptr) {
+        if (int rc = check_order(order)) return rc;
+        if (int rc = check_s_mode(s_mode)) return rc;
+        if (((uintptr_t)d_xq & 15u) != 0) return set_error(JQ_ERR_ALIGN, "Q8_1 blocks must be 16-byte aligned");
+    }
+    if (d_gate == nullptr || d_up == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if (d_mid == nullptr && d_xq == nullptr) return set_error(JQ_ERR_INVALID_ARG, "no output requested");
+    return launch_swiglu_q8_1(static_cast<cudaStream_t>(stream), d_gate, d_up, d_mid, d_xq, intermediate_size, num_tokens, order,
+                              s_mode);
+}
+
 int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                                    int64_t N, int64_t M, int order, int kernel) {
     if (int rc = check_mul_mat_shape(K, N, M)) return rc;

@@ -58,6 +58,11 @@ int *device_fault_ptr();
 int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t K, int64_t M,
                          int order, int s_mode);
 int launch_quantize_q4_0(cudaStream_t st, const float *d_w, void *d_wq, int64_t N, int64_t K);
+// producers.cu: RMSNorm (optionally with the residual add) and SwiGLU with the Q8_1 quantizer folded in
+int launch_rms_norm_q8_1(cudaStream_t st, float *d_input, float *d_residual, const float *d_weight, float *d_normed,
+                         void *d_xq, int64_t H, int64_t T, float epsilon, int order, int s_mode);
+int launch_swiglu_q8_1(cudaStream_t st, const float *d_gate, const float *d_up, float *d_mid, void *d_xq, int64_t I,
+                       int64_t T, int order, int s_mode);
 int launch_mmq_generic(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                        int64_t N, int64_t M, int order);
 int launch_block_sums(cudaStream_t st, const void *d_w, const void *d_xq, int32_t *d_sums, int64_t K,

@@ -1,0 +1,260 @@
+// Producers of the quantized linear's input: the two kernels that run just ahead of it in the
+// reference's transformer layer, with the Q8_1 quantizer folded in, so that the fp32 activation
+// never makes the round trip through HBM and the separate quantize launch disappears.
+//
+//   rms_norm_q8_1_kernel   replaces rms_norm_fused_add_kernel (reference
+//                          src/cuda/rms_norm_fused_add.cu:10-44, feeds the Q/K/V and gate/up
+//                          linears, src/engine/transformer_runner.cpp:208-216, 311-321) and
+//                          rms_norm_kernel (src/cuda/rms_norm.cu:12-41, feeds lm_head).
+//   swiglu_q8_1_kernel     replaces swiglu_silu_mul_kernel (src/cuda/swiglu.cu:5-15, feeds the
+//                          down linear, transformer_runner.cpp:324-328).
+//
+// Both compute the fp32 values with the reference's own operation order, so the fp32 outputs and
+// therefore the quantized blocks are bit-identical to "reference kernel, then quantize_q8_1".
+#include "jq_common.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int RMS_THREADS = 256;  // the reference's block size; the summation order depends on it
+
+// Block sum with the reference's tree (include/cuda_utils.cuh:19-27, 49-65): shuffle-down inside
+// each warp, one partial per warp through shared memory, shuffle-down over the partials in warp 0.
+// Only thread 0 holds the result.
+__device__ __forceinline__ float shuffle_down_sum(float v) {
+    v += __shfl_down_sync(0xFFFFFFFFu, v, 16);
+    v += __shfl_down_sync(0xFFFFFFFFu, v, 8);
+    v += __shfl_down_sync(0xFFFFFFFFu, v, 4);
+    v += __shfl_down_sync(0xFFFFFFFFu, v, 2);
+    v += __shfl_down_sync(0xFFFFFFFFu, v, 1);
+    return v;
+}
+
+__device__ __forceinline__ float block_sum_reference_order(float v, float *warp_partial) {
+    v = shuffle_down_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) warp_partial[warp] = v;
+    __syncthreads();
+    v = (threadIdx.x < ((blockDim.x + 31) >> 5)) ? warp_partial[lane] : 0.f;
+    if (warp == 0) v = shuffle_down_sum(v);
+    return v;
+}
+
+// One CTA per token.  Thread t owns elements t, t + blockDim, ... exactly as in the reference, so
+// the per-thread partial sums of squares, the block tree and rsqrtf give the same inverse RMS bit
+// for bit.  The normalised row is staged in shared memory and quantized from there warp by warp
+// (one warp per 128-value block, one lane four consecutive values: the quantizer's own mapping).
+__global__ void __launch_bounds__(RMS_THREADS)
+rms_norm_q8_1_kernel(float *__restrict__ input, float *__restrict__ residual, const float *__restrict__ weight,
+                     float *__restrict__ normed_out, uint8_t *__restrict__ xq, int H, int T, float epsilon, int n_super,
+                     int order, int s_mode) {
+    extern __shared__ __align__(16) float row[];  // H floats
+    __shared__ float warp_partial[32];
+    __shared__ float inverse_rms;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int token = blockIdx.x;
+    const int64_t base = (int64_t)token * H;
+
+    // z = input (+ residual) into shared memory; the additions are elementwise, so 16-byte accesses
+    // are free to use any thread-to-element mapping
+    const bool vec = (H & 3) == 0 && ((uintptr_t)(input + base) & 15u) == 0 &&
+                     (residual == nullptr || ((uintptr_t)(residual + base) & 15u) == 0);
+    if (vec) {
+        const float4 *in4 = reinterpret_cast<const float4 *>(input + base);
+        float4 *res4 = reinterpret_cast<float4 *>(residual != nullptr ? residual + base : nullptr);
+        float4 *row4 = reinterpret_cast<float4 *>(row);
+        for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+            float4 z = in4[i];
+            if (res4 != nullptr) {
+                const float4 r = res4[i];
+                z = make_float4(z.x + r.x, z.y + r.y, z.z + r.z, z.w + r.w);
+                res4[i] = z;
+            }
+            row4[i] = z;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float z = input[base + i];
+            if (residual != nullptr) {
+                z = z + residual[base + i];
+                residual[base + i] = z;
+            }
+            row[i] = z;
+        }
+    }
+    __syncthreads();
+    // sum of squares in the reference's order: thread t takes elements t, t + blockDim, ...
+    float sum_square = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float z = row[i];
+        sum_square = __fmaf_rn(z, z, sum_square);
+    }
+    sum_square = block_sum_reference_order(sum_square, warp_partial);
+    if (threadIdx.x == 0) inverse_rms = rsqrtf(sum_square / (float)H + epsilon);
+    __syncthreads();
+    const float inv = inverse_rms;
+    if (vec && ((uintptr_t)weight & 15u) == 0 && (normed_out == nullptr || ((uintptr_t)(normed_out + base) & 15u) == 0)) {
+        float4 *row4 = reinterpret_cast<float4 *>(row);
+        const float4 *w4 = reinterpret_cast<const float4 *>(weight);
+        float4 *out4 = reinterpret_cast<float4 *>(normed_out != nullptr ? normed_out + base : nullptr);
+        for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+            const float4 z = row4[i], w = __ldg(w4 + i);
+            const float4 y = make_float4(__fmul_rn(__fmul_rn(z.x, inv), w.x), __fmul_rn(__fmul_rn(z.y, inv), w.y),
+                                         __fmul_rn(__fmul_rn(z.z, inv), w.z), __fmul_rn(__fmul_rn(z.w, inv), w.w));
+            row4[i] = y;
+            if (out4 != nullptr) out4[i] = y;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float y = __fmul_rn(__fmul_rn(row[i], inv), weight[i]);
+            row[i] = y;
+            if (normed_out != nullptr) normed_out[base + i] = y;
+        }
+    }
+    if (xq == nullptr) return;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int ks = warp; ks < n_super; ks += n_warps) {
+        const float4 v = *reinterpret_cast<const float4 *>(row + ks * SUPER + lane * 4);
+        uint32_t ds;
+        const uint32_t q = quantize_group_q8_1(v, s_mode, &ds);
+        uint8_t *blk = xq + q8_block_index(ks, token, n_super, T, order) * Q8_BYTES;
+        reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+        if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
+    }
+}
+
+// silu(gate) * up with the reference's expression (swiglu.cu:5-7,13), one warp per 128-value block.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return __fmul_rn(__fmul_rn(g, 1.0f / (1.0f + expf(-g))), u);
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_q8_1_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ mid,
+                   uint8_t *__restrict__ xq, int64_t I, int64_t T, int64_t n_super, int order, int s_mode) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t total = T * n_super;
+    constexpr int U = 1;  // blocks in flight per warp (2 measured slower: 52 % against 60 % of HBM peak)
+    for (int64_t b0 = warp0; b0 < total; b0 += n_warps * U) {
+        float4 g[U], u[U];
+        int64_t off[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int64_t b = b0 + j * n_warps;
+            g[j] = u[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            off[j] = 0;
+            if (b < total) {
+                const int64_t t = b / n_super, ks = b - t * n_super;
+                off[j] = t * I + ks * SUPER + lane * 4;
+                g[j] = __ldg(reinterpret_cast<const float4 *>(gate + off[j]));
+                u[j] = __ldg(reinterpret_cast<const float4 *>(up + off[j]));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int64_t b = b0 + j * n_warps;  // uniform across the warp
+            if (b >= total) break;
+            const int64_t t = b / n_super, ks = b - t * n_super;
+            const float4 v = make_float4(silu_mul(g[j].x, u[j].x), silu_mul(g[j].y, u[j].y), silu_mul(g[j].z, u[j].z),
+                                         silu_mul(g[j].w, u[j].w));
+            if (mid != nullptr) *reinterpret_cast<float4 *>(mid + off[j]) = v;
+            if (xq != nullptr) {
+                uint32_t ds;
+                const uint32_t q = quantize_group_q8_1(v, s_mode, &ds);
+                uint8_t *blk = xq + q8_block_index(ks, t, n_super, T, order) * Q8_BYTES;
+                reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
+            }
+        }
+    }
+}
+
+// plain elementwise form for sizes that are not a multiple of 128 (no quantized output possible)
+__global__ void swiglu_plain_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ mid,
+                                    int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) mid[i] = silu_mul(gate[i], up[i]);
+}
+
+int launch_with_pdl(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return 0;
+}
+
+}  // namespace
+
+int launch_rms_norm_q8_1(cudaStream_t st, float *d_input, float *d_residual, const float *d_weight, float *d_normed,
+                         void *d_xq, int64_t H, int64_t T, float epsilon, int order, int s_mode) {
+    if (H <= 0 || T <= 0) return set_error(JQ_ERR_INVALID_ARG, "rms_norm: invalid hidden_size=%lld num_tokens=%lld", (long long)H, (long long)T);
+    if (d_xq != nullptr && H % SUPER != 0)
+        return set_error(JQ_ERR_UNSUPPORTED, "rms_norm with Q8_1 output needs hidden_size %% 128 == 0 (got %lld)", (long long)H);
+    if (H > (1 << 24) || T > 0x7FFFFFFF) return set_error(JQ_ERR_TOO_LARGE, "rms_norm: shape too large");
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem + 1024 > (size_t)caps.smem_optin)
+        return set_error(JQ_ERR_TOO_LARGE, "rms_norm: a row of %lld floats does not fit in shared memory", (long long)H);
+    static thread_local int attr_dev = -1;
+    static thread_local size_t attr_bytes = 0;
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && (attr_dev != dev || attr_bytes < smem)) {
+        JQ_CUDA_TRY(cudaFuncSetAttribute(rms_norm_q8_1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_dev = dev;
+        attr_bytes = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)T);
+    cfg.blockDim = dim3((unsigned)(H < RMS_THREADS ? H : RMS_THREADS));  // the reference's rule
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    launch_with_pdl(cfg, attr);
+    const int n_super = (int)(H / SUPER);
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, rms_norm_q8_1_kernel, d_input, d_residual, d_weight, d_normed,
+                                   static_cast<uint8_t *>(d_xq), (int)H, (int)T, epsilon, n_super, order, s_mode));
+    return JQ_OK;
+}
+
+int launch_swiglu_q8_1(cudaStream_t st, const float *d_gate, const float *d_up, float *d_mid, void *d_xq, int64_t I,
+                       int64_t T, int order, int s_mode) {
+    if (I <= 0 || T <= 0) return JQ_OK;
+    const bool aligned = I % SUPER == 0 && ((uintptr_t)d_gate & 15u) == 0 && ((uintptr_t)d_up & 15u) == 0 &&
+                         (d_mid == nullptr || ((uintptr_t)d_mid & 15u) == 0);
+    if (!aligned) {
+        if (d_xq != nullptr)
+            return set_error(JQ_ERR_UNSUPPORTED, "swiglu with Q8_1 output needs intermediate_size %% 128 == 0 and 16-byte aligned buffers");
+        if (d_mid == nullptr) return JQ_OK;
+        const int64_t n = I * T;
+        swiglu_plain_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(d_gate, d_up, d_mid, n);
+        JQ_CUDA_TRY(cudaGetLastError());
+        return JQ_OK;
+    }
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    const int64_t n_super = I / SUPER, total = T * n_super;
+    int64_t ctas = (total + 7) / 8;  // 8 warps, one block per warp and pass
+    if (ctas < 1) ctas = 1;
+    const int64_t cap = (int64_t)caps.sm_count * 8 * 4;
+    if (ctas > cap) ctas = cap;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    launch_with_pdl(cfg, attr);
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, swiglu_q8_1_kernel, d_gate, d_up, d_mid, static_cast<uint8_t *>(d_xq), I, T, n_super,
+                                   order, s_mode));
+    return JQ_OK;
+}
+
+}  // namespace jq

@@ -391,6 +391,70 @@ void jqo_linear_cpu_baseline(const uint8_t *wq, const float *x, uint8_t *xq_ws, 
     free(xf);
 }
 
+/* ------------------------------------------------------------------------------------------------
+ * Producers of the linear's input: RMSNorm (with or without the residual add) and SwiGLU.
+ *
+ * jqo_rms_norm follows rms_norm_fused_add_kernel (reference src/cuda/rms_norm_fused_add.cu:10-44) and
+ * rms_norm_kernel (src/cuda/rms_norm.cu:12-41) including the order of the sum of squares: thread t of a
+ * block of min(H, 256) threads adds z*z for i = t, t + block, ... with one fused multiply-add each
+ * (nvcc contracts `sum += z * z`), then block_reduce_sum (include/cuda_utils.cuh:19-27, 49-65): a
+ * shuffle-down tree inside each warp, one partial per warp, a second shuffle-down tree over the
+ * partials.  The only step that cannot be restated exactly on a CPU is rsqrtf (:35), a hardware
+ * approximation accurate to about 2 ulp; 1/sqrtf stands in for it, so fp32 results may differ from the
+ * device's in the last bits.
+ * residual may be NULL (plain RMSNorm); when given it is updated to z = input + residual. */
+static float shuffle_down_tree(float *v) { /* v[32], clobbered; returns lane 0's result */
+    for (int off = 16; off > 0; off >>= 1) {
+        for (int i = 0; i < off; ++i) v[i] = v[i] + v[i + off];
+    }
+    return v[0];
+}
+
+void jqo_rms_norm(const float *input, float *residual, const float *weight, float *normed, int64_t H,
+                  int64_t T, float epsilon) {
+    const int block = (int)(H < 256 ? H : 256);
+    const int n_warps = (block + 31) / 32;
+    for (int64_t t = 0; t < T; ++t) {
+        const float *in = input + t * H;
+        float *res = residual ? residual + t * H : NULL;
+        float partial[32 * 32];
+        memset(partial, 0, sizeof(partial));
+        for (int th = 0; th < block; ++th) {
+            float acc = 0.0f;
+            for (int64_t i = th; i < H; i += block) {
+                float z = in[i];
+                if (res) z = z + res[i];
+                acc = fmaf(z, z, acc);
+            }
+            partial[th] = acc;
+        }
+        float warp_partial[32];
+        memset(warp_partial, 0, sizeof(warp_partial));
+        for (int w = 0; w < n_warps; ++w) warp_partial[w] = shuffle_down_tree(partial + 32 * w);
+        const float sum_square = shuffle_down_tree(warp_partial);
+        const float inv = 1.0f / sqrtf(sum_square / (float)H + epsilon);
+        for (int64_t i = 0; i < H; ++i) {
+            float z = in[i];
+            if (res) {
+                z = z + res[i];
+            }
+            const float y = (z * inv) * weight[i];
+            if (res) res[i] = z;
+            normed[t * H + i] = y;
+        }
+    }
+}
+
+/* swiglu_silu_mul_kernel (src/cuda/swiglu.cu:5-15): mid = (g * (1 / (1 + expf(-g)))) * u.  The device's
+ * expf and this libm's may differ in the last bit. */
+void jqo_swiglu(const float *gate, const float *up, float *mid, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const float g = gate[i];
+        const float s = g * (1.0f / (1.0f + expf(-g)));
+        mid[i] = s * up[i];
+    }
+}
+
 /* Thread count for the OpenMP loops above (launchers such as torchrun export OMP_NUM_THREADS=1). */
 void jqo_set_num_threads(int n) {
 #ifdef _OPENMP

@@ -56,6 +56,10 @@ def lib() -> ctypes.CDLL:
         L.jqo_dequantize_q8_1.argtypes = [p, i64, i64, ci, p]
         L.jqo_mul_mat_deq_f64.argtypes = [p, p, i64, i64, i64, ci, p]
         L.jqo_linear_cpu_baseline.argtypes = [p, p, p, i64, i64, i64, ci, p]
+        L.jqo_rms_norm.argtypes = [p, p, p, p, i64, i64, ctypes.c_float]
+        L.jqo_rms_norm.restype = None
+        L.jqo_swiglu.argtypes = [p, p, p, i64]
+        L.jqo_swiglu.restype = None
         L.jqo_num_threads.restype = ci
         L.jqo_set_num_threads.argtypes = [ci]
         L.jqo_set_num_threads.restype = None
@@ -173,6 +177,26 @@ def linear_cpu_baseline(wq, x, k, n, m, s_mode=S_D_SUM_Q, y=None, ws=None) -> np
         ws = np.empty(m * (k // 128) * Q8_BYTES, dtype=np.uint8)
     lib().jqo_linear_cpu_baseline(_ptr(wq), _ptr(x), _ptr(ws), k, n, m, s_mode, _ptr(y))
     return y
+
+
+def rms_norm(x: np.ndarray, weight: np.ndarray, epsilon: float, residual: np.ndarray = None):
+    """RMSNorm of ``x`` ``[T, H]`` in the reference's operation order; with ``residual`` the fused-add form.
+    Returns ``(normed, new_residual_or_None)``."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    t, h = x.shape
+    res = None if residual is None else np.array(residual, dtype=np.float32, order="C", copy=True)
+    out = np.empty_like(x)
+    lib().jqo_rms_norm(_ptr(x), None if res is None else _ptr(res), _ptr(weight), _ptr(out), h, t, float(epsilon))
+    return out, res
+
+
+def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    gate = np.ascontiguousarray(gate, dtype=np.float32)
+    up = np.ascontiguousarray(up, dtype=np.float32)
+    out = np.empty_like(gate)
+    lib().jqo_swiglu(_ptr(gate), _ptr(up), _ptr(out), gate.size)
+    return out
 
 
 # ----------------------------------------------------------------------------- NumPy mirror
