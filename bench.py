@@ -506,6 +506,10 @@ def measure_extras(torch, capi, synth, dev, peaks):
     for Mc in (1, 128):
         out["cfg5_chain_M%d" % Mc] = bench_layer_chain(torch, capi, synth, dev, peaks, Mc)
 
+    # lm_head as a quantized GEMV: a 32000 x 4096 table (Llama-2 vocabulary), 73.7 MB
+    t = bench_linear(4096, 32000, 1, steps=100, fused=False)
+    b = synth.algorithmic_bytes(4096, 32000, 1, fused_quantize=False)
+    out["lm_head_q4_0_V32000_M1_mul_mat_only"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
     # the layer's own data flow around the linears, fp32 hand-offs against Q8_1 hand-offs
     for Mc in (1, 128):
         out["layer_dataflow_M%d" % Mc] = bench_layer_dataflow(torch, capi, synth, dev, peaks, Mc)

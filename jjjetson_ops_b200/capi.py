@@ -66,6 +66,7 @@ _SIGS = {
     "rms_norm_forward_device": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, ctypes.c_float]),
     "swiglu_silu_mul_launch_device": (None, [_vp, _vp, _vp, _vp, _ci]),
     "linear_q4_0_forward_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci]),
+    "lm_head_q4_0_forward_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci]),
     "jq_peer_alloc": (_ci, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
     "jq_peer_open": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "jq_peer_close": (_ci, [_vp]),

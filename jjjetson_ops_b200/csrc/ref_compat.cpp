@@ -82,3 +82,22 @@ extern "C" int linear_q4_0_forward_device(void *stream, const float *d_input, co
     report("linear_q4_0_forward_device", rc);
     return rc == JQ_OK ? 0 : -1;
 }
+
+// untied_lm_head_forward_device / tied_lm_head_forward_device (src/cuda/lm_head.cu:20-72) for a Q4_0 table:
+// logits[vocab] per token = W[vocab][hidden] . hidden, W stored as vocab rows of hidden / 32 Q4_0 blocks
+// (the tied layout, row = one token's embedding).  With d_hidden_q8_1 given, the final RMSNorm has already
+// written the blocks (jq_rms_norm_q8_1_device with a NULL residual) and d_hidden / d_ws are not used.
+extern "C" int lm_head_q4_0_forward_device(void *stream, const void *d_lm_head_q4_0, const float *d_hidden,
+                                           const void *d_hidden_q8_1, void *d_ws, float *d_logits, int hidden_size,
+                                           int vocab_size, int num_tokens) {
+    int rc;
+    if (d_hidden_q8_1 != nullptr) {
+        rc = jq_mul_mat_q4_0_q8_1_device(stream, d_lm_head_q4_0, d_hidden_q8_1, d_logits, hidden_size, vocab_size, num_tokens,
+                                         JQ_ORDER_COL_KSUPER);
+    } else {
+        rc = jq_linear_q4_0_device(stream, d_lm_head_q4_0, d_hidden, d_ws, d_logits, hidden_size, vocab_size, num_tokens,
+                                   JQ_S_D_SUM_Q);
+    }
+    report("lm_head_q4_0_forward_device", rc);
+    return rc == JQ_OK ? 0 : -1;
+}

@@ -1,0 +1,329 @@
+// Q4_0 tensors in the reference's weight-fixture format: reader and offline quantizer.
+//
+// Follows weight_loader_load_fixture (reference src/model/weight_loader.cpp:193-260, 330-350): the
+// same config.txt / manifest.txt grammar, the same limits in spirit (every dim positive, file size
+// must match the dims exactly), plus one more tensor type selected by the file's ".q4_0" suffix.
+#include <cuda_runtime.h>
+
+#include <cerrno>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include <sys/stat.h>
+
+#include "../../include/jq_b200.h"
+#include "../../include/jq_weights_io.h"
+
+namespace jq {
+int set_error(int status, const char *fmt, ...);
+}
+using jq::set_error;
+
+namespace {
+
+constexpr int kMaxNdim = 8;
+constexpr int kMaxTensors = 1 << 16;
+
+std::string trim(const std::string &s) {
+    size_t a = 0, b = s.size();
+    while (a < b && (s[a] == ' ' || s[a] == '\t' || s[a] == '\r' || s[a] == '\n')) ++a;
+    while (b > a && (s[b - 1] == ' ' || s[b - 1] == '\t' || s[b - 1] == '\r' || s[b - 1] == '\n')) --b;
+    return s.substr(a, b - a);
+}
+
+bool ends_with(const std::string &s, const char *suffix) {
+    const size_t n = std::strlen(suffix);
+    return s.size() >= n && s.compare(s.size() - n, n, suffix) == 0;
+}
+
+char *dup_c(const std::string &s) {
+    char *p = static_cast<char *>(std::malloc(s.size() + 1));
+    if (p) std::memcpy(p, s.c_str(), s.size() + 1);
+    return p;
+}
+
+bool read_file(const std::string &path, std::vector<char> *out) {
+    std::ifstream in(path, std::ios::binary | std::ios::ate);
+    if (!in.is_open()) return false;
+    const std::streamsize n = in.tellg();
+    if (n < 0) return false;
+    out->resize((size_t)n);
+    in.seekg(0);
+    return n == 0 || (bool)in.read(out->data(), n);
+}
+
+bool write_file(const std::string &path, const void *data, size_t n) {
+    std::ofstream o(path, std::ios::binary | std::ios::trunc);
+    if (!o.is_open()) return false;
+    if (n) o.write(static_cast<const char *>(data), (std::streamsize)n);
+    return (bool)o;
+}
+
+void free_tensor(jq_host_tensor *t) {
+    std::free(t->name);
+    std::free(t->data);
+    std::free(t->dims);
+    *t = jq_host_tensor{};
+}
+
+struct ManifestEntry {
+    std::string name, file;
+    std::vector<int64_t> dims;
+};
+
+int parse_manifest(const std::string &dir, std::vector<ManifestEntry> *entries) {
+    std::ifstream in(dir + "/manifest.txt");
+    if (!in.is_open()) return set_error(JQ_ERR_INVALID_ARG, "cannot open %s/manifest.txt", dir.c_str());
+    std::string line;
+    int lineno = 0;
+    while (std::getline(in, line)) {
+        ++lineno;
+        line = trim(line);
+        if (line.empty() || line[0] == '#') continue;
+        if ((int)entries->size() >= kMaxTensors) return set_error(JQ_ERR_TOO_LARGE, "manifest.txt: too many tensors");
+        std::istringstream iss(line);
+        ManifestEntry e;
+        int ndim = 0;
+        if (!(iss >> e.name >> ndim) || ndim <= 0 || ndim > kMaxNdim)
+            return set_error(JQ_ERR_SHAPE, "manifest.txt:%d: expected \"name ndim dims... file\"", lineno);
+        for (int i = 0; i < ndim; ++i) {
+            long long d = 0;
+            if (!(iss >> d) || d <= 0) return set_error(JQ_ERR_SHAPE, "manifest.txt:%d: bad dimension %d", lineno, i);
+            e.dims.push_back((int64_t)d);
+        }
+        if (!(iss >> e.file)) return set_error(JQ_ERR_SHAPE, "manifest.txt:%d: missing file name", lineno);
+        if (e.file.find("..") != std::string::npos || (!e.file.empty() && e.file[0] == '/'))
+            return set_error(JQ_ERR_INVALID_ARG, "manifest.txt:%d: file must be a path inside the fixture", lineno);
+        entries->push_back(std::move(e));
+    }
+    return JQ_OK;
+}
+
+int64_t numel_of(const std::vector<int64_t> &dims) {
+    int64_t n = 1;
+    for (int64_t d : dims) n *= d;
+    return n;
+}
+
+// bytes a tensor file must have, or -1 with the error recorded
+int64_t expected_bytes(const ManifestEntry &e, int *dtype) {
+    if (ends_with(e.file, ".q4_0")) {
+        *dtype = JQ_WEIGHT_Q4_0;
+        if (e.dims.size() != 2 || e.dims[1] % 32 != 0) {
+            set_error(JQ_ERR_SHAPE, "%s: a Q4_0 tensor needs dims [rows, K] with K %% 32 == 0", e.name.c_str());
+            return -1;
+        }
+        return (int64_t)jq_q4_0_bytes(e.dims[0], e.dims[1]);
+    }
+    *dtype = JQ_WEIGHT_F32;
+    return numel_of(e.dims) * (int64_t)sizeof(float);
+}
+
+bool config_lookup(const char *text, const char *key, double *value) {
+    if (!text || !key) return false;
+    std::istringstream in(text);
+    std::string line;
+    while (std::getline(in, line)) {
+        line = trim(line);
+        const size_t eq = line.find('=');
+        if (line.empty() || line[0] == '#' || eq == std::string::npos) continue;
+        if (trim(line.substr(0, eq)) != key) continue;
+        char *end = nullptr;
+        const std::string v = trim(line.substr(eq + 1));
+        errno = 0;
+        const double d = std::strtod(v.c_str(), &end);
+        if (end == v.c_str() || errno != 0) return false;
+        *value = d;
+        return true;
+    }
+    return false;
+}
+
+// in_features of a linear weight by its name, 0 when the tensor is not a linear weight
+int64_t linear_in_features(const std::string &name, const char *config) {
+    double hidden = 0, inter = 0, qh = 0, hd = 0, tied = 0;
+    config_lookup(config, "hidden_size", &hidden);
+    config_lookup(config, "intermediate_size", &inter);
+    config_lookup(config, "num_q_heads", &qh);
+    config_lookup(config, "head_dim", &hd);
+    config_lookup(config, "tie_word_embeddings", &tied);
+    for (const char *s : {".w_q", ".w_k", ".w_v", ".w_gate", ".w_up"}) {
+        if (ends_with(name, s)) return (int64_t)hidden;
+    }
+    if (ends_with(name, ".w_o")) return (int64_t)(qh * hd);
+    if (ends_with(name, ".w_down")) return (int64_t)inter;
+    if (name == "embed" && tied != 0) return (int64_t)hidden;  // the tied table doubles as lm_head: [vocab][hidden]
+    return 0;
+}
+
+}  // namespace
+
+extern "C" void jq_weight_set_destroy(jq_weight_set *set) {
+    if (!set) return;
+    for (int i = 0; i < set->num_tensors; ++i) free_tensor(&set->tensors[i]);
+    std::free(set->tensors);
+    std::free(set->config_text);
+    std::free(set);
+}
+
+extern "C" const jq_host_tensor *jq_weight_set_find(const jq_weight_set *set, const char *name) {
+    if (!set || !name) return nullptr;
+    for (int i = 0; i < set->num_tensors; ++i) {
+        if (std::strcmp(set->tensors[i].name, name) == 0) return &set->tensors[i];
+    }
+    return nullptr;
+}
+
+extern "C" int jq_weight_set_config_value(const jq_weight_set *set, const char *key, double *value) {
+    double v = 0;
+    if (!set || !value || !config_lookup(set->config_text, key, &v)) return 0;
+    *value = v;
+    return 1;
+}
+
+extern "C" int jq_weights_load_fixture(const char *dir, jq_weight_set **out) {
+    if (!out) return set_error(JQ_ERR_INVALID_ARG, "null out pointer");
+    *out = nullptr;
+    if (!dir) return set_error(JQ_ERR_INVALID_ARG, "null path");
+    std::vector<ManifestEntry> entries;
+    if (int rc = parse_manifest(dir, &entries)) return rc;
+    jq_weight_set *set = static_cast<jq_weight_set *>(std::calloc(1, sizeof(jq_weight_set)));
+    if (!set) return set_error(JQ_ERR_CUDA, "out of host memory");
+    std::vector<char> cfg;
+    read_file(std::string(dir) + "/config.txt", &cfg);  // optional, as for the reference's safetensors path
+    set->config_text = dup_c(std::string(cfg.begin(), cfg.end()));
+    set->tensors = static_cast<jq_host_tensor *>(std::calloc(entries.empty() ? 1 : entries.size(), sizeof(jq_host_tensor)));
+    if (!set->tensors || !set->config_text) {
+        jq_weight_set_destroy(set);
+        return set_error(JQ_ERR_CUDA, "out of host memory");
+    }
+    for (const ManifestEntry &e : entries) {
+        int dtype = 0;
+        const int64_t want = expected_bytes(e, &dtype);
+        if (want < 0) {
+            jq_weight_set_destroy(set);
+            return JQ_ERR_SHAPE;
+        }
+        std::vector<char> blob;
+        const std::string path = std::string(dir) + "/" + e.file;
+        if (!read_file(path, &blob)) {
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_INVALID_ARG, "cannot read %s", path.c_str());
+        }
+        if ((int64_t)blob.size() != want) {
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_SHAPE, "%s: %lld bytes on disk, %lld expected from the manifest dims", path.c_str(),
+                             (long long)blob.size(), (long long)want);
+        }
+        jq_host_tensor *t = &set->tensors[set->num_tensors];
+        t->name = dup_c(e.name);
+        t->dims = static_cast<int64_t *>(std::malloc(e.dims.size() * sizeof(int64_t)));
+        t->data = std::malloc(blob.empty() ? 1 : blob.size());
+        if (!t->name || !t->dims || !t->data) {
+            free_tensor(t);
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_CUDA, "out of host memory");
+        }
+        std::memcpy(t->dims, e.dims.data(), e.dims.size() * sizeof(int64_t));
+        std::memcpy(t->data, blob.data(), blob.size());
+        t->ndim = (int)e.dims.size();
+        t->dtype = dtype;
+        t->nbytes = blob.size();
+        ++set->num_tensors;
+    }
+    *out = set;
+    return JQ_OK;
+}
+
+extern "C" int jq_weights_quantize_fixture(const char *src_dir, const char *dst_dir, int *n_quantized) {
+    if (n_quantized) *n_quantized = 0;
+    if (!src_dir || !dst_dir) return set_error(JQ_ERR_INVALID_ARG, "null path");
+    jq_weight_set *set = nullptr;
+    if (int rc = jq_weights_load_fixture(src_dir, &set)) return rc;
+    if (mkdir(dst_dir, 0777) != 0 && errno != EEXIST) {
+        jq_weight_set_destroy(set);
+        return set_error(JQ_ERR_INVALID_ARG, "cannot create %s: %s", dst_dir, std::strerror(errno));
+    }
+    const std::string dst(dst_dir);
+    std::string manifest;
+    int rc = JQ_OK, converted = 0;
+    cudaStream_t stream = nullptr;
+    void *d_in = nullptr, *d_out = nullptr;
+    size_t cap_in = 0, cap_out = 0;
+    if (!write_file(dst + "/config.txt", set->config_text, std::strlen(set->config_text)))
+        rc = set_error(JQ_ERR_INVALID_ARG, "cannot write %s/config.txt", dst_dir);
+    for (int i = 0; rc == JQ_OK && i < set->num_tensors; ++i) {
+        const jq_host_tensor &t = set->tensors[i];
+        std::string base(t.name);
+        for (char &ch : base) {
+            if (ch == '.') ch = '_';  // the reference's file naming (tests/fixture_utils.py:95)
+        }
+        int64_t numel = 1;
+        for (int d = 0; d < t.ndim; ++d) numel *= t.dims[d];
+        const int64_t K = t.dtype == JQ_WEIGHT_F32 ? linear_in_features(t.name, set->config_text) : 0;
+        std::ostringstream line;
+        if (K > 0 && K % 32 == 0 && numel % K == 0) {
+            const int64_t rows = numel / K;
+            const size_t out_bytes = jq_q4_0_bytes(rows, K);
+            std::vector<char> host_out(out_bytes);
+            cudaError_t e = cudaSuccess;
+            if (!stream) e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+            if (e == cudaSuccess && t.nbytes > cap_in) {
+                cudaFree(d_in);
+                d_in = nullptr;
+                e = cudaMalloc(&d_in, t.nbytes);
+                cap_in = e == cudaSuccess ? t.nbytes : 0;
+            }
+            if (e == cudaSuccess && out_bytes > cap_out) {
+                cudaFree(d_out);
+                d_out = nullptr;
+                e = cudaMalloc(&d_out, out_bytes);
+                cap_out = e == cudaSuccess ? out_bytes : 0;
+            }
+            if (e == cudaSuccess) e = cudaMemcpyAsync(d_in, t.data, t.nbytes, cudaMemcpyHostToDevice, stream);
+            if (e != cudaSuccess) {
+                rc = set_error(JQ_ERR_CUDA, "%s: %s", t.name, cudaGetErrorString(e));
+                break;
+            }
+            rc = jq_quantize_q4_0_device(stream, static_cast<const float *>(d_in), d_out, rows, K);
+            if (rc != JQ_OK) break;
+            e = cudaMemcpyAsync(host_out.data(), d_out, out_bytes, cudaMemcpyDeviceToHost, stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+            if (e != cudaSuccess) {
+                rc = set_error(JQ_ERR_CUDA, "%s: %s", t.name, cudaGetErrorString(e));
+                break;
+            }
+            const std::string file = base + ".q4_0";
+            if (!write_file(dst + "/" + file, host_out.data(), out_bytes)) {
+                rc = set_error(JQ_ERR_INVALID_ARG, "cannot write %s/%s", dst_dir, file.c_str());
+                break;
+            }
+            line << t.name << " 2 " << rows << " " << K << " " << file;
+            ++converted;
+        } else {
+            const std::string file = base + (t.dtype == JQ_WEIGHT_Q4_0 ? ".q4_0" : ".f32");
+            if (!write_file(dst + "/" + file, t.data, t.nbytes)) {
+                rc = set_error(JQ_ERR_INVALID_ARG, "cannot write %s/%s", dst_dir, file.c_str());
+                break;
+            }
+            line << t.name << " " << t.ndim;
+            for (int d = 0; d < t.ndim; ++d) line << " " << t.dims[d];
+            line << " " << file;
+        }
+        manifest += line.str() + "\n";
+    }
+    if (rc == JQ_OK && !write_file(dst + "/manifest.txt", manifest.data(), manifest.size()))
+        rc = set_error(JQ_ERR_INVALID_ARG, "cannot write %s/manifest.txt", dst_dir);
+    cudaFree(d_in);
+    cudaFree(d_out);
+    if (stream) cudaStreamDestroy(stream);
+    jq_weight_set_destroy(set);
+    if (n_quantized) *n_quantized = converted;
+    return rc;
+}

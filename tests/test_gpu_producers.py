@@ -264,3 +264,32 @@ def test_layer_dataflow_with_folded_quantizers(native_lib, oracle, cuda_device):
         assert torch.equal(gate, gate_b) and torch.equal(up, up_b)
         assert torch.equal(out_a, out_b)
         assert torch.isfinite(out_b).all()
+
+
+def test_lm_head_q4_0_after_final_norm(native_lib, oracle, cuda_device):
+    """Final RMSNorm (no residual) -> logits over a Q4_0 table, fp32 hand-off and Q8_1 hand-off: same logits,
+    within 1e-3 of dequantise-then-matmul."""
+    import torch
+
+    c, O = native_lib, oracle
+    rng = np.random.default_rng(21)
+    H, V = 512, 1000  # a vocabulary that is not a multiple of 32
+    table = (rng.standard_normal((V, H)) * 0.05).astype(np.float32)
+    tq = O.quantize_q4_0(table)
+    dt = torch.from_numpy(tq).to(cuda_device)
+    wn = torch.from_numpy((1 + 0.1 * rng.standard_normal(H)).astype(np.float32)).to(cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    for T in (1, 3, 17):
+        h = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(cuda_device)
+        normed = torch.empty_like(h)
+        hq = c.rms_norm_q8_1(h, wn, 1e-6, normed=normed)
+        ws = torch.empty(c.q8_1_bytes(H, T) + 16, dtype=torch.uint8, device=cuda_device)
+        la = torch.empty((T, V), dtype=torch.float32, device=cuda_device)
+        lb = torch.empty((T, V), dtype=torch.float32, device=cuda_device)
+        assert c.lib().lm_head_q4_0_forward_device(st, dt.data_ptr(), normed.data_ptr(), None, ws.data_ptr(), la.data_ptr(), H, V, T) == 0
+        assert c.lib().lm_head_q4_0_forward_device(st, dt.data_ptr(), None, hq.data_ptr(), None, lb.data_ptr(), H, V, T) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(la, lb)
+        xq = O.quantize_q8_1(normed.cpu().numpy(), O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+        assert np.array_equal(xq, hq.cpu().numpy()[: xq.size])
+        assert O.err_max_rel(lb.cpu().numpy(), O.mul_mat_deq_f64(tq, xq, H, V, T)) <= 1e-3
