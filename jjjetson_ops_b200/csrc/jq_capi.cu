@@ -616,9 +616,7 @@ struct jq_weights {
     cudaStream_t stream = nullptr;
     void *d_x = nullptr, *d_ws = nullptr, *d_y = nullptr;
     int64_t m_cap = 0;
-    // last host buffers seen and their device aliases (non-null when the buffer is pinned and mapped)
-    const void *seen_x = nullptr;
-    const void *seen_y = nullptr;
+    // device aliases of the current call's host buffers (non-null when the buffer is pinned and mapped)
     const float *x_alias = nullptr;
     float *y_alias = nullptr;
     // completion ticket in pinned, mapped host memory (written by the copy kernel, polled by the host)
@@ -699,14 +697,10 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
         JQ_CUDA_TRY(cudaMalloc(&w->d_y, (size_t)M * w->N * sizeof(float) + 16));
         w->m_cap = M;
     }
-    if (x != w->seen_x) {
-        w->seen_x = x;
-        w->x_alias = static_cast<const float *>(mapped_alias(x));
-    }
-    if (y != w->seen_y) {
-        w->seen_y = y;
-        w->y_alias = static_cast<float *>(mapped_alias(y));
-    }
+    // Asked on every call: a buffer freed and allocated again may come back at the same address
+    // with a different mapping, and a stale alias would be a wild device pointer.
+    w->x_alias = static_cast<const float *>(mapped_alias(x));
+    w->y_alias = static_cast<float *>(mapped_alias(y));
     const size_t y_count = (size_t)M * w->N;
     // Small decode batches from pinned, mapped host memory skip the copy engines: the quantizer
     // reads the activations over the bus itself and a copy kernel writes the result back.
@@ -751,15 +745,15 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
 
     bool launched = false;
     if (ticketed) {
-        const bool same = w->graph_x == x && w->graph_y == y && w->graph_m == M && w->graph_s_mode == s_mode;
+        const bool same = w->graph_x == w->x_alias && w->graph_y == w->y_alias && w->graph_m == M && w->graph_s_mode == s_mode;
         if (!same) {
             if (w->graph) {
                 JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
                 cudaGraphExecDestroy(w->graph);
                 w->graph = nullptr;
             }
-            w->graph_x = x;
-            w->graph_y = y;
+            w->graph_x = w->x_alias;  // the recorded launches hold the device aliases, so they are the key
+            w->graph_y = w->y_alias;
             w->graph_m = M;
             w->graph_s_mode = s_mode;
             w->graph_hits = 0;
@@ -782,21 +776,32 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
         }
     }
     unsigned expect = 0;
-    if (ticketed) expect = ++w->ticket;  // the flag counts completed ticketed calls
+    if (ticketed) expect = w->ticket + 1;  // the flag counts completed ticketed calls
     if (!launched) {
-        if (int rc = enqueue(0u)) return rc;
+        if (int rc = enqueue(0u)) {
+            // part of the call may be queued: drain it and take the count as it stands, so that the next
+            // call's expectation matches the device again
+            cudaStreamSynchronize(w->stream);
+            (void)cudaGetLastError();
+            if (w->h_done) w->ticket = *static_cast<volatile unsigned *>(w->h_done);
+            return rc;
+        }
     }
+    if (ticketed) w->ticket = expect;
     bool polled = false;
     if (ticketed) {
         volatile unsigned *h = w->h_done;
         for (long spin = 0; spin < 20000000L; ++spin) {
-            if (*h == expect) {
+            if ((int)(*h - expect) >= 0) {
                 polled = true;
                 break;
             }
         }
     }
-    if (!polled) JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+    if (!polled) {
+        JQ_CUDA_TRY(cudaStreamSynchronize(w->stream));
+        if (ticketed) w->ticket = *static_cast<volatile unsigned *>(w->h_done);  // resynchronise after a slow call
+    }
     return JQ_OK;
 }
 

@@ -194,6 +194,13 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
     named_bar_sync(1, NW * 32);
 }
 
+// unsigned bytes of a times signed bytes of b, accumulated in c
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // ------------------------------------------------------------------------------------------------
 // dp4a variant: one warp per weight row, one lane per 128-value slice (four Q4_0 blocks = 72
 // bytes, read as nine conflict-free 8-byte shared loads), activations of that slice in registers.
@@ -260,7 +267,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                 const uint32_t dsv[4] = {ds.x, ds.y, ds.z, ds.w};
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    xd[i][m][g] = half_bits_to_float(dsv[g] & 0xFFFFu);
+                    xd[i][m][g] = 0.0625f * half_bits_to_float(dsv[g] & 0xFFFFu);  // d8 / 16, exact
                     xms[i][m][g] = -8.0f * half_bits_to_float(dsv[g] >> 16);
                 }
 #pragma unroll
@@ -283,18 +290,23 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     int64_t r_begin, r_end;
     cta_row_range(p.N, &r_begin, &r_end);
     const int R = p.rows_per_stage;
-    const int n_chunks = (int)((r_end - r_begin + R - 1) / R);
+    const int rows_cta_total = (int)(r_end - r_begin);
+    const int n_chunks = (rows_cta_total + R - 1) / R;
     const uint32_t ring_addr = smem_u32(ring);
+    const bool tracing = p.trace != nullptr && threadIdx.x == 0;
 
+    // Ring position, phase parity and row offset advance incrementally: with one row per warp and
+    // stage, anything computed per stage is paid per row.
+    int s = 0;
+    uint32_t parity = 0;
+    uint32_t stage = ring_addr;
+    int row0 = 0;  // first row of the stage, relative to r_begin
     for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % p.stages;
-        const uint32_t round = (uint32_t)(c / p.stages);
-        if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
-        if (threadIdx.x == 0 && c == 0) trace_stamp(p, 5);  // first stage landed
-        if (threadIdx.x == 0 && c == n_chunks - 1) trace_stamp(p, 6);  // last stage landed
-        const uint32_t stage = ring_addr + (uint32_t)s * p.stage_bytes;
-        const int64_t r0 = r_begin + (int64_t)c * R;
-        const int rows = (int)min((int64_t)R, r_end - r0);
+        if (!mbar_wait_bounded(&full[s], parity, p.fault)) return;
+        if (tracing && c == 0) trace_stamp(p, 5);  // first stage landed
+        if (tracing && c == n_chunks - 1) trace_stamp(p, 6);  // last stage landed
+        const int rows = min(R, rows_cta_total - row0);
+        const int64_t r0 = r_begin + row0;
 
         for (int r = warp; r < rows; r += NW) {
             const uint32_t rowp = stage + (uint32_t)r * p.row_bytes;
@@ -328,21 +340,24 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                             for (int t = 0; t < 4; ++t) q[t] = wv[w0 + 1 + t];
                         }
                         const float d4 = half_bits_to_float(dbits);
-                        int sumi[M_T];
+                        // low nibbles as they are, high nibbles left in place (16 x their value, unsigned
+                        // bytes): 16 * sumi = 16 * lo + hi16 exactly, and xd carries d8 / 16
+                        int lo_acc[M_T], hi_acc[M_T];
 #pragma unroll
-                        for (int m = 0; m < M_T; ++m) sumi[m] = 0;
+                        for (int m = 0; m < M_T; ++m) lo_acc[m] = hi_acc[m] = 0;
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
-                            const int lo = (int)(q[t] & MASK4), hi = (int)((q[t] >> 4) & MASK4);
+                            const uint32_t lo = q[t] & MASK4, hi16 = q[t] & (MASK4 << 4);
 #pragma unroll
                             for (int m = 0; m < M_T; ++m) {
-                                sumi[m] = __dp4a(lo, xq[i][m][8 * b + t], sumi[m]);
-                                sumi[m] = __dp4a(hi, xq[i][m][8 * b + t + 4], sumi[m]);
+                                lo_acc[m] = dp4a_u8s8(lo, xq[i][m][8 * b + t], lo_acc[m]);
+                                hi_acc[m] = dp4a_u8s8(hi16, xq[i][m][8 * b + t + 4], hi_acc[m]);
                             }
                         }
 #pragma unroll
                         for (int m = 0; m < M_T; ++m) {
-                            acc[m] = fmaf(d4, fmaf((float)sumi[m], xd[i][m][b], xms[i][m][b]), acc[m]);
+                            const int s16 = lo_acc[m] * 16 + hi_acc[m];
+                            acc[m] = fmaf(d4, fmaf((float)s16, xd[i][m][b], xms[i][m][b]), acc[m]);
                         }
                     }
                 }
@@ -363,6 +378,13 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+        row0 += R;
+        stage += p.stage_bytes;
+        if (++s == p.stages) {
+            s = 0;
+            parity ^= 1u;
+            stage = ring_addr;
+        }
     }
     if (threadIdx.x == 0) trace_stamp(p, 7);  // warp 0 done
 

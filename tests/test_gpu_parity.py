@@ -396,3 +396,45 @@ def test_device_hw_info(env):
     info = env.c.query_device_hw_info(0)
     assert info["sm_count"] > 0 and info["cc_major"] >= 10, info
     assert info["peak_dram_gbs"] > 1000 and info["peak_int8_dense_tops"] > 1000
+
+
+def test_show_device_info_prints_the_reference_line_format(native_lib, cuda_device, capsys):
+    from jjjetson_ops_b200 import show_device_info
+
+    assert show_device_info.main(["0"]) == 0
+    out = capsys.readouterr().out.strip().splitlines()
+    assert all(line.startswith("[DeviceHwInfo] ") for line in out)
+    keys = {line.split("] ", 1)[1].split(":", 1)[0] for line in out}
+    for k in ("device_id", "name", "compute_capability", "sm_count", "peak_dram_theoretical", "peak_tc_int8_dense_tops_nominal"):
+        assert k in keys
+    assert show_device_info.main(["4096"]) == 1  # no such device: message on stderr, status 1, no exit()
+
+
+def test_trace_stamps_of_a_decode_launch_are_ordered(native_lib, cuda_device):
+    """jq_trace_enable: the next launch of a streaming GEMV writes eight increasing time stamps per CTA."""
+    import torch
+
+    c = native_lib
+    K, N = 1024, 2048
+    rng = np.random.default_rng(3)
+    w = torch.from_numpy(rng.integers(0, 256, size=c.q4_0_bytes(N, K), dtype=np.uint8)).to(cuda_device)
+    blocks = w.view(N, K // 32, 18)
+    blocks[:, :, 0] = 0
+    blocks[:, :, 1] = 0x20
+    x = torch.from_numpy(rng.standard_normal((1, K)).astype(np.float32)).to(cuda_device)
+    ref = c.linear_q4_0(w, x, N)
+    buf = torch.zeros(2 * 512 * 8, dtype=torch.int64, device=cuda_device)
+    c.check(c.lib().jq_trace_enable(buf.data_ptr(), 2))
+    y = c.linear_q4_0(w, x, N)
+    torch.cuda.synchronize()
+    c.check(c.lib().jq_trace_enable(None, 0))
+    assert torch.equal(y, ref)  # tracing does not change the result
+    t = buf.cpu().numpy()[: 512 * 8].reshape(512, 8)
+    live = t[t[:, 0] > 0]
+    assert len(live) >= 1 and len(live) <= 296
+    # start <= predecessor finished <= activations staged <= first stage seen <= last stage seen <= done
+    for a, b in ((0, 3), (3, 4), (4, 5), (5, 6), (6, 7)):
+        assert (live[:, a] <= live[:, b]).all(), (a, b)
+    assert (buf.cpu().numpy()[512 * 8:] == 0).all()  # only one launch happened
+    y2 = c.linear_q4_0(w, x, N)  # tracing is off again
+    assert torch.equal(y2, ref)
