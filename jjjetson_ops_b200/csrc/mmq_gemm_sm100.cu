@@ -32,16 +32,23 @@ namespace jq {
 
 namespace {
 
-constexpr int GM_BN = 128;                 // weight rows per CTA
-constexpr int GM_BM = 128;                 // activation columns per CTA
-constexpr int GM_THREADS = 256;            // 8 warps: 2 along rows x 4 along columns
+// The CTA tile is (32 * RT weight rows) x (32 * CT activation columns): 8 warps, 2 along rows x 4
+// along columns, each owning RT m16 row tiles and CT n8 column tiles.  RT = CT = 4 is the 128 x 128
+// tile described above; RT = CT = 2 (64 x 64, two CTAs per SM) serves shapes whose 128 x 128 tiles
+// would not fill the SMs (a 4096 -> 4096 projection at M = 128 is 32 of those, but 128 of these).
+constexpr int GM_THREADS = 256;
 constexpr int GM_STAGES = 3;
 constexpr int GM_KCHUNK = 256;             // values of K per pipeline stage
 constexpr int GM_W_PITCH = 144;            // bytes per weight row per chunk (8 blocks)
 constexpr int GM_X_PITCH = 304;            // 2 x 144 bytes per column per chunk + 16 (bank spread)
-constexpr int GM_W_BYTES = GM_BN * GM_W_PITCH;
-constexpr int GM_X_BYTES = GM_BM * GM_X_PITCH;
-constexpr int GM_STAGE_BYTES = GM_W_BYTES + GM_X_BYTES;
+template <int RT, int CT>
+struct GemmTile {
+    static constexpr int BN = 32 * RT, BM = 32 * CT;
+    static constexpr int W_BYTES = BN * GM_W_PITCH, X_BYTES = BM * GM_X_PITCH;
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    static constexpr int SMEM = GM_STAGES * STAGE_BYTES;
+    static constexpr int MIN_CTAS = SMEM <= 100 * 1024 ? 2 : 1;
+};
 constexpr uint32_t MASK4 = 0x0F0F0F0Fu;
 constexpr int MAGIC_I = 0x4B400000;        // bit pattern of 1.5 * 2^23
 constexpr float MAGIC_F = 12582912.0f;
@@ -83,9 +90,11 @@ struct GemmParams {
     uint32_t row_bytes;  // K / 32 * 18
 };
 
+template <int RT, int CT>
 __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_addr, int chunk, int64_t n0, int64_t m0,
                                            int tid) {
-    // weights: 128 rows x 9 sixteen-byte units
+    constexpr int GM_BN = GemmTile<RT, CT>::BN, GM_BM = GemmTile<RT, CT>::BM, GM_W_BYTES = GemmTile<RT, CT>::W_BYTES;
+    // weights: BN rows x 9 sixteen-byte units
 #pragma unroll
     for (int i = 0; i < (GM_BN * 9 + GM_THREADS - 1) / GM_THREADS; ++i) {
         const int idx = tid + i * GM_THREADS;
@@ -96,11 +105,12 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
                         p.w + n * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16);
         }
     }
-    // activations: 128 columns x 2 blocks x 9 units
+    // activations: BM columns x 2 blocks x 9 units
     const uint32_t xs = stage_addr + GM_W_BYTES;
 #pragma unroll
-    for (int i = 0; i < GM_BM * 18 / GM_THREADS; ++i) {
+    for (int i = 0; i < (GM_BM * 18 + GM_THREADS - 1) / GM_THREADS; ++i) {
         const int idx = tid + i * GM_THREADS;
+        if (idx >= GM_BM * 18) break;
         const int col = idx / 18, part = idx - col * 18;
         const int ks = part / 9, unit = part - ks * 9;
         const int64_t m = min(m0 + col, p.M - 1);
@@ -109,26 +119,29 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
     }
 }
 
-__global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const GemmParams p) {
+template <int RT, int CT>
+__global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q4_0_q8_1_mma_kernel(const GemmParams p) {
+    constexpr int GM_BN = GemmTile<RT, CT>::BN, GM_BM = GemmTile<RT, CT>::BM, GM_W_BYTES = GemmTile<RT, CT>::W_BYTES;
+    constexpr int GM_STAGE_BYTES = GemmTile<RT, CT>::STAGE_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int wn = warp & 1, wm = warp >> 1;  // warp tile: rows wn*64.., columns wm*32..
+    const int wn = warp & 1, wm = warp >> 1;  // warp tile: rows wn * 16 * RT .., columns wm * 8 * CT ..
     const int64_t n0 = (int64_t)blockIdx.x * GM_BN, m0 = (int64_t)blockIdx.y * GM_BM;
     const int n_chunks = p.K / GM_KCHUNK;
 
-    float acc[4][4][4];  // [row tile][column tile][c0..c3]
+    float acc[RT][CT][4];  // [row tile][column tile][c0..c3]
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RT; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < CT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
 
 #pragma unroll
     for (int s = 0; s < GM_STAGES - 1; ++s) {
-        if (s < n_chunks) load_stage(p, smem_base + s * GM_STAGE_BYTES, s, n0, m0, tid);
+        if (s < n_chunks) load_stage<RT, CT>(p, smem_base + s * GM_STAGE_BYTES, s, n0, m0, tid);
         cp_async_commit();
     }
 
@@ -139,24 +152,24 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
         __syncthreads();  // chunk c has landed for everyone; stage (c-1)%S is free again
         {
             const int nc = c + GM_STAGES - 1;
-            if (nc < n_chunks) load_stage(p, smem_base + (nc % GM_STAGES) * GM_STAGE_BYTES, nc, n0, m0, tid);
+            if (nc < n_chunks) load_stage<RT, CT>(p, smem_base + (nc % GM_STAGES) * GM_STAGE_BYTES, nc, n0, m0, tid);
             cp_async_commit();
         }
         const uint32_t ws = smem_base + (c % GM_STAGES) * GM_STAGE_BYTES;
         const uint32_t xs = ws + GM_W_BYTES;
-        const uint32_t w_lane = ws + (wn * 64 + g) * GM_W_PITCH + 4 * t;
-        const uint32_t x_frag = xs + (wm * 32 + g) * GM_X_PITCH + Q8_QS_OFFSET + 4 * t;
-        const uint32_t x_scale = xs + (wm * 32 + 2 * t) * GM_X_PITCH;
+        const uint32_t w_lane = ws + (wn * 16 * RT + g) * GM_W_PITCH + 4 * t;
+        const uint32_t x_frag = xs + (wm * 8 * CT + g) * GM_X_PITCH + Q8_QS_OFFSET + 4 * t;
+        const uint32_t x_scale = xs + (wm * 8 * CT + 2 * t) * GM_X_PITCH;
 
 #pragma unroll
         for (int jp = 0; jp < 4; ++jp) {  // pairs of blocks (even, odd): the pair starts 4-byte aligned
             const int ks = jp >> 1;       // which of the chunk's two activation blocks
             const int sub_e = (2 * jp) & 3, sub_o = sub_e + 1;
-            // activation fragments and scales of the two blocks, 4 column tiles
-            uint32_t be[4][2], bo[4][2];
-            float2 de[4], ce[4], d_o[4], co[4];
+            // activation fragments and scales of the two blocks, CT column tiles
+            uint32_t be[CT][2], bo[CT][2];
+            float2 de[CT], ce[CT], d_o[CT], co[CT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < CT; ++j) {
                 const uint32_t xb = x_frag + j * 8 * GM_X_PITCH + ks * Q8_BYTES;
                 be[j][0] = lds_u32(xb + sub_e * QK);
                 be[j][1] = lds_u32(xb + sub_e * QK + 16);
@@ -171,7 +184,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
                 co[j] = make_float2(-MAGIC_F * d_o[j].x, -MAGIC_F * d_o[j].y);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < RT; ++i) {
                 uint32_t a_e[4], a_o[4];
                 float d4e[2], d4o[2];
 #pragma unroll
@@ -188,7 +201,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
                     d4o[h] = half_bits_to_float(lds_u16(prd + Q4_BYTES));
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < CT; ++j) {
                     int c4[4];
                     mma_u8s8_16832(c4, a_e, be[j], magic4);
                     float2 lo = ffma2(make_float2(__int_as_float(c4[0]), __int_as_float(c4[1])), de[j], ce[j]);
@@ -210,27 +223,27 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
 
         // zero-point term of the chunk's 8 blocks: acc += (-8 * d4)[16 x 8] * s8[8 x 8] per tile pair
         {
-            uint32_t sfrag[4];
+            uint32_t sfrag[CT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < CT; ++j) {
                 // B fragment: k = 2t, 2t+1 (blocks of the chunk), column g
-                const uint32_t sb = xs + (wm * 32 + j * 8 + g) * GM_X_PITCH + ((2 * t) >> 2) * Q8_BYTES + 4 * ((2 * t) & 3);
+                const uint32_t sb = xs + (wm * 8 * CT + j * 8 + g) * GM_X_PITCH + ((2 * t) >> 2) * Q8_BYTES + 4 * ((2 * t) & 3);
                 const uint2 ds = lds_v2(sb);
                 sfrag[j] = (ds.x >> 16) | (ds.y & 0xFFFF0000u);  // (s of block 2t, s of block 2t+1)
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < RT; ++i) {
                 uint32_t dfrag[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint32_t pr = ws + (wn * 64 + i * 16 + h * 8 + g) * GM_W_PITCH + (2 * t) * Q4_BYTES;
+                    const uint32_t pr = ws + (wn * 16 * RT + i * 16 + h * 8 + g) * GM_W_PITCH + (2 * t) * Q4_BYTES;
                     const uint32_t lo = lds_u16(pr), hi = lds_u16(pr + Q4_BYTES);
                     const __half2 d2 = __halves2half2(__ushort_as_half((unsigned short)lo), __ushort_as_half((unsigned short)hi));
                     const __half2 scaled = __hmul2(d2, __float2half2_rn(-8.0f));  // exact: a power of two
                     dfrag[h] = *reinterpret_cast<const uint32_t *>(&scaled);
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) mma_f16_1688(acc[i][j], dfrag, sfrag[j]);
+                for (int j = 0; j < CT; ++j) mma_f16_1688(acc[i][j], dfrag, sfrag[j]);
             }
         }
     }
@@ -238,11 +251,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
 
     // y[m * N + n]: thread owns rows g, g+8 and columns 2t, 2t+1 of each 16 x 8 tile
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < RT; ++i) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t n = n0 + wn * 64 + i * 16 + g;
-            const int64_t m = m0 + wm * 32 + j * 8 + 2 * t;
+        for (int j = 0; j < CT; ++j) {
+            const int64_t n = n0 + wn * 16 * RT + i * 16 + g;
+            const int64_t m = m0 + wm * 8 * CT + j * 8 + 2 * t;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int64_t nn = n + (e >> 1) * 8, mm = m + (e & 1);
@@ -254,14 +267,36 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_q4_0_q8_1_mma_kernel(const
 
 }  // namespace
 
+namespace {
+
+template <int RT, int CT>
+int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
+    using Tile = GemmTile<RT, CT>;
+    const int64_t gx = (p.N + Tile::BN - 1) / Tile::BN, gy = (p.M + Tile::BM - 1) / Tile::BM;
+    if (gy > 65535) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
+    static thread_local int attr_done_dev = -1;
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (attr_done_dev != dev) {
+        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_mma_kernel<RT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile::SMEM));
+        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_mma_kernel<RT, CT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+        attr_done_dev = dev;
+    }
+    gemm_q4_0_q8_1_mma_kernel<RT, CT><<<dim3((unsigned)gx, (unsigned)gy), GM_THREADS, Tile::SMEM, st>>>(p);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+}  // namespace
+
 int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
                     int order) {
     if (K % GM_KCHUNK != 0) return set_error(JQ_ERR_UNSUPPORTED, "tensor-core GEMM needs K %% 256 == 0 (K = %lld)", (long long)K);
     if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
         return set_error(JQ_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands");
     if (N == 0 || M == 0) return JQ_OK;
-    const int64_t gx = (N + GM_BN - 1) / GM_BN, gy = (M + GM_BM - 1) / GM_BM;
-    if (gy > 65535 || K > (1 << 24)) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
+    if (K > (1 << 24)) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
     GemmParams p{};
     p.w = static_cast<const uint8_t *>(d_w);
     p.xq = static_cast<const uint8_t *>(d_xq);
@@ -272,17 +307,12 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.order = order;
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
-    constexpr int smem = GM_STAGES * GM_STAGE_BYTES;
-    static thread_local int attr_done_dev = -1;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (attr_done_dev != dev) {
-        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done_dev = dev;
-    }
-    gemm_q4_0_q8_1_mma_kernel<<<dim3((unsigned)gx, (unsigned)gy), GM_THREADS, smem, st>>>(p);
-    JQ_CUDA_TRY(cudaGetLastError());
-    return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    // 128 x 128 tiles unless they would leave a good part of the SMs without work
+    const int64_t big_tiles = ((N + 127) / 128) * ((M + 127) / 128);
+    if (big_tiles * 5 < (int64_t)caps.sm_count * 4) return run_gemm_mma<2, 2>(st, p);
+    return run_gemm_mma<4, 4>(st, p);
 }
 
 }  // namespace jq
