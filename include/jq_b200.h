@@ -158,17 +158,20 @@ int jq_swiglu_q8_1_device(void *stream, const float *d_gate, const float *d_up, 
 /* ---- N-sharded decode (no counterpart in the reference, which is single-GPU) -------------------
  * One process per GPU owns a contiguous band of weight rows.  jq_linear_q4_0_allgather_device
  * runs this rank's quantize + multiply (M <= 2) and writes its band of the output directly into
- * every rank's [M][N_total] buffer through peer-mapped pointers (plain stores over NVLink), then
- * raises its arrival flag on every rank.  The kernel does not wait for the other ranks at its end:
- * whoever consumes the gathered output waits for the flags - the next sharded layer by passing
+ * every rank's [M][N_total] buffer through peer-mapped pointers (plain stores over NVLink); each
+ * CTA then adds its share to the arrival count that every rank keeps for this rank (one
+ * system-scope release-add per CTA and peer; a whole all-gather adds 65536).  The kernel does not
+ * wait for the other ranks at its end:
+ * whoever consumes the gathered output waits for the counts - the next sharded layer by passing
  * wait_epoch (its prologue then waits, while its weight stream is already running), anything
  * else by queueing jq_allgather_wait_device first.  All ranks must make the same sequence of calls.
  *   y_peers[q]     : rank q's pair of output buffers as mapped on this device (q == rank: local);
  *                    the second buffer starts y_stride_bytes after the first
- *   flag_peers[q]  : rank q's uint32[world] flag array, likewise; zero before the first call
+ *   flag_peers[q]  : rank q's uint32[world] arrival counts, likewise; zero before the first call
  *   d_epoch        : a local uint32, zero before the first call: how many all-gathers this rank has
- *                    finished.  Call number e = *d_epoch + 1 stores into buffer (e & 1), raises the
- *                    flags to e and sets *d_epoch = e (on the device, so CUDA graphs can be replayed)
+ *                    finished.  Call number e = *d_epoch + 1 stores into buffer (e & 1), brings the
+ *                    counts to e * 65536 (mod 2^32) and sets *d_epoch = e (on the device, so CUDA
+ *                    graphs can be replayed)
  *   wait_previous  : non-zero: the activations are the output of all-gather number *d_epoch; the
  *                    kernel waits for all its bands before reading them
  *   d_counter      : a local int, zero before the first call
@@ -189,8 +192,8 @@ int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *
                                     void *const *flag_peers, int world, int rank, int64_t n_offset,
                                     int64_t N_total, size_t y_stride_bytes, int wait_previous,
                                     unsigned *d_epoch, int *d_counter);
-/* Blocks the stream (bounded) until all `world` flags at d_flags have reached *d_epoch, i.e. until
- * the bands of this rank's latest all-gather have arrived from every rank. */
+/* Blocks the stream (bounded) until all `world` counts at d_flags have reached *d_epoch * 65536,
+ * i.e. until the bands of this rank's latest all-gather have arrived from every rank. */
 int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const unsigned *d_epoch);
 
 /* No counterpart in the reference.  jq_linear_q4_0_device() without the d_ws argument, for callers

@@ -103,14 +103,23 @@ __device__ __forceinline__ int64_t walk_stage(const RowWalk &w, int c, int R, in
     return w.tail_begin;
 }
 
-// Lanes 0..world-1 of one warp poll this rank's arrival flags until each has reached `epoch`.
+// Arrival counts: every all-gather adds GATHER_UNITS to the count a rank keeps for each sender, split over
+// the sender's CTAs in shares that sum to exactly that (so the receiver need not know the sender's grid).
+constexpr uint32_t GATHER_UNITS = 1u << 16;
+__device__ __forceinline__ uint32_t gather_share() {
+    return (uint32_t)(((uint64_t)(blockIdx.x + 1) * GATHER_UNITS) / gridDim.x - ((uint64_t)blockIdx.x * GATHER_UNITS) / gridDim.x);
+}
+
+// Lanes 0..world-1 of one warp poll this rank's arrival counts until all of all-gather number `epoch`
+// has arrived from each sender (counts and the product wrap together modulo 2^32).
 __device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uint32_t epoch, int lane, int *fault) {
     if (lane < world) {
+        const uint32_t expected = epoch * GATHER_UNITS;
         bool seen = false;
         for (uint32_t spin = 0; spin < (1u << 22) && !seen; ++spin) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
-            seen = (int32_t)(v - epoch) >= 0;
+            seen = (int32_t)(v - expected) >= 0;
         }
         if (!seen && fault != nullptr) atomicExch(fault, 2);
     }
@@ -439,25 +448,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         }
         named_bar_sync(1, NW * 32);  // all of this CTA's peer stores have been issued
         if (warp == 0) {
-            int last = 0;
-            if (lane == 0) {
-                __threadfence_system();  // cumulative over the stores ordered before it by the barrier
-                const int prev = atomicAdd(ga.counter, 1);
-                last = (prev == (int)gridDim.x - 1);
+            // Tell every rank that this CTA's part of the band is there: a release at system scope (cumulative
+            // over the stores that the barrier ordered before it) adding this CTA's share to the count the
+            // receiver keeps for this rank.  No CTA waits for another one and nobody waits here; the consumer
+            // of the gathered output waits for the counts.
+            if (lane < ga.world) {
+                asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ga.flag_peer[lane] + ga.rank), "r"(gather_share())
+                             : "memory");
             }
-            last = __shfl_sync(0xFFFFFFFFu, last, 0);
-            if (last) {
-                // every CTA of this rank has made its band visible system-wide: tell every rank.
-                // Nobody waits here; the consumer of the gathered output waits for the flags.
-                __threadfence_system();
-                if (lane == 0) {
+            // bookkeeping off the critical path: the last CTA advances this rank's own step number, which
+            // the next launch reads after the kernel boundary
+            if (lane == 0) {
+                const int prev = atomicAdd(ga.counter, 1);
+                if (prev == (int)gridDim.x - 1) {
                     *ga.counter = 0;
                     *ga.epoch_ptr = gather_epoch;
-                    __threadfence();
-                }
-                if (lane < ga.world) {
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ga.flag_peer[lane] + ga.rank), "r"(gather_epoch)
-                                 : "memory");
                 }
             }
         }
