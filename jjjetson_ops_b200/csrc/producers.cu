@@ -131,46 +131,32 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fmul_rn(__fmul_rn(g, 1.0f / (1.0f + expf(-g))), u);
 }
 
+// IDX: 32-bit block counter whenever T * I / 128 fits (a 64-bit division per block would cost more than
+// the block's arithmetic).
+template <typename IDX>
 __global__ void __launch_bounds__(256)
 swiglu_q8_1_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ mid,
-                   uint8_t *__restrict__ xq, int64_t I, int64_t T, int64_t n_super, int order, int s_mode) {
+                   uint8_t *__restrict__ xq, int64_t I, int64_t T, int64_t n_super_, int order, int s_mode) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
-    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int64_t total = T * n_super;
-    constexpr int U = 1;  // blocks in flight per warp (2 measured slower: 52 % against 60 % of HBM peak)
-    for (int64_t b0 = warp0; b0 < total; b0 += n_warps * U) {
-        float4 g[U], u[U];
-        int64_t off[U];
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-            const int64_t b = b0 + j * n_warps;
-            g[j] = u[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            off[j] = 0;
-            if (b < total) {
-                const int64_t t = b / n_super, ks = b - t * n_super;
-                off[j] = t * I + ks * SUPER + lane * 4;
-                g[j] = __ldg(reinterpret_cast<const float4 *>(gate + off[j]));
-                u[j] = __ldg(reinterpret_cast<const float4 *>(up + off[j]));
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-            const int64_t b = b0 + j * n_warps;  // uniform across the warp
-            if (b >= total) break;
-            const int64_t t = b / n_super, ks = b - t * n_super;
-            const float4 v = make_float4(silu_mul(g[j].x, u[j].x), silu_mul(g[j].y, u[j].y), silu_mul(g[j].z, u[j].z),
-                                         silu_mul(g[j].w, u[j].w));
-            if (mid != nullptr) *reinterpret_cast<float4 *>(mid + off[j]) = v;
-            if (xq != nullptr) {
-                uint32_t ds;
-                const uint32_t q = quantize_group_q8_1(v, s_mode, &ds);
-                uint8_t *blk = xq + q8_block_index(ks, t, n_super, T, order) * Q8_BYTES;
-                reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
-                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
-            }
+    const IDX n_super = (IDX)n_super_;
+    const IDX warp0 = (IDX)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const IDX n_warps = (IDX)(((int64_t)gridDim.x * blockDim.x) >> 5);
+    const IDX total = (IDX)(T * n_super_);
+    for (IDX b = warp0; b < total; b += n_warps) {
+        const IDX t = b / n_super, ks = b - t * n_super;
+        const int64_t off = (int64_t)t * I + (int64_t)ks * SUPER + lane * 4;
+        const float4 g = __ldg(reinterpret_cast<const float4 *>(gate + off));
+        const float4 u = __ldg(reinterpret_cast<const float4 *>(up + off));
+        const float4 v = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
+        if (mid != nullptr) *reinterpret_cast<float4 *>(mid + off) = v;
+        if (xq != nullptr) {
+            uint32_t ds;
+            const uint32_t q = quantize_group_q8_1(v, s_mode, &ds);
+            uint8_t *blk = xq + q8_block_index(ks, t, n_super_, T, order) * Q8_BYTES;
+            reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
+            if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
         }
     }
 }
@@ -252,8 +238,13 @@ int launch_swiglu_q8_1(cudaStream_t st, const float *d_gate, const float *d_up, 
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     launch_with_pdl(cfg, attr);
-    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, swiglu_q8_1_kernel, d_gate, d_up, d_mid, static_cast<uint8_t *>(d_xq), I, T, n_super,
-                                   order, s_mode));
+    if (total + ctas * 256 < (int64_t)0x7FFFFFFF) {
+        JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, swiglu_q8_1_kernel<uint32_t>, d_gate, d_up, d_mid, static_cast<uint8_t *>(d_xq), I, T,
+                                       n_super, order, s_mode));
+    } else {
+        JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, swiglu_q8_1_kernel<int64_t>, d_gate, d_up, d_mid, static_cast<uint8_t *>(d_xq), I, T,
+                                       n_super, order, s_mode));
+    }
     return JQ_OK;
 }
 

@@ -13,38 +13,44 @@ namespace {
 constexpr int QUANT_THREADS = 256;
 constexpr int QUANT_UNROLL = 4;
 
+// IDX is the type of the block counter: 32-bit whenever M * K / 128 fits (64-bit division costs more
+// instructions than the quantization of a block itself).
+template <typename IDX>
 __global__ void __launch_bounds__(QUANT_THREADS)
 quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq, int64_t K, int64_t M,
-                           int64_t n_super, int order, int s_mode) {
+                           int64_t n_super_, int order, int s_mode) {
     // let the multiply that follows on the stream start its weight stream right away; wait for
     // whatever produced x before reading it
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
-    const int64_t warp0 = ((int64_t)blockIdx.x * QUANT_THREADS + threadIdx.x) >> 5;
-    const int64_t n_warps = ((int64_t)gridDim.x * QUANT_THREADS) >> 5;
-    const int64_t total = M * n_super;
+    const IDX n_super = (IDX)n_super_;
+    const IDX warp0 = (IDX)(((int64_t)blockIdx.x * QUANT_THREADS + threadIdx.x) >> 5);
+    const IDX n_warps = (IDX)(((int64_t)gridDim.x * QUANT_THREADS) >> 5);
+    const IDX total = (IDX)(M * n_super_);
 
-    for (int64_t base = warp0; base < total; base += n_warps * QUANT_UNROLL) {
+    for (IDX base = warp0; base < total; base += n_warps * QUANT_UNROLL) {
         float4 xi[QUANT_UNROLL];
+        IDX row[QUANT_UNROLL], ks[QUANT_UNROLL];
 #pragma unroll
         for (int u = 0; u < QUANT_UNROLL; ++u) {
-            const int64_t b = base + (int64_t)u * n_warps;
+            const IDX b = base + (IDX)u * n_warps;
             xi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            row[u] = ks[u] = 0;
             if (b < total) {
-                const int64_t m = b / n_super, ks = b - m * n_super;
-                const int64_t k = ks * SUPER + lane * 4;
-                if (k < K) xi[u] = __ldg(reinterpret_cast<const float4 *>(x + m * K + k));
+                row[u] = b / n_super;
+                ks[u] = b - row[u] * n_super;
+                const int64_t k = (int64_t)ks[u] * SUPER + lane * 4;
+                if (k < K) xi[u] = __ldg(reinterpret_cast<const float4 *>(x + (int64_t)row[u] * K + k));
             }
         }
 #pragma unroll
         for (int u = 0; u < QUANT_UNROLL; ++u) {
-            const int64_t b = base + (int64_t)u * n_warps;  // uniform across the warp
+            const IDX b = base + (IDX)u * n_warps;  // uniform across the warp
             if (b >= total) break;
             uint32_t ds;
             const uint32_t q = quantize_group_q8_1(xi[u], s_mode, &ds);
-            const int64_t m = b / n_super, ks = b - m * n_super;
-            uint8_t *blk = xq + q8_block_index(ks, m, n_super, M, order) * Q8_BYTES;
+            uint8_t *blk = xq + q8_block_index(ks[u], row[u], n_super_, M, order) * Q8_BYTES;
             reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
             if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
         }
@@ -133,8 +139,13 @@ int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100, d_x, static_cast<uint8_t *>(d_xq), K, M, n_super,
-                                   order, s_mode));
+    if (total + (int64_t)ctas * QUANT_THREADS < (int64_t)0x7FFFFFFF) {
+        JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100<uint32_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
+                                       n_super, order, s_mode));
+    } else {
+        JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100<int64_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
+                                       n_super, order, s_mode));
+    }
     return JQ_OK;
 }
 

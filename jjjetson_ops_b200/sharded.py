@@ -83,7 +83,7 @@ class PeerBands:
 
     Every rank allocates one block of peer-mappable memory holding two ``[M_max, N_total]`` fp32
     output buffers (used alternately, so that a fast rank never overwrites what a slow rank's
-    consumer still reads) and its arrival flags, and maps the blocks of all other ranks.  The
+    consumer still reads) and its arrival counts, and maps the blocks of all other ranks.  The
     64-byte handles travel through ``all_gather_object``.
     """
 
