@@ -46,9 +46,10 @@ __device__ __forceinline__ float block_sum_reference_order(float v, float *warp_
 // for bit.  The normalised row is staged in shared memory and quantized from there warp by warp
 // (one warp per 128-value block, one lane four consecutive values: the quantizer's own mapping).
 __global__ void __launch_bounds__(RMS_THREADS)
-rms_norm_q8_1_kernel(float *__restrict__ input, float *__restrict__ residual, const float *__restrict__ weight,
-                     float *__restrict__ normed_out, uint8_t *__restrict__ xq, int H, int T, float epsilon, int n_super,
-                     int order, int s_mode) {
+rms_norm_q8_1_kernel(float *input, float *residual, const float *__restrict__ weight, float *normed_out,
+                     uint8_t *__restrict__ xq, int H, int T, float epsilon, int n_super, int order, int s_mode) {
+    // input, residual and normed_out carry no __restrict__: normed_out may be input itself (the reference's
+    // in-place form); every read of a row happens before the barrier that precedes the first write to it
     extern __shared__ __align__(16) float row[];  // H floats
     __shared__ float warp_partial[32];
     __shared__ float inverse_rms;
@@ -135,8 +136,10 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // the block's arithmetic).
 template <typename IDX>
 __global__ void __launch_bounds__(256)
-swiglu_q8_1_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ mid,
-                   uint8_t *__restrict__ xq, int64_t I, int64_t T, int64_t n_super_, int order, int s_mode) {
+swiglu_q8_1_kernel(const float *gate, const float *up, float *mid, uint8_t *__restrict__ xq, int64_t I, int64_t T,
+                   int64_t n_super_, int order, int s_mode) {
+    // gate, up and mid may be the same buffer (in-place use): plain loads, each thread reads its own four
+    // values before it writes them
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
@@ -147,8 +150,8 @@ swiglu_q8_1_kernel(const float *__restrict__ gate, const float *__restrict__ up,
     for (IDX b = warp0; b < total; b += n_warps) {
         const IDX t = b / n_super, ks = b - t * n_super;
         const int64_t off = (int64_t)t * I + (int64_t)ks * SUPER + lane * 4;
-        const float4 g = __ldg(reinterpret_cast<const float4 *>(gate + off));
-        const float4 u = __ldg(reinterpret_cast<const float4 *>(up + off));
+        const float4 g = *reinterpret_cast<const float4 *>(gate + off);
+        const float4 u = *reinterpret_cast<const float4 *>(up + off);
         const float4 v = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
         if (mid != nullptr) *reinterpret_cast<float4 *>(mid + off) = v;
         if (xq != nullptr) {
@@ -162,8 +165,7 @@ swiglu_q8_1_kernel(const float *__restrict__ gate, const float *__restrict__ up,
 }
 
 // plain elementwise form for sizes that are not a multiple of 128 (no quantized output possible)
-__global__ void swiglu_plain_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ mid,
-                                    int64_t n) {
+__global__ void swiglu_plain_kernel(const float *gate, const float *up, float *mid, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) mid[i] = silu_mul(gate[i], up[i]);
 }

@@ -116,7 +116,8 @@ def _check_mul_mat(env, wq, x, K, N, M, kernel, order, s_mode, rows=None):
 
 SMALL = [(128, 32, 1), (256, 32, 2), (256, 33, 5), (512, 100, 8), (768, 7, 3), (1024, 257, 1), (256, 1, 1),
          (2048, 130, 4), (4096, 300, 2), (8192, 70, 1), (11008, 50, 1), (16384, 40, 1), (1280, 64, 8),
-         (512, 200, 33), (1024, 129, 130), (256, 64, 300), (768, 256, 128), (4096, 384, 17)]
+         (512, 200, 33), (1024, 129, 130), (256, 64, 300), (768, 256, 128), (4096, 384, 17),
+         (1024, 96, 9), (2048, 64, 32), (768, 40, 24), (6144, 33, 12), (512, 72, 48), (512, 72, 49)]
 
 
 @pytest.mark.parametrize("K,N,M", SMALL)

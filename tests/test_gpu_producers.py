@@ -293,3 +293,18 @@ def test_lm_head_q4_0_after_final_norm(native_lib, oracle, cuda_device):
         xq = O.quantize_q8_1(normed.cpu().numpy(), O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
         assert np.array_equal(xq, hq.cpu().numpy()[: xq.size])
         assert O.err_max_rel(lb.cpu().numpy(), O.mul_mat_deq_f64(tq, xq, H, V, T)) <= 1e-3
+
+
+def test_swiglu_in_place_on_the_gate_buffer(native_lib, oracle, cuda_device):
+    """mid may be the gate buffer itself: each thread reads its values before it writes them."""
+    import torch
+
+    c = native_lib
+    rng = np.random.default_rng(31)
+    g = torch.from_numpy((rng.standard_normal((6, 512)) * 2).astype(np.float32)).to(cuda_device)
+    u = torch.from_numpy(rng.standard_normal((6, 512)).astype(np.float32)).to(cuda_device)
+    want = torch.empty_like(g)
+    want_q = c.swiglu_q8_1(g, u, mid=want)
+    got_q = c.swiglu_q8_1(g, u, mid=g)
+    torch.cuda.synchronize()
+    assert torch.equal(g, want) and torch.equal(got_q, want_q)
