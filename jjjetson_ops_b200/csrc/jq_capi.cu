@@ -142,10 +142,10 @@ int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *
     int rc = JQ_ERR_UNSUPPORTED;
     if (M <= 2) rc = launch_gemv_dp4a(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
     if (rc == JQ_ERR_UNSUPPORTED && M <= 8) rc = launch_gemv_mma(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
-    if (M > 8 && M <= 48 && order == JQ_ORDER_COL_KSUPER && K <= 6144) {
+    if (M > 8 && M <= 32 && order == JQ_ORDER_COL_KSUPER && K <= 6144) {
         // A handful of columns more than one GEMV pass takes: passes of eight columns (the weights of the
         // later passes come from L2) beat a GEMM tile that would be mostly padding (cfg2 shape: M = 16 in
-        // 18.8 us against 99 us, M = 32 in 37 us against 76 us; from M = 64 on the GEMM wins).
+        // 18.8 us against 41.7 us, M = 32 in 37 us against 44 us; from M = 40 on the GEMM wins).
         const size_t col_bytes = (size_t)(K / SUPER) * Q8_BYTES;  // one column's blocks are contiguous in this order
         for (int64_t m0 = 0; m0 < M; m0 += 8) {
             const int64_t mc = M - m0 < 8 ? M - m0 : 8;

@@ -100,9 +100,11 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
         const int idx = tid + i * GM_THREADS;
         if (idx < GM_BN * 9) {
             const int row = idx / 9, part = idx - row * 9;
-            const int64_t n = min(n0 + row, p.N - 1);  // rows past the end are clamped, never stored
-            cp_async_16(stage_addr + row * GM_W_PITCH + part * 16,
-                        p.w + n * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16);
+            // rows past the end are not loaded: whatever the stage holds there only reaches outputs that are never stored
+            if (n0 + row < p.N) {
+                cp_async_16(stage_addr + row * GM_W_PITCH + part * 16,
+                            p.w + (n0 + row) * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16);
+            }
         }
     }
     // activations: BM columns x 2 blocks x 9 units
@@ -113,9 +115,10 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
         if (idx >= GM_BM * 18) break;
         const int col = idx / 18, part = idx - col * 18;
         const int ks = part / 9, unit = part - ks * 9;
-        const int64_t m = min(m0 + col, p.M - 1);
-        const int64_t blk = q8_block_index(2 * chunk + ks, m, p.n_super, p.M, p.order);
-        cp_async_16(xs + col * GM_X_PITCH + ks * Q8_BYTES + unit * 16, p.xq + blk * Q8_BYTES + unit * 16);
+        if (m0 + col < p.M) {  // columns past the end: as for the rows
+            const int64_t blk = q8_block_index(2 * chunk + ks, m0 + col, p.n_super, p.M, p.order);
+            cp_async_16(xs + col * GM_X_PITCH + ks * Q8_BYTES + unit * 16, p.xq + blk * Q8_BYTES + unit * 16);
+        }
     }
 }
 
