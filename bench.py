@@ -510,6 +510,9 @@ def measure_extras(torch, capi, synth, dev, peaks):
     t = bench_linear(4096, 32000, 1, steps=100, fused=False)
     b = synth.algorithmic_bytes(4096, 32000, 1, fused_quantize=False)
     out["lm_head_q4_0_V32000_M1_mul_mat_only"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    # separate q / k / v and gate / up weight buffers (the reference's layout): one launch per matrix against one
+    # launch over the concatenated rows
+    out["multi_linear_M1"] = bench_multi_linear(torch, capi, dev, 1)
     # the layer's own data flow around the linears, fp32 hand-offs against Q8_1 hand-offs
     for Mc in (1, 128):
         out["layer_dataflow_M%d" % Mc] = bench_layer_dataflow(torch, capi, synth, dev, peaks, Mc)
@@ -521,6 +524,43 @@ def measure_extras(torch, capi, synth, dev, peaks):
     out["cfg3_M512"] = {"us": t * 1e6, "TOPS": o / t / 1e12, "frac_int8_peak": o / t / 1e12 / int8_peak,
                         "int8_peak_tops": int8_peak, "int8_peak_note": "2 x cuBLAS bf16 %s burst" % peaks["source"]}
     return out
+
+
+def bench_multi_linear(torch, capi, dev, M):
+    """q, k, v (three 4096 x 4096 matrices) and gate, up (two 11008 x 4096) as separate weight buffers."""
+    rng = np.random.default_rng(6)
+    res = {}
+    for name, K, Ns in (("qkv_3x4096", 4096, (4096, 4096, 4096)), ("gate_up_2x11008", 4096, (11008, 11008))):
+        layer_bytes = sum(capi.q4_0_bytes(n, K) for n in Ns)
+        R = max(2, -(-3 * L2_BYTES // layer_bytes) + 1)
+        sets = []
+        for _ in range(R):
+            ws = []
+            for n in Ns:
+                b = torch.from_numpy(rng.integers(0, 256, size=capi.q4_0_bytes(n, K), dtype=np.uint8)).to(dev).view(n, -1)
+                blk = b.view(n, K // 32, 18)
+                blk[:, :, 0] = 0
+                blk[:, :, 1] = 0x20
+                ws.append(b)
+            sets.append(ws)
+        x = torch.from_numpy(rng.standard_normal((M, K), dtype=np.float32)).to(dev)
+        scratch = torch.zeros(max(capi.q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
+        outs = [torch.zeros((M, n), dtype=torch.float32, device=dev) for n in Ns]
+
+        def separate(i):
+            for w, n, y in zip(sets[i % R], Ns, outs):
+                capi.linear_q4_0(w, x, n, capi.S_D_SUM_Q, ws=scratch, out=y)
+
+        def together(i):
+            capi.linear_q4_0_multi(sets[i % R], Ns, x=x, ws=scratch, outs=outs)
+
+        t_sep, _ = time_graph_steps(torch, separate, 60, 3, lambda: None)
+        t_one, _ = time_graph_steps(torch, together, 60, 3, lambda: None)
+        res[name] = {"separate_us": t_sep / 60 * 1e6, "one_launch_us": t_one / 60 * 1e6,
+                     "GB/s_one_launch": layer_bytes / (t_one / 60) / 1e9}
+        del sets
+        torch.cuda.empty_cache()
+    return res
 
 
 def bench_producers(torch, capi, dev, peaks):
@@ -557,7 +597,7 @@ def bench_layer_dataflow(torch, capi, synth, dev, peaks, M):
     src/engine/transformer_runner.cpp:208-328, without attention, which is not on this path): RMSNorm with
     residual add -> QKV -> (first 4096 columns) -> O -> RMSNorm with residual add -> gate, up -> SwiGLU -> down.
     Timed twice: fp32 hand-offs (every linear quantizes its input itself) and Q8_1 hand-offs (the producers
-    write the blocks; gate and up share them)."""
+    write the blocks; gate and up share them and run as one launch over their concatenated rows)."""
     rng = np.random.default_rng(4)
     shapes = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096)]
     layer_bytes = sum(capi.q4_0_bytes(n, k) for _, k, n in shapes)
@@ -612,8 +652,7 @@ def bench_layer_dataflow(torch, capi, synth, dev, peaks, M):
         attn.copy_(y_qkv[:, :H])
         capi.linear_q4_0(w[1], attn, H, D, ws=scratch, out=mid_h)  # its producer (attention) is not on this path
         capi.rms_norm_q8_1(mid_h, wn, 1e-6, residual=residual, xq=hq)
-        capi.mul_mat_q4_0_q8_1(w[2], hq, H, I, M, KS, out=y_gate)
-        capi.mul_mat_q4_0_q8_1(w[3], hq, H, I, M, KS, out=y_up)
+        capi.linear_q4_0_multi([w[2], w[3]], (I, I), xq=hq, K=H, M=M, outs=[y_gate, y_up])  # gate and up in one launch
         capi.swiglu_q8_1(y_gate, y_up, xq=mq)
         capi.mul_mat_q4_0_q8_1(w[4], mq, I, H, M, KS, out=y_down)
 
@@ -625,7 +664,8 @@ def bench_layer_dataflow(torch, capi, synth, dev, peaks, M):
     alg = sum(synth.algorithmic_bytes(k, n, M) for _, k, n in shapes)
     res["GB/s_q8_1_handoffs"] = alg / (res["q8_1_handoffs_us"] * 1e-6) / 1e9
     res["frac_hbm_q8_1_handoffs"] = res["GB/s_q8_1_handoffs"] / peaks["hbm_gbs"]
-    res["kernels_per_layer"] = "5 multiplies + 2 RMSNorm + SwiGLU (+3 small copies/fills); attention not included"
+    res["kernels_per_layer"] = ("fp32 hand-offs: 5 multiplies + 2 RMSNorm + SwiGLU; Q8_1 hand-offs: 4 multiplies (gate + up in one) "
+                                "+ 2 RMSNorm + SwiGLU; +3 small copies/fills each; attention not included")
     res["weight_copies"] = R
     del layers
     torch.cuda.empty_cache()

@@ -130,6 +130,20 @@ int jq_mul_mat_q4_0_q8_1_device_ex(void *stream, const void *d_w, const void *d_
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y,
                           int64_t K, int64_t N, int64_t M, int s_mode);
 
+/* Several linears that share their input, in one call: the separate q / k / v projections
+ * (src/engine/transformer_runner.cpp:214-216) or gate / up (:319-321) of the reference's layer,
+ * whose weights live in separate buffers (src/model/transformer_model.h:13-23).  Matrix i has
+ * N[i] rows of K / 32 Q4_0 blocks and writes d_y[i] = [M][N[i]].  Give either d_x (fp32, then
+ * d_ws receives the Q8_1 blocks as in jq_linear_q4_0_device) or d_xq (blocks in
+ * JQ_ORDER_COL_KSUPER order, e.g. from jq_rms_norm_q8_1_device; d_ws unused).  For M <= 8 and
+ * K within the decode kernels' reach the matrices are treated as one matrix of sum(N) rows and
+ * multiplied by a single launch, with the same results as separate calls; other shapes quantize
+ * once and run one multiply per matrix.  No counterpart in the reference (its linears are
+ * separate cuBLAS calls). */
+int jq_linear_q4_0_multi_device(void *stream, int n_mats, const void *const *d_w, const int64_t *N,
+                                float *const *d_y, const float *d_x, const void *d_xq, void *d_ws,
+                                int64_t K, int64_t M, int s_mode);
+
 /* ---- producers of the quantized linear's input ---------------------------------------------
  * The two kernels that run just ahead of a linear in the reference's transformer layer
  * (src/engine/transformer_runner.cpp:208-216, 311-328), with the Q8_1 quantizer folded in: the

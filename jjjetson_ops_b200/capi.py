@@ -67,6 +67,8 @@ _SIGS = {
     "swiglu_silu_mul_launch_device": (None, [_vp, _vp, _vp, _vp, _ci]),
     "linear_q4_0_forward_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci]),
     "lm_head_q4_0_forward_device": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci]),
+    "jq_linear_q4_0_multi_device": (_ci, [_vp, _ci, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_vp), _vp, _vp, _vp,
+                                          _i64, _i64, _ci]),
     "jq_peer_alloc": (_ci, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
     "jq_peer_open": (_ci, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "jq_peer_close": (_ci, [_vp]),
@@ -178,6 +180,29 @@ def linear_q4_0(w: torch.Tensor, x: torch.Tensor, N: int, s_mode: int = S_D_SUM_
         check(_lib.jq_linear_q4_0_device(_stream(x), _dev(w, torch.uint8, "w"), _dev(x, torch.float32, "x"),
                                          _dev(ws, torch.uint8, "ws"), _dev(out, torch.float32, "out"), K, N, M, s_mode))
     return out
+
+
+def linear_q4_0_multi(ws_list, N_list, x: Optional[torch.Tensor] = None, xq: Optional[torch.Tensor] = None,
+                      K: Optional[int] = None, M: Optional[int] = None, s_mode: int = S_D_SUM_Q,
+                      ws: Optional[torch.Tensor] = None, outs=None):
+    """Several linears that share their input in one call (separate q/k/v or gate/up weights).  Give ``x``
+    (fp32 ``[M, K]``) or ``xq`` (Q8_1 blocks, with ``K`` and ``M``).  Returns the list of outputs."""
+    dev = ws_list[0].device
+    if x is not None:
+        M, K = x.shape
+        if ws is None:
+            ws = torch.empty(max(q8_1_bytes(K, M), 16), dtype=torch.uint8, device=dev)
+    n = len(ws_list)
+    if outs is None:
+        outs = [torch.empty((M, int(Ni)), dtype=torch.float32, device=dev) for Ni in N_list]
+    wp = (_vp * n)(*[_dev(w, torch.uint8, "w") for w in ws_list])
+    yp = (_vp * n)(*[_dev(y, torch.float32, "out") for y in outs])
+    np_ = (_i64 * n)(*[int(v) for v in N_list])
+    with torch.cuda.device(dev):
+        check(_lib.jq_linear_q4_0_multi_device(
+            _stream(ws_list[0]), n, wp, np_, yp, None if x is None else _dev(x, torch.float32, "x"),
+            None if xq is None else _dev(xq, torch.uint8, "xq"), None if ws is None else _dev(ws, torch.uint8, "ws"), K, M, s_mode))
+    return outs
 
 
 def rms_norm_q8_1(x: torch.Tensor, weight: torch.Tensor, epsilon: float, residual: Optional[torch.Tensor] = None,

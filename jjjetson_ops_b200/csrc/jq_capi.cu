@@ -343,6 +343,65 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
     return dispatch_mul_mat(st, d_w, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO);
 }
 
+int jq_linear_q4_0_multi_device(void *stream, int n_mats, const void *const *d_w, const int64_t *N, float *const *d_y,
+                                const float *d_x, const void *d_xq, void *d_ws, int64_t K, int64_t M, int s_mode) {
+    if (n_mats < 1 || n_mats > 4) return set_error(JQ_ERR_INVALID_ARG, "1 to 4 weight matrices per call (got %d)", n_mats);
+    if (d_w == nullptr || N == nullptr || d_y == nullptr) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+    if ((d_x == nullptr) == (d_xq == nullptr)) return set_error(JQ_ERR_INVALID_ARG, "give either fp32 activations or Q8_1 blocks");
+    if (int rc = check_s_mode(s_mode)) return rc;
+    int64_t n_total = 0;
+    for (int i = 0; i < n_mats; ++i) {
+        if (int rc = check_mul_mat_shape(K, N[i], M)) return rc;
+        if (N[i] > 0 && (d_y[i] == nullptr || (K > 0 && d_w[i] == nullptr))) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
+        if (((uintptr_t)d_w[i] & 1u) != 0) return set_error(JQ_ERR_ALIGN, "Q4_0 blocks must be 2-byte aligned");
+        n_total += N[i];
+    }
+    if (M == 0 || n_total == 0) return JQ_OK;
+    if (d_x != nullptr && K > 0 && d_ws == nullptr) return set_error(JQ_ERR_INVALID_ARG, "fp32 activations need a Q8_1 workspace");
+    if (((uintptr_t)d_x & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0 || ((uintptr_t)d_ws & 15u) != 0)
+        return set_error(JQ_ERR_ALIGN, "activations, Q8_1 blocks and workspace must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // one launch over the concatenated rows while the decode kernels take the shape
+    bool all_rows = true;
+    for (int i = 0; i < n_mats; ++i) all_rows = all_rows && N[i] > 0;
+    if (K > 0 && M <= 8 && all_rows) {
+        MultiMat mm{};
+        mm.n = n_mats;
+        for (int i = 0; i < n_mats; ++i) {
+            mm.w[i] = d_w[i];
+            mm.y[i] = d_y[i];
+            mm.rows[i] = N[i];
+        }
+        const bool fuse_quantizer = d_x != nullptr && M * (K / SUPER) <= 64;
+        if (d_x != nullptr && !fuse_quantizer) {
+            if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
+        }
+        const float *xf = fuse_quantizer ? d_x : nullptr;
+        const void *xq = fuse_quantizer ? nullptr : (d_x != nullptr ? d_ws : d_xq);
+        int rc = JQ_ERR_UNSUPPORTED;
+        if (M <= 2) rc = launch_gemv_dp4a(st, nullptr, xq, xf, fuse_quantizer ? d_ws : nullptr, nullptr, K, n_total, M,
+                                          JQ_ORDER_COL_KSUPER, s_mode, nullptr, &mm);
+        if (rc == JQ_ERR_UNSUPPORTED)
+            rc = launch_gemv_mma(st, nullptr, xq, xf, fuse_quantizer ? d_ws : nullptr, nullptr, K, n_total, M, JQ_ORDER_COL_KSUPER,
+                                 s_mode, &mm);
+        if (rc != JQ_ERR_UNSUPPORTED) return rc;
+        // not a shape for the decode kernels: the activations may already be quantized in d_ws, go on below
+        if (d_x != nullptr && !fuse_quantizer) {
+            d_xq = d_ws;
+            d_x = nullptr;
+        }
+    }
+    if (d_x != nullptr && K > 0) {
+        if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
+        d_xq = d_ws;
+    }
+    for (int i = 0; i < n_mats; ++i) {
+        if (N[i] == 0) continue;
+        if (int rc = dispatch_mul_mat(st, d_w[i], d_xq, d_y[i], K, N[i], M, JQ_ORDER_COL_KSUPER, JQ_KERNEL_AUTO)) return rc;
+    }
+    return JQ_OK;
+}
+
 // ---- N-sharded decode: multiply + all-gather in one kernel -----------------------------------------
 
 int jq_peer_alloc(size_t bytes, void **d_ptr, unsigned char *handle_out) {

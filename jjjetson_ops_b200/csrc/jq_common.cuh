@@ -90,12 +90,20 @@ int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, c
 // Streaming GEMV family.  d_x_f32 != nullptr fuses the activation quantizer into the prologue
 // (d_xq then receives the quantized blocks in JQ_ORDER_COL_KSUPER order, may be nullptr).
 // Returns JQ_ERR_UNSUPPORTED when the shape or alignment rules of the fast path do not hold.
+// With `multi`, several weight matrices that share K and the activations are multiplied in one launch
+// (d_w, d_y are ignored and N is the sum of their rows).
+struct MultiMat {
+    int n;                 // 2..4
+    const void *w[4];
+    float *y[4];           // [M][rows[i]] each
+    int64_t rows[4];
+};
 int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
                      void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
-                     int s_mode, const GatherArgs *gather = nullptr);
+                     int s_mode, const GatherArgs *gather = nullptr, const MultiMat *multi = nullptr);
 int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32,
                     void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
-                    int s_mode);
+                    int s_mode, const MultiMat *multi = nullptr);
 int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                     int64_t N, int64_t M, int order);
 int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,

@@ -30,7 +30,17 @@ constexpr int GV_BAR_BYTES = 256;  // full[8] + empty[8] ring mbarriers, red_ful
 constexpr int GV_RED_SLOTS = 4;
 constexpr uint32_t MASK4 = 0x0F0F0F0Fu;
 
+constexpr int GV_MAX_MATS = 4;
+
 struct GemvParams {
+    // Up to GV_MAX_MATS weight matrices that share K and the activations, treated as one matrix whose rows are
+    // theirs in order (separate q / k / v or gate / up projections in one launch): matrix i owns the rows
+    // [mat_begin[i], mat_begin[i + 1]) and writes to y_mat[i], an [M][its row count] array.  n_mats == 1:
+    // plain single matrix (w, y).
+    const uint8_t *w_mat[GV_MAX_MATS];
+    float *y_mat[GV_MAX_MATS];
+    int64_t mat_begin[GV_MAX_MATS + 1];
+    int n_mats;
     const uint8_t *w;
     const uint8_t *xq;     // quantized activations (nullptr when x_f32 is given)
     const float *x_f32;    // raw activations to quantize in the prologue, or nullptr
@@ -54,6 +64,19 @@ struct GemvParams {
     uint32_t y_rows;
     unsigned long long *trace;  // 8 timestamps per CTA of this launch (tracing aid), or nullptr
 };
+
+// matrix that owns row r of the concatenation (n_mats is tiny: a linear scan)
+__device__ __forceinline__ int mat_of_row(const GemvParams &p, int64_t r) {
+    int i = 0;
+    while (i + 1 < p.n_mats && r >= p.mat_begin[i + 1]) ++i;
+    return i;
+}
+// where output (column m, row r of the concatenation) lives
+__device__ __forceinline__ float *y_slot(const GemvParams &p, int m, int64_t r) {
+    if (p.n_mats <= 1) return p.y + (size_t)m * p.N + r;
+    const int i = mat_of_row(p, r);
+    return p.y_mat[i] + (size_t)m * (p.mat_begin[i + 1] - p.mat_begin[i]) + (r - p.mat_begin[i]);
+}
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -161,13 +184,32 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
         }
         if (!ok) return;
         uint8_t *dst = ring + (size_t)s * p.stage_bytes;
-        const uint8_t *src = p.w + r0 * p.row_bytes;
-        if (PER_ROW) {
+        if (p.n_mats <= 1) {
+            const uint8_t *src = p.w + r0 * p.row_bytes;
+            if (PER_ROW) {
+                for (int r = lane; r < rows; r += 32) {
+                    bulk_g2s(dst + (size_t)r * p.row_stride, src + (size_t)r * p.row_bytes, p.row_bytes, &full[s]);
+                }
+            } else {
+                bulk_g2s(dst, src, (uint32_t)rows * p.row_bytes, &full[s]);
+            }
+        } else if (PER_ROW) {
             for (int r = lane; r < rows; r += 32) {
-                bulk_g2s(dst + (size_t)r * p.row_stride, src + (size_t)r * p.row_bytes, p.row_bytes, &full[s]);
+                const int i = mat_of_row(p, r0 + r);
+                bulk_g2s(dst + (size_t)r * p.row_stride, p.w_mat[i] + (r0 + r - p.mat_begin[i]) * p.row_bytes, p.row_bytes, &full[s]);
             }
         } else {
-            bulk_g2s(dst, src, (uint32_t)rows * p.row_bytes, &full[s]);
+            // a stage may straddle matrices: one copy per matrix it touches, landing back to back
+            int64_t r = r0;
+            int left = rows;
+            while (left > 0) {
+                const int i = mat_of_row(p, r);
+                const int take = (int)min((int64_t)left, p.mat_begin[i + 1] - r);
+                bulk_g2s(dst, p.w_mat[i] + (r - p.mat_begin[i]) * p.row_bytes, (uint32_t)take * p.row_bytes, &full[s]);
+                dst += (size_t)take * p.row_bytes;
+                r += take;
+                left -= take;
+            }
         }
     }
 }
@@ -417,7 +459,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                     if (p.gather.world > 0) {
                         ybuf[(size_t)m * p.y_rows + (size_t)(r0 + r - r_begin)] = v;
                     } else {
-                        p.y[(size_t)m * p.N + (r0 + r)] = v;
+                        *y_slot(p, m, r0 + r) = v;
                     }
                 }
             }
@@ -538,7 +580,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
 #pragma unroll
                 for (int w = 0; w < NW; ++w) v += src[w * 128 + idx];
                 const int row = idx >> 3, col = idx & 7;
-                if (row < rows && col < p.M) p.y[(size_t)col * p.N + (r0 + row)] = v;
+                if (row < rows && col < p.M) *y_slot(p, col, r0 + row) = v;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&red_empty[slot]);
@@ -755,6 +797,7 @@ int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
 
 int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
                 float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+    p.n_mats = 1;
     p.w = static_cast<const uint8_t *>(d_w);
     p.xq = d_x_f32 ? nullptr : static_cast<const uint8_t *>(d_xq);
     p.x_f32 = d_x_f32;
@@ -783,6 +826,26 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
 
 }  // namespace
 
+namespace {
+int apply_multi(GemvParams &p, const MultiMat *multi, const GatherArgs *gather) {
+    if (multi == nullptr) return JQ_OK;
+    if (multi->n < 1 || multi->n > GV_MAX_MATS) return set_error(JQ_ERR_INVALID_ARG, "1 to %d weight matrices per launch", GV_MAX_MATS);
+    if (gather != nullptr) return set_error(JQ_ERR_UNSUPPORTED, "the all-gather epilogue takes a single weight matrix");
+    p.n_mats = multi->n;
+    p.mat_begin[0] = 0;
+    for (int i = 0; i < multi->n; ++i) {
+        if (((uintptr_t)multi->w[i] & 15u) != 0) return set_error(JQ_ERR_UNSUPPORTED, "streaming GEMV needs 16-byte aligned weights");
+        p.w_mat[i] = static_cast<const uint8_t *>(multi->w[i]);
+        p.y_mat[i] = multi->y[i];
+        p.mat_begin[i + 1] = p.mat_begin[i] + multi->rows[i];
+    }
+    if (p.mat_begin[multi->n] != p.N) return set_error(JQ_ERR_INVALID_ARG, "row counts of the matrices do not add up to N");
+    p.w = p.w_mat[0];
+    p.y = p.y_mat[0];
+    return JQ_OK;
+}
+}  // namespace
+
 int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, const uint32_t *d_epoch) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1);
@@ -798,7 +861,9 @@ int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, c
 }
 
 int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
-                     float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode, const GatherArgs *gather) {
+                     float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode, const GatherArgs *gather,
+                     const MultiMat *multi) {
+    if (multi != nullptr) d_w = multi->w[0];
     if (M < 1 || M > 2) return set_error(JQ_ERR_UNSUPPORTED, "dp4a GEMV handles M <= 2 (M = %lld)", (long long)M);
     if (int rc = fast_path_ok(d_w, d_xq, d_x_f32, K, N)) return rc;
     if (N == 0) return JQ_OK;
@@ -807,6 +872,7 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     GemvParams p{};
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
     if (gather != nullptr) p.gather = *gather;
+    if (int rc = apply_multi(p, multi, gather)) return rc;
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {
@@ -832,7 +898,8 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
 }
 
 int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
-                    float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode) {
+                    float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode, const MultiMat *multi) {
+    if (multi != nullptr) d_w = multi->w[0];
     if (M < 1 || M > 8) return set_error(JQ_ERR_UNSUPPORTED, "mma GEMV handles M <= 8 (M = %lld)", (long long)M);
     if (int rc = fast_path_ok(d_w, d_xq, d_x_f32, K, N)) return rc;
     if (N == 0) return JQ_OK;
@@ -840,6 +907,7 @@ int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const fl
     if (int rc = device_caps(&caps)) return rc;
     GemvParams p{};
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
+    if (int rc = apply_multi(p, multi, nullptr)) return rc;
     const int nb = (int)(K / QK);
     if (nb <= 8 * 8) return run_mma<8, 8>(st, p, caps);
     if (nb <= 16 * 8) return run_mma<8, 16>(st, p, caps);

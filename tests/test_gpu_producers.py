@@ -308,3 +308,29 @@ def test_swiglu_in_place_on_the_gate_buffer(native_lib, oracle, cuda_device):
     got_q = c.swiglu_q8_1(g, u, mid=g)
     torch.cuda.synchronize()
     assert torch.equal(g, want) and torch.equal(got_q, want_q)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 20])
+def test_multi_linear_equals_separate_linears(native_lib, oracle, cuda_device, M):
+    """q / k / v (and gate / up) in one launch over the concatenated rows: same bits as separate calls, from fp32
+    input and from Q8_1 blocks; row counts that make a stage straddle two matrices."""
+    import torch
+
+    c, O = native_lib, oracle
+    rng = np.random.default_rng(100 + M)
+    for K, Ns in ((1024, (512, 136, 136)), (4096, (1000, 1000)), (768, (40, 7, 300, 33)), (2048, (96,))):
+        wq = [torch.from_numpy(O.quantize_q4_0((rng.standard_normal((n, K)) * 0.03).astype(np.float32))).to(cuda_device) for n in Ns]
+        x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(cuda_device)
+        want = [c.linear_q4_0(w, x, n) for w, n in zip(wq, Ns)]
+        got = c.linear_q4_0_multi(wq, Ns, x=x)
+        xq = c.quantize_q8_1(x, c.ORDER_COL_KSUPER, c.S_D_SUM_Q)
+        got_q = c.linear_q4_0_multi(wq, Ns, xq=xq, K=K, M=M)
+        torch.cuda.synchronize()
+        for a, b, d, n in zip(want, got, got_q, Ns):
+            assert a.shape == (M, n)
+            assert torch.equal(a, b), (K, Ns, M, "fp32 input")
+            assert torch.equal(a, d), (K, Ns, M, "Q8_1 input")
+    with pytest.raises(c.JqError):
+        c.linear_q4_0_multi(wq, Ns, x=x, xq=xq, K=K, M=M)  # both kinds of input
+    with pytest.raises(c.JqError):
+        c.linear_q4_0_multi(wq * 5, list(Ns) * 5, x=x)  # more than four matrices
