@@ -60,6 +60,9 @@ int set_error(int status, const char *fmt, ...) {
 }
 
 int cuda_error(cudaError_t e, const char *what) {
+    // The runtime keeps a failed call's code as its "last error" until somebody reads it; take it, so that
+    // the post-launch check of a later, unrelated call does not report this failure a second time.
+    (void)cudaGetLastError();
     return set_error(JQ_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
 }
 

@@ -286,6 +286,7 @@ int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
                                          cudaSharedmemCarveoutMaxShared));
         attr_done_dev = dev;
     }
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     gemm_q4_0_q8_1_mma_kernel<RT, CT><<<dim3((unsigned)gx, (unsigned)gy), GM_THREADS, Tile::SMEM, st>>>(p);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;

@@ -529,6 +529,7 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
         JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
         attr_done_dev = dev;
     }
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     gemm_q4_0_q8_1_tc_kernel<<<dim3((unsigned)gx, (unsigned)gy), TC_THREADS, TC_SMEM_BYTES, st>>>(p);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;

@@ -217,52 +217,65 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
 // Prologue of the consumer warps: put the quantized activations into shared memory, laid out
 // [m][k/128] as 144-byte blocks.  Either quantize fp32 input (bit-identical to the stand-alone
 // quantizer) or copy already quantized blocks, honouring their order.
+// One batch of the fused quantizer: U 128-value blocks per warp, indices base, base + NW, ...; all U are
+// quantized together (no early exit inside the batch), so that their shuffle chains overlap.
+template <int NW, int U>
+__device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs, uint64_t *x_ready, int warp, int lane,
+                                               int base, int total, bool first) {
+    float4 xi[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int idx = base + u * NW;
+        xi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < total) {
+            const int m = idx / p.n_super, ks = idx - m * p.n_super;
+            xi[u] = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
+        }
+    }
+    if (first) {
+        // this warp's first (usually only) batch of loads has landed: let the weight stream go on
+        float touch = 0.0f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) touch += xi[u].x;
+        touch = __shfl_xor_sync(0xFFFFFFFFu, touch, 1, 32);
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // after %1" ::"r"(smem_u32(x_ready)), "f"(touch)
+                         : "memory");
+        }
+    }
+    uint32_t qv[U], dsv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) qv[u] = quantize_group_q8_1(xi[u], p.s_mode, &dsv[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int idx = base + u * NW;  // uniform across the warp
+        if (idx < total) {
+            const int m = idx / p.n_super, ks = idx - m * p.n_super;
+            uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+            reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = qv[u];
+            if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = dsv[u];
+            if (p.xq_out != nullptr && blockIdx.x == 0) {
+                uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+                reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = qv[u];
+                if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = dsv[u];
+            }
+        }
+    }
+}
+
 template <int NW>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, uint64_t *x_ready, int warp,
                                                   int lane) {
     const int total = p.M * p.n_super;
     if (p.x_f32 != nullptr) {
-        constexpr int U = 4;  // groups per warp in flight: the prologue is latency-, not bandwidth-bound
-        for (int base = warp; base < total; base += NW * U) {
-            float4 xi[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = base + u * NW;
-                xi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (idx < total) {
-                    const int m = idx / p.n_super, ks = idx - m * p.n_super;
-                    xi[u] = __ldg(reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane);
-                }
-            }
-            if (base == warp) {
-                // this warp's first (usually only) batch of loads has landed: let the weight stream go on
-                float touch = 0.0f;
-#pragma unroll
-                for (int u = 0; u < U; ++u) touch += xi[u].x;
-                touch = __shfl_xor_sync(0xFFFFFFFFu, touch, 1, 32);
-                if (lane == 0) {
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // after %1" ::"r"(smem_u32(x_ready)), "f"(touch)
-                                 : "memory");
-                }
-            }
-            // all U groups are quantized together (no early exit), so that their shuffle chains overlap
-            uint32_t qv[U], dsv[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) qv[u] = quantize_group_q8_1(xi[u], p.s_mode, &dsv[u]);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = base + u * NW;  // uniform across the warp
-                if (idx < total) {
-                    const int m = idx / p.n_super, ks = idx - m * p.n_super;
-                    uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-                    reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = qv[u];
-                    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = dsv[u];
-                    if (p.xq_out != nullptr && blockIdx.x == 0) {
-                        uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-                        reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = qv[u];
-                        if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = dsv[u];
-                    }
-                }
+        // The prologue is bound by instruction issue (every CTA repeats it, ~100 instructions per block and
+        // lane): a warp takes exactly the blocks it has to, two at a time when that covers them all
+        // (one activation row of K = 4096 over 16 warps), else four at a time.
+        if (total <= 2 * NW) {
+            if (warp < total) quantize_batch<NW, 2>(p, xs, x_ready, warp, lane, warp, total, true);
+        } else {
+            for (int base = warp; base < total; base += NW * 4) {
+                quantize_batch<NW, 4>(p, xs, x_ready, warp, lane, base, total, base == warp);
             }
         }
     } else {

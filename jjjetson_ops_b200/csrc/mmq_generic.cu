@@ -109,6 +109,7 @@ int launch_mmq_generic(cudaStream_t st, const void *d_w, const void *d_xq, float
     const int64_t gx = (N + GEN_WARPS - 1) / GEN_WARPS, gy = (M + GEN_COLS - 1) / GEN_COLS;
     if (gy > 65535) return set_error(JQ_ERR_TOO_LARGE, "generic multiply: M = %lld exceeds %d", (long long)M,
                                      65535 * GEN_COLS);
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     mmq_generic_kernel<<<dim3((unsigned)gx, (unsigned)gy), GEN_WARPS * 32, 0, st>>>(
         static_cast<const uint8_t *>(d_w), static_cast<const uint8_t *>(d_xq), d_y, K, N, M, order);
     JQ_CUDA_TRY(cudaGetLastError());
@@ -121,6 +122,7 @@ int launch_block_sums(cudaStream_t st, const void *d_w, const void *d_xq, int32_
     if (total == 0 || M == 0) return JQ_OK;
     int64_t ctas = (total + 255) / 256;
     if (ctas > 148 * 16) ctas = 148 * 16;
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     block_sums_kernel<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const uint8_t *>(d_w),
                                                       static_cast<const uint8_t *>(d_xq), d_sums, K, N, M, order);
     JQ_CUDA_TRY(cudaGetLastError());

@@ -223,6 +223,7 @@ int launch_swiglu_q8_1(cudaStream_t st, const float *d_gate, const float *d_up, 
             return set_error(JQ_ERR_UNSUPPORTED, "swiglu with Q8_1 output needs intermediate_size %% 128 == 0 and 16-byte aligned buffers");
         if (d_mid == nullptr) return JQ_OK;
         const int64_t n = I * T;
+        (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
         swiglu_plain_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(d_gate, d_up, d_mid, n);
         JQ_CUDA_TRY(cudaGetLastError());
         return JQ_OK;

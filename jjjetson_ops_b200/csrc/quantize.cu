@@ -157,6 +157,7 @@ int launch_quantize_q4_0(cudaStream_t st, const float *d_w, void *d_wq, int64_t 
     int64_t ctas = (n_blocks + 31) / 32;  // 32 blocks per 256-thread CTA per pass
     const int64_t cap = (int64_t)caps.sm_count * 32;
     if (ctas > cap) ctas = cap;
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     quantize_q4_0_kernel_sm100<<<(unsigned)ctas, 256, 0, st>>>(d_w, static_cast<uint8_t *>(d_wq), n_blocks);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
