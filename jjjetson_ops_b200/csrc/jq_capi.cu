@@ -320,6 +320,11 @@ int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq,
     return jq_mul_mat_q4_0_q8_1_device_ex(stream, d_w, d_xq, d_y, K, N, M, order, JQ_KERNEL_AUTO);
 }
 
+// The quantizer runs in the multiply kernel's own prologue while the activations are at most this many
+// 128-value blocks: every CTA repeats it and it is bound by instruction issue (about 1 us per 32 blocks),
+// while a quantize launch of its own costs about 2.9 us in a dependent chain whatever the size.
+constexpr int64_t FUSE_QUANTIZER_MAX_BLOCKS = 32;
+
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y, int64_t K,
                           int64_t N, int64_t M, int s_mode) {
     if (int rc = check_mul_mat_shape(K, N, M)) return rc;
@@ -333,7 +338,7 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Decode regime: with few activation blocks the quantizer runs in the multiply kernel's own
     // prologue (every CTA redoes it, which only pays while it is a handful of blocks per warp).
-    if (K > 0 && N > 0 && M <= 8 && M * (K / SUPER) <= 64) {
+    if (K > 0 && N > 0 && M <= 8 && M * (K / SUPER) <= FUSE_QUANTIZER_MAX_BLOCKS) {
         int rc = JQ_ERR_UNSUPPORTED;
         if (M <= 2) rc = launch_gemv_dp4a(st, d_w, nullptr, d_x, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, s_mode);
         if (rc == JQ_ERR_UNSUPPORTED)
@@ -375,7 +380,7 @@ int jq_linear_q4_0_multi_device(void *stream, int n_mats, const void *const *d_w
             mm.y[i] = d_y[i];
             mm.rows[i] = N[i];
         }
-        const bool fuse_quantizer = d_x != nullptr && M * (K / SUPER) <= 64;
+        const bool fuse_quantizer = d_x != nullptr && M * (K / SUPER) <= FUSE_QUANTIZER_MAX_BLOCKS;
         if (d_x != nullptr && !fuse_quantizer) {
             if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
         }
