@@ -323,7 +323,12 @@ int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq,
 // The quantizer runs in the multiply kernel's own prologue while the activations are at most this many
 // 128-value blocks: every CTA repeats it and it is bound by instruction issue (about 1 us per 32 blocks),
 // while a quantize launch of its own costs about 2.9 us in a dependent chain whatever the size.
+// (One activation row of K = 8192 is the exception that was measured: 26.2 us fused, 27.3 us as two launches.)
 constexpr int64_t FUSE_QUANTIZER_MAX_BLOCKS = 32;
+inline bool fuse_quantizer_pays(int64_t M, int64_t K) {
+    const int64_t blocks = M * (K / SUPER);
+    return blocks <= FUSE_QUANTIZER_MAX_BLOCKS || (M == 1 && blocks <= 2 * FUSE_QUANTIZER_MAX_BLOCKS);
+}
 
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y, int64_t K,
                           int64_t N, int64_t M, int s_mode) {
@@ -338,7 +343,7 @@ int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Decode regime: with few activation blocks the quantizer runs in the multiply kernel's own
     // prologue (every CTA redoes it, which only pays while it is a handful of blocks per warp).
-    if (K > 0 && N > 0 && M <= 8 && M * (K / SUPER) <= FUSE_QUANTIZER_MAX_BLOCKS) {
+    if (K > 0 && N > 0 && M <= 8 && fuse_quantizer_pays(M, K)) {
         int rc = JQ_ERR_UNSUPPORTED;
         if (M <= 2) rc = launch_gemv_dp4a(st, d_w, nullptr, d_x, d_ws, d_y, K, N, M, JQ_ORDER_COL_KSUPER, s_mode);
         if (rc == JQ_ERR_UNSUPPORTED)
@@ -380,7 +385,7 @@ int jq_linear_q4_0_multi_device(void *stream, int n_mats, const void *const *d_w
             mm.y[i] = d_y[i];
             mm.rows[i] = N[i];
         }
-        const bool fuse_quantizer = d_x != nullptr && M * (K / SUPER) <= FUSE_QUANTIZER_MAX_BLOCKS;
+        const bool fuse_quantizer = d_x != nullptr && fuse_quantizer_pays(M, K);
         if (d_x != nullptr && !fuse_quantizer) {
             if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
         }
