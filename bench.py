@@ -317,7 +317,7 @@ def run_ours(args) -> None:
     bands = None
     collective = "none"
     if world > 1:
-        collective = args.collective if M <= 2 else "nccl"
+        collective = args.collective
     if collective == "fused":
         from jjjetson_ops_b200.sharded import PeerBands
 
@@ -744,7 +744,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4096)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--m", type=int, default=1, help="activation rows of the headline workload (1..8)")
+    ap.add_argument("--m", type=int, default=1, help="activation rows of the workload (1..8 for cfg2; any with --shape cfg4)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary shapes and the CPU baseline")
     ap.add_argument("--shape", choices=["cfg2", "cfg4"], default="cfg2",
                     help="cfg2 (default): the headline shape per GPU, weak scaling; cfg4: K=8192, N=28672 split along N over "

@@ -171,7 +171,8 @@ int jq_swiglu_q8_1_device(void *stream, const float *d_gate, const float *d_up, 
 
 /* ---- N-sharded decode (no counterpart in the reference, which is single-GPU) -------------------
  * One process per GPU owns a contiguous band of weight rows.  jq_linear_q4_0_allgather_device
- * runs this rank's quantize + multiply (M <= 2) and writes its band of the output directly into
+ * runs this rank's quantize + multiply (M <= 2: one streaming kernel; larger M: a quantize launch
+ * and the tensor-core GEMM, K % 256 == 0) and writes its band of the output directly into
  * every rank's [M][N_total] buffer through peer-mapped pointers (plain stores over NVLink); each
  * CTA then adds its share to the arrival count that every rank keeps for this rank (one
  * system-scope release-add per CTA and peer; a whole all-gather adds 65536).  The kernel does not
@@ -191,8 +192,9 @@ int jq_swiglu_q8_1_device(void *stream, const float *d_gate, const float *d_up, 
  *   d_counter      : a local int, zero before the first call
  * The two buffers alternate, and with wait_previous (or a jq_allgather_wait_device between calls) a
  * fast rank cannot overwrite a band that a slow rank still has to read.
- * Every wait inside the kernels is bounded; if one runs out jq_device_fault() reports 2.  Other
- * shapes return JQ_ERR_UNSUPPORTED: multiply locally and all-gather with NCCL.
+ * With M > 2, wait_previous is carried out by a jq_allgather_wait_device queued ahead of the launches.
+ * Every wait inside the kernels is bounded; if one runs out jq_device_fault() reports 2.  Shapes
+ * the kernels refuse return JQ_ERR_UNSUPPORTED: multiply locally and all-gather with NCCL.
  * jq_peer_alloc / jq_peer_open: device memory that other processes on the node can map
  * (cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle); the 64-byte handle travels through any
  * host channel (e.g. torch.distributed all_gather_object). */

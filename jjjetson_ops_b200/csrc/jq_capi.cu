@@ -463,8 +463,8 @@ int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *
     if (!y_peers || !flag_peers || !d_counter || !d_epoch || !d_w || !d_x) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
     if (n_offset < 0 || n_offset + N_local > N_total) return set_error(JQ_ERR_INVALID_ARG, "band [%lld, %lld) outside N_total = %lld",
                                                                        (long long)n_offset, (long long)(n_offset + N_local), (long long)N_total);
-    if (M < 1 || M > 2 || N_local < 1 || K < 1)
-        return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather covers M <= 2 (M = %lld); gather with NCCL instead", (long long)M);
+    if (M < 1 || N_local < 1 || K < 1) return set_error(JQ_ERR_INVALID_ARG, "empty shape");
+    if (M > 2 && d_ws == nullptr) return set_error(JQ_ERR_INVALID_ARG, "M > 2 needs the Q8_1 workspace");
     if (((uintptr_t)d_x & 15u) != 0 || (d_ws && ((uintptr_t)d_ws & 15u) != 0))
         return set_error(JQ_ERR_ALIGN, "activations and workspace must be 16-byte aligned");
     GatherArgs ga;
@@ -481,8 +481,19 @@ int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *
     ga.y_stride_bytes = y_stride_bytes;
     ga.wait_previous = wait_previous;
     ga.counter = d_counter;
-    return launch_gemv_dp4a(static_cast<cudaStream_t>(stream), d_w, nullptr, d_x, d_ws, nullptr, K, N_local, M,
-                            JQ_ORDER_COL_KSUPER, s_mode, &ga);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M <= 2) {
+        const int rc = launch_gemv_dp4a(st, d_w, nullptr, d_x, d_ws, nullptr, K, N_local, M, JQ_ORDER_COL_KSUPER, s_mode, &ga);
+        if (rc != JQ_ERR_UNSUPPORTED || d_ws == nullptr) return rc;
+    }
+    // Larger batches (and decode shapes the streaming kernel refuses): quantize, then the tensor-core GEMM
+    // whose epilogue stores its tiles into every rank's buffer.  The activations are this call's input, not
+    // a gathered output the kernel could wait for itself: queue jq_allgather_wait_device first if they are.
+    if (wait_previous) {
+        if (int rc = launch_allgather_wait(st, ga.flag_peer[rank], world, d_epoch)) return rc;
+    }
+    if (int rc = launch_quantize_q8_1(st, d_x, d_ws, K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
+    return launch_gemm_mma(st, d_w, d_ws, nullptr, K, N_local, M, JQ_ORDER_COL_KSUPER, &ga);
 }
 
 int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const unsigned *d_epoch) {

@@ -105,7 +105,7 @@ int launch_gemv_mma(cudaStream_t st, const void *d_w, const void *d_xq, const fl
                     void *d_xq_out, float *d_y, int64_t K, int64_t N, int64_t M, int order,
                     int s_mode, const MultiMat *multi = nullptr);
 int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
-                    int64_t N, int64_t M, int order);
+                    int64_t N, int64_t M, int order, const GatherArgs *gather = nullptr);
 int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                    int64_t N, int64_t M, int order);
 

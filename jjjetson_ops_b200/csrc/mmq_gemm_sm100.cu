@@ -88,7 +88,11 @@ struct GemmParams {
     int K, order;
     int n_super;         // K / 128
     uint32_t row_bytes;  // K / 32 * 18
+    int *fault;
+    GatherArgs gather;   // world > 0: the tile goes to every rank's [M][N_total] buffer instead of y (all-gather epilogue)
 };
+
+constexpr uint32_t GM_GATHER_UNITS = 1u << 16;  // what one all-gather adds to each arrival count (shares of the CTAs sum to it)
 
 template <int RT, int CT>
 __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_addr, int chunk, int64_t n0, int64_t m0,
@@ -252,6 +256,61 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
     }
     cp_async_wait<0>();
 
+    if (p.gather.world > 0) {
+        // ---- all-gather epilogue: the tile is staged in shared memory ([column m][row n], n contiguous as
+        // in y) and stored into every rank's [M][N_total] buffer through peer-mapped pointers, 16 bytes per
+        // lane and 512 contiguous bytes per tile row; then this CTA adds its share to the arrival count each
+        // rank keeps for this one (system-scope release, cumulative over the stores the barrier ordered
+        // before it).  Nobody waits here: the consumer of the gathered output waits for the counts.
+        const GatherArgs &ga = p.gather;
+        constexpr int TP = GM_BN + 4;  // floats per staged tile row (padded against bank conflicts)
+        float *tile = reinterpret_cast<float *>(smem);
+        const uint32_t gather_epoch = *reinterpret_cast<const volatile uint32_t *>(ga.epoch_ptr) + 1u;
+        __syncthreads();  // every warp is done with the pipeline stages
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+#pragma unroll
+            for (int j = 0; j < CT; ++j) {
+                const int nl = wn * 16 * RT + i * 16 + g, ml = wm * 8 * CT + j * 8 + 2 * t;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tile[(ml + (e & 1)) * TP + nl + (e >> 1) * 8] = acc[i][j][e];
+            }
+        }
+        __syncthreads();
+        const int64_t rows_here = min((int64_t)GM_BM, p.M - m0), cols_here = min((int64_t)GM_BN, p.N - n0);
+        for (int q = 0; q < ga.world; ++q) {
+            float *base = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ga.y_peer[q]) +
+                                                    (size_t)(gather_epoch & 1u) * ga.y_stride_bytes) +
+                          m0 * ga.N_total + ga.n_offset + n0;
+            const bool vec_ok = ((reinterpret_cast<uintptr_t>(base) | ((uintptr_t)ga.N_total * 4u)) & 15u) == 0;
+            for (int idx = tid; idx < GM_BM * (GM_BN / 4); idx += GM_THREADS) {
+                const int ml = idx / (GM_BN / 4), c4 = (idx - ml * (GM_BN / 4)) * 4;
+                if (ml >= rows_here || c4 >= cols_here) continue;
+                const float *src = tile + ml * TP + c4;
+                float *dst = base + (int64_t)ml * ga.N_total + c4;
+                if (vec_ok && c4 + 3 < cols_here) {
+                    *reinterpret_cast<float4 *>(dst) = make_float4(src[0], src[1], src[2], src[3]);
+                } else {
+                    for (int e = 0; e < 4 && c4 + e < cols_here; ++e) dst[e] = src[e];
+                }
+            }
+        }
+        __syncthreads();  // all of this CTA's peer stores have been issued
+        const uint32_t cta = blockIdx.y * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y;
+        if (tid < ga.world) {
+            const uint32_t share = (uint32_t)(((uint64_t)(cta + 1) * GM_GATHER_UNITS) / n_ctas - ((uint64_t)cta * GM_GATHER_UNITS) / n_ctas);
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ga.flag_peer[tid] + ga.rank), "r"(share) : "memory");
+        }
+        if (tid == 0) {  // bookkeeping off the critical path: the last CTA advances this rank's own step number
+            const int prev = atomicAdd(ga.counter, 1);
+            if (prev == (int)n_ctas - 1) {
+                *ga.counter = 0;
+                *ga.epoch_ptr = gather_epoch;
+            }
+        }
+        return;
+    }
+
     // y[m * N + n]: thread owns rows g, g+8 and columns 2t, 2t+1 of each 16 x 8 tile
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
@@ -295,7 +354,7 @@ int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
 }  // namespace
 
 int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
-                    int order) {
+                    int order, const GatherArgs *gather) {
     if (K % GM_KCHUNK != 0) return set_error(JQ_ERR_UNSUPPORTED, "tensor-core GEMM needs K %% 256 == 0 (K = %lld)", (long long)K);
     if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
         return set_error(JQ_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned operands");
@@ -311,6 +370,8 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.order = order;
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
+    p.fault = device_fault_ptr();
+    if (gather != nullptr) p.gather = *gather;
     DeviceCaps caps;
     if (int rc = device_caps(&caps)) return rc;
     // 128 x 128 tiles unless they would leave a good part of the SMs without work

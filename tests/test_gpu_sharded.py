@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("K,N,M", [(4096, 11008, 1), (4096, 1000, 2), (8192, 4096, 1), (2048, 37, 1)])
+@pytest.mark.parametrize("K,N,M", [(4096, 11008, 1), (4096, 1000, 2), (8192, 4096, 1), (2048, 37, 1),
+                                   (1024, 256, 64), (2048, 200, 130), (512, 96, 5), (4096, 4096, 512)])
 def test_fused_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M):
     import torch
 
@@ -54,12 +55,13 @@ def test_fused_allgather_refuses_other_shapes(native_lib, cuda_device):
     c = native_lib
     bands = PeerBands(4, 64, cuda_device)
     try:
-        d_w = torch.zeros(c.q4_0_bytes(64, 256), dtype=torch.uint8, device=cuda_device)
-        x = torch.zeros((4, 256), dtype=torch.float32, device=cuda_device)
-        ws = torch.zeros(c.q8_1_bytes(256, 4), dtype=torch.uint8, device=cuda_device)
+        # K = 384 is not a multiple of 256: neither the streaming kernel nor the tensor-core GEMM takes it
+        d_w = torch.zeros(c.q4_0_bytes(64, 384), dtype=torch.uint8, device=cuda_device)
+        x = torch.zeros((4, 384), dtype=torch.float32, device=cuda_device)
+        ws = torch.zeros(c.q8_1_bytes(384, 4), dtype=torch.uint8, device=cuda_device)
         with pytest.raises(c.JqError) as ei:
             bands.linear(d_w, x, ws, 0, 64)
-        assert ei.value.status == c.ERR_UNSUPPORTED  # M = 4: gather with NCCL instead
+        assert ei.value.status == c.ERR_UNSUPPORTED  # gather with NCCL instead
     finally:
         bands.close()
 
@@ -100,8 +102,24 @@ def _two_rank_worker(rank: int, world: int, port: int, q):
             y = bands.latest().cpu().numpy()
             xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
             ok = ok and O.err_max_rel(y, O.mul_mat_ref(wq, xq, K, N, M)) <= 1e-5  # all bands, not just ours
-        ok = ok and capi.device_fault() == 0
         bands.close()
+        # a prefill batch through the tensor-core GEMM's all-gather epilogue (ragged last tile on both axes)
+        M2, N2 = 200, 1000 + 24
+        w2 = (rng.standard_normal((N2, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        wq2 = O.quantize_q4_0(w2)
+        b2, e2 = synth.shard_rows(N2, world, rank)
+        d_w2 = torch.from_numpy(np.ascontiguousarray(wq2[b2:e2])).to(dev)
+        ws2 = torch.zeros(capi.q8_1_bytes(K, M2), dtype=torch.uint8, device=dev)
+        bands2 = PeerBands(M2, N2, dev)
+        for step in range(3):
+            x = rng.standard_normal((M2, K), dtype=np.float32)
+            bands2.linear(d_w2, torch.from_numpy(x).to(dev), ws2, b2, e2 - b2)
+            bands2.wait()
+            y = bands2.latest().cpu().numpy()
+            xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+            ok = ok and O.err_max_rel(y, O.mul_mat_ref(wq2, xq, K, N2, M2)) <= 1e-5
+        bands2.close()
+        ok = ok and capi.device_fault() == 0
         q.put((rank, bool(ok)))
     except Exception as ex:
         q.put((rank, repr(ex)))
