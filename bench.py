@@ -744,7 +744,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4096)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--m", type=int, default=1, help="activation rows of the workload (1..8 for cfg2; any with --shape cfg4)")
+    ap.add_argument("--m", "--rows", dest="m", type=int, default=1, help="activation rows of the workload (1..8 for cfg2; any with --shape cfg4); under torchrun spell it --rows "
+                         "(the launcher takes --m for an abbreviation of its own options)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary shapes and the CPU baseline")
     ap.add_argument("--shape", choices=["cfg2", "cfg4"], default="cfg2",
                     help="cfg2 (default): the headline shape per GPU, weak scaling; cfg4: K=8192, N=28672 split along N over "
