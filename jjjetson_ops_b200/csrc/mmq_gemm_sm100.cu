@@ -26,8 +26,6 @@
 // summation order (the zero-point terms are added per 8 blocks rather than inside each block).
 #include <cuda_fp16.h>
 
-#include <algorithm>
-
 #include "jq_common.cuh"
 
 namespace jq {
@@ -91,7 +89,6 @@ struct GemmParams {
     int n_super;         // K / 128
     uint32_t row_bytes;  // K / 32 * 18
     int *fault;
-    int tiles_x, n_tiles;  // tiles along N, tiles in all; CTA b takes tiles b, b + gridDim.x, ...
     GatherArgs gather;   // world > 0: the tile goes to every rank's [M][N_total] buffer instead of y (all-gather epilogue)
 };
 
@@ -138,16 +135,8 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp & 1, wm = warp >> 1;  // warp tile: rows wn * 16 * RT .., columns wm * 8 * CT ..
+    const int64_t n0 = (int64_t)blockIdx.x * GM_BN, m0 = (int64_t)blockIdx.y * GM_BM;
     const int n_chunks = p.K / GM_KCHUNK;
-    // all-gather epilogue only: number of this all-gather, and arrival shares stored but not yet released
-    const uint32_t gather_epoch = p.gather.world > 0 ? *reinterpret_cast<const volatile uint32_t *>(p.gather.epoch_ptr) + 1u : 0u;
-    uint32_t pending_share = 0;
-
-    // One tile per CTA for a plain launch (grid = number of tiles).  With the all-gather epilogue the grid is
-    // one wave of persistent CTAs that walk the tiles, so that a tile's peer stores drain while the next tile
-    // is being computed.
-    for (int tile_id = blockIdx.x; tile_id < p.n_tiles; tile_id += gridDim.x) {
-    const int64_t n0 = (int64_t)(tile_id % p.tiles_x) * GM_BN, m0 = (int64_t)(tile_id / p.tiles_x) * GM_BM;
 
     float acc[RT][CT][4];  // [row tile][column tile][c0..c3]
 #pragma unroll
@@ -270,17 +259,13 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
     if (p.gather.world > 0) {
         // ---- all-gather epilogue: the tile is staged in shared memory ([column m][row n], n contiguous as
         // in y) and stored into every rank's [M][N_total] buffer through peer-mapped pointers, 16 bytes per
-        // lane and 512 contiguous bytes per tile row.  Then the CTA owes every rank the tile's share of the
-        // arrival count (system-scope release-add, cumulative over the stores the barrier ordered before it).
-        // A release has to wait until the stores before it are performed, so it is paid one tile late: by
-        // then they have had a whole tile's computation to drain over NVLink.  Nobody waits for a peer here:
-        // the consumer of the gathered output waits for the counts.
+        // lane and 512 contiguous bytes per tile row; then this CTA adds its share to the arrival count each
+        // rank keeps for this one (system-scope release, cumulative over the stores the barrier ordered
+        // before it).  Nobody waits here: the consumer of the gathered output waits for the counts.
         const GatherArgs &ga = p.gather;
         constexpr int TP = GM_BN + 4;  // floats per staged tile row (padded against bank conflicts)
         float *tile = reinterpret_cast<float *>(smem);
-        if (pending_share != 0 && tid < ga.world) {
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ga.flag_peer[tid] + ga.rank), "r"(pending_share) : "memory");
-        }
+        const uint32_t gather_epoch = *reinterpret_cast<const volatile uint32_t *>(ga.epoch_ptr) + 1u;
         __syncthreads();  // every warp is done with the pipeline stages
 #pragma unroll
         for (int i = 0; i < RT; ++i) {
@@ -310,21 +295,20 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
                 }
             }
         }
-        __syncthreads();  // all of this tile's peer stores have been issued; the stages may be refilled
-        pending_share = (uint32_t)(((uint64_t)(tile_id + 1) * GM_GATHER_UNITS) / p.n_tiles - ((uint64_t)tile_id * GM_GATHER_UNITS) / p.n_tiles);
-        if (tile_id + (int)gridDim.x >= p.n_tiles) {  // this CTA's last tile: nothing left to hide the release behind
-            if (tid < ga.world) {
-                asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ga.flag_peer[tid] + ga.rank), "r"(pending_share) : "memory");
-            }
-            if (tid == 0) {  // bookkeeping off the critical path: the last CTA advances this rank's own step number
-                const int prev = atomicAdd(ga.counter, 1);
-                if (prev == (int)gridDim.x - 1) {
-                    *ga.counter = 0;
-                    *ga.epoch_ptr = gather_epoch;
-                }
+        __syncthreads();  // all of this CTA's peer stores have been issued
+        const uint32_t cta = blockIdx.y * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y;
+        if (tid < ga.world) {
+            const uint32_t share = (uint32_t)(((uint64_t)(cta + 1) * GM_GATHER_UNITS) / n_ctas - ((uint64_t)cta * GM_GATHER_UNITS) / n_ctas);
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ga.flag_peer[tid] + ga.rank), "r"(share) : "memory");
+        }
+        if (tid == 0) {  // bookkeeping off the critical path: the last CTA advances this rank's own step number
+            const int prev = atomicAdd(ga.counter, 1);
+            if (prev == (int)n_ctas - 1) {
+                *ga.counter = 0;
+                *ga.epoch_ptr = gather_epoch;
             }
         }
-        continue;
+        return;
     }
 
     // y[m * N + n]: thread owns rows g, g+8 and columns 2t, 2t+1 of each 16 x 8 tile
@@ -341,7 +325,6 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
             }
         }
     }
-    }  // tile loop
 }
 
 }  // namespace
@@ -349,15 +332,10 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
 namespace {
 
 template <int RT, int CT>
-int run_gemm_mma(cudaStream_t st, const GemmParams &p, int sm_count) {
+int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
     using Tile = GemmTile<RT, CT>;
     const int64_t gx = (p.N + Tile::BN - 1) / Tile::BN, gy = (p.M + Tile::BM - 1) / Tile::BM;
-    if (gx * gy > (int64_t)0x7FFFFFF0) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
-    GemmParams q = p;
-    q.tiles_x = (int)gx;
-    q.n_tiles = (int)(gx * gy);
-    int64_t grid = gx * gy;
-    if (q.gather.world > 0) grid = std::min<int64_t>(grid, (int64_t)sm_count * Tile::MIN_CTAS);  // one persistent wave
+    if (gy > 65535) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
     static thread_local int attr_done_dev = -1;
     int dev = 0;
     JQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -368,7 +346,7 @@ int run_gemm_mma(cudaStream_t st, const GemmParams &p, int sm_count) {
         attr_done_dev = dev;
     }
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
-    gemm_q4_0_q8_1_mma_kernel<RT, CT><<<(unsigned)grid, GM_THREADS, Tile::SMEM, st>>>(q);
+    gemm_q4_0_q8_1_mma_kernel<RT, CT><<<dim3((unsigned)gx, (unsigned)gy), GM_THREADS, Tile::SMEM, st>>>(p);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }
@@ -398,8 +376,8 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     if (int rc = device_caps(&caps)) return rc;
     // 128 x 128 tiles unless they would leave a good part of the SMs without work
     const int64_t big_tiles = ((N + 127) / 128) * ((M + 127) / 128);
-    if (big_tiles * 5 < (int64_t)caps.sm_count * 4) return run_gemm_mma<2, 2>(st, p, caps.sm_count);
-    return run_gemm_mma<4, 4>(st, p, caps.sm_count);
+    if (big_tiles * 5 < (int64_t)caps.sm_count * 4) return run_gemm_mma<2, 2>(st, p);
+    return run_gemm_mma<4, 4>(st, p);
 }
 
 }  // namespace jq
