@@ -317,7 +317,9 @@ def run_ours(args) -> None:
     bands = None
     collective = "none"
     if world > 1:
-        collective = args.collective
+        # prefill batches: the GEMM's peer-store epilogue was measured level with NCCL (8 GPUs, cfg4 M=2048: 960 us
+        # against 950 us), so the plain all-gather stays the default there; --collective fused still selects it
+        collective = args.collective if args.collective is not None else ("fused" if M <= 2 else "nccl")
     if collective == "fused":
         from jjjetson_ops_b200.sharded import PeerBands
 
@@ -750,7 +752,7 @@ def main() -> None:
     ap.add_argument("--shape", choices=["cfg2", "cfg4"], default="cfg2",
                     help="cfg2 (default): the headline shape per GPU, weak scaling; cfg4: K=8192, N=28672 split along N over "
                          "the GPUs, strong scaling (a secondary measurement, implies --no-extras)")
-    ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
+    ap.add_argument("--collective", choices=["fused", "nccl"], default=None,
                     help="N > 1: all-gather fused into the multiply kernel (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-overlap", action="store_true",
                     help="do not let a step's weight stream start before the previous step has finished")
