@@ -65,7 +65,10 @@ typedef enum jq_kernel {
     JQ_KERNEL_GEMV_DP4A = 2, /* M <= 2: bulk-copy ring, dp4a, warp per row */
     JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
     JQ_KERNEL_GEMM_MMA = 4,  /* M > 8: tiled int8 mma.sync GEMM with per-block rescale */
-    JQ_KERNEL_GEMM_TC = 5    /* M > 8, K % 128 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
+    JQ_KERNEL_GEMM_TC = 5,   /* M > 8, K % 128 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
+    JQ_KERNEL_GEMM_F16 = 6   /* M > 8, K % 128 == 0: operands dequantised to fp16, tcgen05.mma.kind::f16, fp32 accumulation.
+                                Rounds every scaled operand to fp16 (about 3e-4 of the largest output); never picked
+                                by JQ_KERNEL_AUTO */
 } jq_kernel;
 
 /* Process-wide switches. */

@@ -29,11 +29,12 @@ CUDA_SOURCES = [
     "mmq_gemv_sm100.cu",
     "mmq_gemm_sm100.cu",
     "mmq_gemm_tc_sm100.cu",
+    "mmq_gemm_f16_sm100.cu",
     "jq_capi.cu",
     "ref_compat.cpp",
     "weights_io.cpp",
 ]
-HEADERS = ["jq_common.cuh", os.path.join(INCLUDE_DIR, "jq_b200.h"), os.path.join(INCLUDE_DIR, "jq_weights_io.h")]
+HEADERS = ["jq_common.cuh", "tc_common.cuh", os.path.join(INCLUDE_DIR, "jq_b200.h"), os.path.join(INCLUDE_DIR, "jq_weights_io.h")]
 BINDINGS = {"q8_1_me": "q8_1_binding.cpp", "mm_q4_0_q8_1_me": "mm_q4_0_q8_1_binding.cpp"}
 
 NVCC_FLAGS = [

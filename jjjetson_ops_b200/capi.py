@@ -19,7 +19,7 @@ OK = 0
 ERR_INVALID_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_TOO_LARGE = range(1, 8)
 ORDER_KSUPER_COL, ORDER_COL_KSUPER = 0, 1
 S_SUM_X, S_D_SUM_Q = 0, 1
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV_DP4A, KERNEL_GEMV_MMA, KERNEL_GEMM_MMA, KERNEL_GEMM_TC = range(6)
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV_DP4A, KERNEL_GEMV_MMA, KERNEL_GEMM_MMA, KERNEL_GEMM_TC, KERNEL_GEMM_F16 = range(7)
 KERNEL_NAMES = {
     KERNEL_AUTO: "auto",
     KERNEL_GENERIC: "generic",
@@ -27,6 +27,7 @@ KERNEL_NAMES = {
     KERNEL_GEMV_MMA: "gemv_mma",
     KERNEL_GEMM_MMA: "gemm_mma",
     KERNEL_GEMM_TC: "gemm_tc",
+    KERNEL_GEMM_F16: "gemm_f16",
 }
 
 Q4_BYTES = 18

@@ -139,6 +139,7 @@ int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *
         case JQ_KERNEL_GEMV_MMA: return launch_gemv_mma(st, d_w, d_xq, nullptr, nullptr, d_y, K, N, M, order, 0);
         case JQ_KERNEL_GEMM_MMA: return launch_gemm_mma(st, d_w, d_xq, d_y, K, N, M, order);
         case JQ_KERNEL_GEMM_TC: return launch_gemm_tc(st, d_w, d_xq, d_y, K, N, M, order);
+        case JQ_KERNEL_GEMM_F16: return launch_gemm_f16(st, d_w, d_xq, d_y, K, N, M, order);
         case JQ_KERNEL_AUTO: break;
         default: return set_error(JQ_ERR_INVALID_ARG, "unknown kernel family %d", kernel);
     }

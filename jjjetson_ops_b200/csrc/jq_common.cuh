@@ -108,6 +108,8 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
                     int64_t N, int64_t M, int order, const GatherArgs *gather = nullptr);
 int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                    int64_t N, int64_t M, int order);
+int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
+                    int64_t N, int64_t M, int order);
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__

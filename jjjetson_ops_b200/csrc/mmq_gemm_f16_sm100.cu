@@ -1,0 +1,379 @@
+// Prefill-regime multiply with the block scales folded into the operands: both matrices are
+// dequantised to fp16 on their way into shared memory and multiplied by tcgen05.mma.kind::f16 with
+// fp32 accumulation in tensor memory, so nothing is drained or rescaled between blocks.
+//
+// Work to replace: q4_0_q8_1_mat_mul_kernel (reference src/cuda/mm_q4_0_q8_1.cu:164-289) for large
+// batches.  The reference adds, per 32-wide block, d4 * (sumi * d8 - 8 * s8) (mm_q4_0_q8_1.cu:92).
+// With sumi = sum(q4 * q8) that is
+//     sum_i ((q4_i - 8) * d4) * (q8_i * d8)   +   (-8 * d4) * (s8 - d8 * sum_i q8_i)
+// The first term is a plain product of two fp16 matrices B[n][k] = (q4 - 8) * d4 and
+// A[m][k] = q8 * d8; the second is rank one per block and joins the same accumulator as one more
+// MMA per 128 values of K (operands s8 - d8 * sum(q8), computed in fp32, and -8 * d4, exact).  It
+// vanishes up to the rounding of s8 when the quantizer stored s = d * sum(q), and carries the
+// quantisation residue when it stored the sum of the unquantised values.
+//
+// Precision.  q4 - 8 and q8 are exact in fp16; their products with the fp16 scales are rounded once
+// to fp16 (relative error <= 2^-11 per element), the accumulation is fp32.  The result differs from
+// the reference formula by about 3e-4 of the largest output on the configurations this kernel is
+// measured on, where the integer kernels differ by 1e-6: it meets the 1e-3 bound against the
+// dequantised product but not bit-level parity of the per-block sums, which is why it is selected
+// by name only.  Operands must stay inside fp16's range: |x| <= 65504 for the activations, and
+// scales whose products are not subnormal (|d| * |q| >= 6.1e-5) keep full precision.
+//
+// A CTA owns a 128 (activation columns) x 128 (weight rows) tile of Y.  K advances in stages of 128
+// values (one Q8_1 block per column, four Q4_0 blocks per row):
+//   warps 0-3   one weight row per thread: 72 bytes loaded one stage ahead into registers, nibbles
+//               turned into fp16 by the magic-number trick (0x6400 | q is 1024 + q), scaled, stored
+//               as eight 128 x 16 operand tiles in the tensor core's canonical K-major layout.
+//   warps 4-7   one activation column per thread: 144 bytes, int8 -> fp16 the same way, scaled.
+//   warp 8      allocates tensor memory and issues, per stage, the rank-one MMA and eight
+//               128 x 128 x 16 MMAs; tcgen05.commit hands the stage back to the producers.
+// After the last stage warps 0-7 read the 128 x 128 fp32 accumulator and store it.
+// Every mbarrier wait is a bounded poll; a wait that runs out sets the device fault word, and every
+// warp still reaches the common exit where tensor memory is released.
+#include "tc_common.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int HF_BM = 128;    // activation columns per CTA (MMA M, TMEM lanes)
+constexpr int HF_BN = 128;    // weight rows per CTA (MMA N, TMEM columns)
+constexpr int HF_KT = 8;      // operand tiles of 16 values of K per stage
+constexpr int HF_STAGES = 3;
+constexpr int HF_A_OFF = 0;                           // activations: HF_KT tiles
+constexpr int HF_B_OFF = HF_KT * TC_TILE;             // weights:     HF_KT tiles
+constexpr int HF_ZA_OFF = 2 * HF_KT * TC_TILE;        // fp16 (s8 - d8 * sum q8)[128 columns][16] (4 blocks + 12 zeros)
+constexpr int HF_ZB_OFF = HF_ZA_OFF + TC_TILE;        // fp16 (-8 * d4)[128 rows][16]
+constexpr int HF_STAGE_BYTES = HF_ZB_OFF + TC_TILE;
+constexpr int HF_BAR_OFF = HF_STAGES * HF_STAGE_BYTES;
+constexpr int HF_SMEM_BYTES = HF_BAR_OFF + 128;
+constexpr int HF_PROD_WARPS = 8;
+constexpr int HF_MMA_WARP = 8;
+constexpr int HF_THREADS = 9 * 32;
+constexpr uint32_t HF_TMEM_COLS = 128;
+static_assert(HF_SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
+
+// fp16 constants, two per word
+constexpr uint32_t H2_MAGIC_BYTES = 0x64646464u;  // high byte of 1024 + v for an 8-bit v
+constexpr uint32_t H2_LOW_NIBBLE = 0x640F640Fu;   // keeps 1024 + (v & 15)
+constexpr uint32_t H2_HIGH_NIBBLE = 0x64F064F0u;  // keeps 1024 + 16 * (v >> 4)
+constexpr uint32_t H2_1032 = 0x64086408u;
+constexpr uint32_t H2_1152 = 0x64806480u;
+constexpr uint32_t H2_SIXTEENTH = 0x2C002C00u;
+constexpr uint32_t H2_MINUS_72 = 0xD480D480u;
+
+struct HfParams {
+    const uint8_t *w;
+    const uint8_t *xq;
+    float *y;
+    int *fault;
+    int64_t N, M;
+    int K, order, n_super;
+    uint32_t row_bytes;
+};
+
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
+
+// (v - offset) * scale: the subtraction is exact, the product is rounded once
+__device__ __forceinline__ uint32_t h2_sub_scale(uint32_t v, uint32_t offset, __half2 scale) {
+    return as_u32(__hmul2(__hsub2(as_h2(v), as_h2(offset)), scale));
+}
+// (v / 16 - 72) * scale for v = 1024 + 16 * q: the fma is exact (q - 8), the product is rounded once
+__device__ __forceinline__ uint32_t h2_high_scale(uint32_t v, __half2 scale) {
+    return as_u32(__hmul2(__hfma2(as_h2(v), as_h2(H2_SIXTEENTH), as_h2(H2_MINUS_72)), scale));
+}
+
+// One weight row of a stage (72 bytes = 18 words in registers) -> its 128 values (q4 - 8) * d4 in
+// the eight weight tiles, and the row of the rank-one operand.
+__device__ __forceinline__ void hf_convert_weight_row(uint32_t st, int r, const uint2 (&wv)[9]) {
+    const uint32_t *ww = reinterpret_cast<const uint32_t *>(wv);
+    uint32_t zb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t q[4], dbits;
+        if ((j & 1) == 0) {  // block starts on a word boundary: [d | q0 q1] [q2..q5] ...
+            const int w0 = (j / 2) * 9;
+            dbits = ww[w0] & 0xFFFFu;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) q[t] = __funnelshift_r(ww[w0 + t], ww[w0 + t + 1], 16);
+        } else {  // block starts in the middle of a word
+            const int w0 = (j / 2) * 9 + 4;
+            dbits = ww[w0] >> 16;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) q[t] = ww[w0 + 1 + t];
+        }
+        zb[j] = dbits;
+        const __half2 d2 = as_h2(dbits | (dbits << 16));
+        // byte i of the block holds value i (low nibble) and value i + 16 (high nibble): the low nibbles
+        // fill tile 2j, the high nibbles tile 2j + 1; bytes 0-7 are K-chunk 0 of a tile, bytes 8-15 chunk 1
+        const uint32_t tile_lo = st + HF_B_OFF + (2 * j) * TC_TILE, tile_hi = tile_lo + TC_TILE;
+#pragma unroll
+        for (int kc = 0; kc < 2; ++kc) {
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const uint32_t p01 = __byte_perm(q[2 * kc + t], H2_MAGIC_BYTES, 0x4140);  // 1024 + byte 0 | 1024 + byte 1
+                const uint32_t p23 = __byte_perm(q[2 * kc + t], H2_MAGIC_BYTES, 0x4342);
+                lo[2 * t] = h2_sub_scale(p01 & H2_LOW_NIBBLE, H2_1032, d2);
+                lo[2 * t + 1] = h2_sub_scale(p23 & H2_LOW_NIBBLE, H2_1032, d2);
+                hi[2 * t] = h2_high_scale(p01 & H2_HIGH_NIBBLE, d2);
+                hi[2 * t + 1] = h2_high_scale(p23 & H2_HIGH_NIBBLE, d2);
+            }
+            sts_v4(tile_lo + tile_off(r, kc), make_uint4(lo[0], lo[1], lo[2], lo[3]));
+            sts_v4(tile_hi + tile_off(r, kc), make_uint4(hi[0], hi[1], hi[2], hi[3]));
+        }
+    }
+    // -8 * d4 as fp16 (exact: a power of two; finite unless |d4| > 8188); the 12 padding values stay zero
+    const __half2 m8 = __float2half2_rn(-8.0f);
+    sts_v4(st + HF_ZB_OFF + tile_off(r, 0),
+           make_uint4(as_u32(__hmul2(as_h2(zb[0] | (zb[1] << 16)), m8)), as_u32(__hmul2(as_h2(zb[2] | (zb[3] << 16)), m8)), 0u, 0u));
+}
+
+// One activation column of a stage (a 144-byte block in registers) -> its 128 values q8 * d8 in the
+// eight activation tiles, and the column of the rank-one operand.
+__device__ __forceinline__ void hf_convert_activation_col(uint32_t st, int r, const uint4 (&xv)[9]) {
+    const uint32_t dsw[4] = {xv[0].x, xv[0].y, xv[0].z, xv[0].w};
+    float zc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t dbits = dsw[j] & 0xFFFFu;
+        const __half2 d2 = as_h2(dbits | (dbits << 16));
+        int isum = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // values 16h .. 16h + 15 of the block: tile 2j + h
+            const uint4 v = xv[1 + 2 * j + h];
+            const uint32_t wq[4] = {v.x, v.y, v.z, v.w};
+            uint32_t a[8];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                isum = __dp4a((int)wq[t], 0x01010101, isum);
+                const uint32_t wu = wq[t] ^ 0x80808080u;  // q + 128 in 1..255
+                a[2 * t] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4140), H2_1152, d2);
+                a[2 * t + 1] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4342), H2_1152, d2);
+            }
+            const uint32_t tile = st + HF_A_OFF + (2 * j + h) * TC_TILE;
+            sts_v4(tile + tile_off(r, 0), make_uint4(a[0], a[1], a[2], a[3]));
+            sts_v4(tile + tile_off(r, 1), make_uint4(a[4], a[5], a[6], a[7]));
+        }
+        // what the stored s differs by from d8 * sum(q8); d8 * isum is exact in fp32
+        zc[j] = fmaf(-half_bits_to_float(dbits), (float)isum, half_bits_to_float(dsw[j] >> 16));
+    }
+    sts_v4(st + HF_ZA_OFF + tile_off(r, 0),
+           make_uint4(as_u32(__floats2half2_rn(zc[0], zc[1])), as_u32(__floats2half2_rn(zc[2], zc[3])), 0u, 0u));
+}
+
+__global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const HfParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + HF_BAR_OFF);
+    uint64_t *stage_full = bars;                  // [HF_STAGES] producer warps -> MMA warp
+    uint64_t *stage_empty = bars + HF_STAGES;     // [HF_STAGES] MMA completion -> producers
+    uint64_t *acc_full = bars + 2 * HF_STAGES;    // all MMAs complete -> epilogue
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    static_assert((2 * HF_STAGES + 1) * 8 + 4 <= 128, "barrier block too small");
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t n0 = (int64_t)blockIdx.x * HF_BN, m0 = (int64_t)blockIdx.y * HF_BM;
+    const int n_chunks = p.K / SUPER;
+
+    if (tid == 0) {
+        for (int s = 0; s < HF_STAGES; ++s) {
+            mbar_init(&stage_full[s], HF_PROD_WARPS);
+            mbar_init(&stage_empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        fence_mbar_init();
+    }
+    if (tid < 128) {
+        // the zero half (K = 8..15) of every stage's rank-one operands
+        for (int s = 0; s < HF_STAGES; ++s) {
+            sts_v4(sbase + s * HF_STAGE_BYTES + HF_ZA_OFF + tile_off(tid, 1), make_uint4(0u, 0u, 0u, 0u));
+            sts_v4(sbase + s * HF_STAGE_BYTES + HF_ZB_OFF + tile_off(tid, 1), make_uint4(0u, 0u, 0u, 0u));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // read by the tensor core
+    }
+    if (warp == HF_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(HF_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+
+    if (warp < HF_PROD_WARPS) {
+        // =============================== producers, then epilogue ==============================
+        bool alive = true;
+        int s = 0;
+        uint32_t round = 0;  // how often the ring has wrapped
+        // the whole warp takes the same decision, so that its aligned instructions stay convergent
+        auto stage_is_free = [&]() {
+            const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
+            return __all_sync(0xFFFFFFFFu, ok) != 0;
+        };
+        auto publish_and_advance = [&]() {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&stage_full[s]);
+            if (++s == HF_STAGES) {
+                s = 0;
+                ++round;
+            }
+        };
+        if (warp < 4) {
+            // rows past the end are clamped: their results are never stored
+            const uint8_t *wp = p.w + min(n0 + tid, p.N - 1) * (int64_t)p.row_bytes;
+            uint2 cur[9], nxt[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) cur[i] = __ldg(reinterpret_cast<const uint2 *>(wp) + i);
+#pragma unroll 1
+            for (int c = 0; c < n_chunks; ++c) {
+                if (c + 1 < n_chunks) {
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint2 *>(wp + (size_t)(c + 1) * (4 * Q4_BYTES)) + i);
+                }
+                if (round > 0 && !stage_is_free()) {
+                    alive = false;
+                    break;
+                }
+                hf_convert_weight_row(sbase + s * HF_STAGE_BYTES, tid, cur);
+                publish_and_advance();
+#pragma unroll
+                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+            }
+        } else {
+            const int col = tid - 128;
+            const int64_t m = min(m0 + col, p.M - 1);  // clamped like the rows
+            uint4 cur[9], nxt[9];
+            {
+                const uint4 *xb = reinterpret_cast<const uint4 *>(p.xq + q8_block_index(0, m, p.n_super, p.M, p.order) * Q8_BYTES);
+#pragma unroll
+                for (int i = 0; i < 9; ++i) cur[i] = __ldg(xb + i);
+            }
+#pragma unroll 1
+            for (int c = 0; c < n_chunks; ++c) {
+                if (c + 1 < n_chunks) {
+                    const uint4 *xb = reinterpret_cast<const uint4 *>(p.xq + q8_block_index(c + 1, m, p.n_super, p.M, p.order) * Q8_BYTES);
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(xb + i);
+                }
+                if (round > 0 && !stage_is_free()) {
+                    alive = false;
+                    break;
+                }
+                hf_convert_activation_col(sbase + s * HF_STAGE_BYTES, col, cur);
+                publish_and_advance();
+#pragma unroll
+                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+            }
+        }
+
+        // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 64 of the 128 weight rows
+        if (alive && __all_sync(0xFFFFFFFFu, mbar_wait_bounded(acc_full, 0u, p.fault))) {
+            tc_fence_after();
+            const int half = warp >> 2;
+            const int row = (warp & 3) * 32 + lane;
+            const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 64);
+            const int64_t m = m0 + row;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t v[32];
+                tmem_ld32_nowait(t_lane + h * 32, v);
+                tmem_ld_wait();
+                if (m < p.M) {
+                    const int64_t n = n0 + half * 64 + h * 32;
+                    float *dst = p.y + m * p.N + n;
+                    const int64_t n_left = p.N - n;
+                    if (n_left >= 32 && ((uintptr_t)dst & 15u) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            reinterpret_cast<float4 *>(dst)[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < n_left) dst[j] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // =============================== MMA issuer ============================================
+        const uint32_t idesc = tc_idesc_f16(HF_BM, HF_BN);
+        int s = 0;
+        uint32_t parity = 0;
+        bool alive = true;
+        for (int c = 0; c < n_chunks; ++c) {
+            if (!mbar_wait_bounded(&stage_full[s], parity, p.fault)) {
+                alive = false;
+                break;
+            }
+            const uint32_t st = sbase + s * HF_STAGE_BYTES;
+            tc_fence_after();
+            tc_mma_f16(tmem, tc_desc(st + HF_ZA_OFF), tc_desc(st + HF_ZB_OFF), idesc, c > 0 ? 1u : 0u);
+#pragma unroll
+            for (int t = 0; t < HF_KT; ++t) {
+                tc_mma_f16(tmem, tc_desc(st + HF_A_OFF + t * TC_TILE), tc_desc(st + HF_B_OFF + t * TC_TILE), idesc, 1u);
+            }
+            tc_commit(&stage_empty[s]);  // the stage may be overwritten once these MMAs have read it
+            if (++s == HF_STAGES) {
+                s = 0;
+                parity ^= 1u;
+            }
+        }
+        if (alive) tc_commit(acc_full);
+    }
+
+    // common exit: nobody touches tensor memory any more, release it
+    tc_fence_before();
+    __syncthreads();
+    if (warp == HF_MMA_WARP) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(HF_TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
+                    int order) {
+    if (K % SUPER != 0) return set_error(JQ_ERR_UNSUPPORTED, "fp16-operand tcgen05 GEMM needs K %% 128 == 0 (K = %lld)", (long long)K);
+    if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
+        return set_error(JQ_ERR_UNSUPPORTED, "fp16-operand tcgen05 GEMM needs 16-byte aligned operands");
+    if (N == 0 || M == 0) return JQ_OK;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    if (caps.cc / 10 != 10) return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 needs an sm_100-class device");
+    const int64_t gx = (N + HF_BN - 1) / HF_BN, gy = (M + HF_BM - 1) / HF_BM;
+    if (gy > 65535 || K > (1 << 24)) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tcgen05 GEMM");
+    HfParams p{};
+    p.w = static_cast<const uint8_t *>(d_w);
+    p.xq = static_cast<const uint8_t *>(d_xq);
+    p.y = d_y;
+    p.fault = device_fault_ptr();
+    p.N = N;
+    p.M = M;
+    p.K = (int)K;
+    p.order = order;
+    p.n_super = (int)(K / SUPER);
+    p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
+    static thread_local int attr_done_dev = -1;
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (attr_done_dev != dev) {
+        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HF_SMEM_BYTES));
+        attr_done_dev = dev;
+    }
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
+    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy), HF_THREADS, HF_SMEM_BYTES, st>>>(p);
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
+}  // namespace jq

@@ -41,7 +41,7 @@
 //
 // Every mbarrier wait is a bounded poll; a wait that runs out sets the device fault word, and every
 // warp still reaches the common exit where TMEM is released.
-#include "jq_common.cuh"
+#include "tc_common.cuh"
 
 namespace jq {
 
@@ -52,7 +52,6 @@ constexpr int TC_BN = 128;   // weight rows per CTA (MMA N, TMEM columns)
 constexpr int TC_KB = 4;     // 32-wide blocks per pipeline stage (one Q8_1 super-block of K)
 constexpr int TC_KB_LOG2 = 2;
 constexpr int TC_STAGES = 4;
-constexpr int TC_TILE = 4096;                      // one 128 x 32-byte int8 operand tile
 constexpr int TC_A_OFF = 0;                        // activations: TC_KB tiles
 constexpr int TC_B_OFF = TC_KB * TC_TILE;          // weights:     TC_KB tiles
 constexpr int TC_ZA_OFF = 2 * TC_KB * TC_TILE;     // fp16 s8[128 columns][16] (4 blocks + 12 zeros), canonical layout
@@ -76,7 +75,6 @@ static_assert(8 * TC_DRAIN_REGS + 4 * TC_PROD_REGS <= 12 * 168, "setmaxnreg budg
 constexpr int TC_ACC_BUFS = 3;                     // integer accumulator buffers of 128 columns
 constexpr uint32_t TC_ZP_COL = TC_ACC_BUFS * TC_BN;  // fp32 zero-point accumulator, 128 columns
 constexpr uint32_t TC_TMEM_COLS = 512;
-constexpr uint32_t TC_LBO = 128, TC_SBO = 256;     // canonical layout strides (bytes)
 constexpr uint32_t TC_BIAS_BYTE = 0x40u;           // 32 * 64 * 64 = 2^17
 constexpr int TC_BIAS_LOG2 = 17;
 constexpr int TC_D8_SHIFT = 100;                   // d8 is carried as d8 * 2^100 ...
@@ -117,41 +115,8 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
     return d;
 }
 
-__device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 32 lanes x 32 consecutive columns of 32-bit accumulator -> registers (completion: tcgen05.wait::ld)
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
-        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-// shared-memory matrix descriptor: K-major, no swizzle, version 1
-__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(TC_LBO >> 4) << 16) | ((uint64_t)(TC_SBO >> 4) << 32) |
-           ((uint64_t)1 << 46);
-}
-
-// canonical position of the 16-byte K-chunk kc (0/1) of row r inside a 128 x 32-byte tile
-__device__ __forceinline__ uint32_t tile_off(int r, int kc) {
-    return (uint32_t)((r >> 3) * TC_SBO + kc * TC_LBO + (r & 7) * 16);
 }
 
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
