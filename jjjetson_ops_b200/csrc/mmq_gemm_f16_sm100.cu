@@ -40,19 +40,30 @@ namespace {
 constexpr int HF_BM = 128;    // activation columns per CTA (MMA M, TMEM lanes)
 constexpr int HF_BN = 128;    // weight rows per CTA (MMA N, TMEM columns)
 constexpr int HF_KT = 8;      // operand tiles of 16 values of K per stage
-constexpr int HF_STAGES = 3;
+constexpr int HF_STAGES = 2;  // fp16 operand stages
 constexpr int HF_A_OFF = 0;                           // activations: HF_KT tiles
 constexpr int HF_B_OFF = HF_KT * TC_TILE;             // weights:     HF_KT tiles
 constexpr int HF_ZA_OFF = 2 * HF_KT * TC_TILE;        // fp16 (s8 - d8 * sum q8)[128 columns][16] (4 blocks + 12 zeros)
 constexpr int HF_ZB_OFF = HF_ZA_OFF + TC_TILE;        // fp16 (-8 * d4)[128 rows][16]
 constexpr int HF_STAGE_BYTES = HF_ZB_OFF + TC_TILE;
-constexpr int HF_BAR_OFF = HF_STAGES * HF_STAGE_BYTES;
+// ring of quantized bytes as they lie in global memory: 128 rows x 72 bytes of weights, then 128 blocks of activations
+constexpr int HF_RAW_STAGES = 3;
+constexpr int HF_W_CHUNK = 4 * Q4_BYTES;              // 72 bytes of a weight row per stage
+constexpr int HF_RAW_X_OFF = 128 * HF_W_CHUNK;
+constexpr int HF_RAW_BYTES = HF_RAW_X_OFF + 128 * Q8_BYTES;
+constexpr int HF_RAW_OFF = HF_STAGES * HF_STAGE_BYTES;
+constexpr int HF_BAR_OFF = HF_RAW_OFF + HF_RAW_STAGES * HF_RAW_BYTES;
 constexpr int HF_SMEM_BYTES = HF_BAR_OFF + 128;
+constexpr int HF_COPIES = 128 * 9;                    // copies per operand and stage: 8 bytes each for weights, 16 for activations
+constexpr int HF_PROD_THREADS = 256;
+constexpr int HF_COPY_ITERS = (HF_COPIES + HF_PROD_THREADS - 1) / HF_PROD_THREADS;
+constexpr int HF_OUT_PITCH = 33;                      // words per row of a warp's 32 x 32 output staging block
 constexpr int HF_PROD_WARPS = 8;
 constexpr int HF_MMA_WARP = 8;
 constexpr int HF_THREADS = 9 * 32;
 constexpr uint32_t HF_TMEM_COLS = 128;
 static_assert(HF_SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
+static_assert(8 * 32 * HF_OUT_PITCH * 4 <= HF_STAGE_BYTES, "output staging does not fit in an operand stage");
 
 // fp16 constants, two per word
 constexpr uint32_t H2_MAGIC_BYTES = 0x64646464u;  // high byte of 1024 + v for an 8-bit v
@@ -72,6 +83,13 @@ struct HfParams {
     int K, order, n_super;
     uint32_t row_bytes;
 };
+
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
@@ -207,100 +225,106 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
 
     if (warp < HF_PROD_WARPS) {
         // =============================== producers, then epilogue ==============================
-        bool alive = true;
-        int s = 0;
-        uint32_t round = 0;  // how often the ring has wrapped
-        // the whole warp takes the same decision, so that its aligned instructions stay convergent
-        auto stage_is_free = [&]() {
-            const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
-            return __all_sync(0xFFFFFFFFu, ok) != 0;
+        // Raw ring.  The 1152 8-byte pieces of the weight rows and the 1152 16-byte pieces of the activation blocks
+        // of a stage are dealt to the 256 threads in memory order, so that one warp instruction touches a few
+        // cache lines instead of 32; a stage later, every source lies a fixed step further.
+        const uint8_t *w_src[HF_COPY_ITERS], *x_src[HF_COPY_ITERS];
+        uint32_t w_dst[HF_COPY_ITERS], x_dst[HF_COPY_ITERS];
+#pragma unroll
+        for (int i = 0; i < HF_COPY_ITERS; ++i) {
+            const int idx = min(tid + i * HF_PROD_THREADS, HF_COPIES - 1);
+            const int r = idx / 9, piece = idx - 9 * r;
+            // rows and columns past the end are clamped: their results are never stored
+            w_src[i] = p.w + min(n0 + r, p.N - 1) * (int64_t)p.row_bytes + piece * 8;
+            w_dst[i] = (uint32_t)(r * HF_W_CHUNK + piece * 8);
+            x_src[i] = p.xq + q8_block_index(0, min(m0 + r, p.M - 1), p.n_super, p.M, p.order) * Q8_BYTES + piece * 16;
+            x_dst[i] = (uint32_t)(HF_RAW_X_OFF + r * Q8_BYTES + piece * 16);
+        }
+        const int64_t x_step = (p.order == JQ_ORDER_KSUPER_COL ? p.M : (int64_t)1) * Q8_BYTES;
+        int load_slot = 0;
+        auto issue_stage = [&](int c) {  // stage c -> the next raw slot; always one commit group per call
+            if (c < n_chunks) {
+                const uint32_t raw = sbase + HF_RAW_OFF + load_slot * HF_RAW_BYTES;
+#pragma unroll
+                for (int i = 0; i < HF_COPY_ITERS; ++i) {
+                    if (tid + i * HF_PROD_THREADS < HF_COPIES) {
+                        cp_async8(raw + w_dst[i], w_src[i] + (int64_t)c * HF_W_CHUNK);
+                        cp_async16(raw + x_dst[i], x_src[i] + c * x_step);
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            load_slot = load_slot == HF_RAW_STAGES - 1 ? 0 : load_slot + 1;
         };
-        auto publish_and_advance = [&]() {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&stage_full[s]);
+
+        bool alive = true;
+        int s = 0, raw_slot = 0;
+        uint32_t round = 0;  // how often the operand ring has wrapped
+        issue_stage(0);
+        issue_stage(1);
+#pragma unroll 1
+        for (int c = 0; c < n_chunks; ++c) {
+            // Stage c has landed for this thread; after the barrier, for every thread.  The barrier also says that
+            // everybody has finished reading stage c - 1, whose slot stage c + 2 is about to overwrite.  A warp that
+            // gave up on a wait keeps coming here, so that the barrier always completes.
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            named_bar_sync(1, HF_PROD_THREADS);
+            issue_stage(c + 2);
+            if (alive && round > 0) {
+                // the whole warp takes the same decision, so that its aligned instructions stay convergent
+                const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
+                alive = __all_sync(0xFFFFFFFFu, ok) != 0;
+            }
+            if (alive) {
+                const uint32_t st = sbase + s * HF_STAGE_BYTES, raw = sbase + HF_RAW_OFF + raw_slot * HF_RAW_BYTES;
+                if (warp < 4) {  // one weight row per thread
+                    uint2 v[9];
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) v[i] = lds_v2(raw + tid * HF_W_CHUNK + i * 8);
+                    hf_convert_weight_row(st, tid, v);
+                } else {  // one activation column per thread
+                    const int col = tid - 128;
+                    uint4 v[9];
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) v[i] = lds_v4(raw + HF_RAW_X_OFF + col * Q8_BYTES + i * 16);
+                    hf_convert_activation_col(st, col, v);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&stage_full[s]);
+            }
             if (++s == HF_STAGES) {
                 s = 0;
                 ++round;
             }
-        };
-        if (warp < 4) {
-            // rows past the end are clamped: their results are never stored
-            const uint8_t *wp = p.w + min(n0 + tid, p.N - 1) * (int64_t)p.row_bytes;
-            uint2 cur[9], nxt[9];
-#pragma unroll
-            for (int i = 0; i < 9; ++i) cur[i] = __ldg(reinterpret_cast<const uint2 *>(wp) + i);
-#pragma unroll 1
-            for (int c = 0; c < n_chunks; ++c) {
-                if (c + 1 < n_chunks) {
-#pragma unroll
-                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint2 *>(wp + (size_t)(c + 1) * (4 * Q4_BYTES)) + i);
-                }
-                if (round > 0 && !stage_is_free()) {
-                    alive = false;
-                    break;
-                }
-                hf_convert_weight_row(sbase + s * HF_STAGE_BYTES, tid, cur);
-                publish_and_advance();
-#pragma unroll
-                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
-            }
-        } else {
-            const int col = tid - 128;
-            const int64_t m = min(m0 + col, p.M - 1);  // clamped like the rows
-            uint4 cur[9], nxt[9];
-            {
-                const uint4 *xb = reinterpret_cast<const uint4 *>(p.xq + q8_block_index(0, m, p.n_super, p.M, p.order) * Q8_BYTES);
-#pragma unroll
-                for (int i = 0; i < 9; ++i) cur[i] = __ldg(xb + i);
-            }
-#pragma unroll 1
-            for (int c = 0; c < n_chunks; ++c) {
-                if (c + 1 < n_chunks) {
-                    const uint4 *xb = reinterpret_cast<const uint4 *>(p.xq + q8_block_index(c + 1, m, p.n_super, p.M, p.order) * Q8_BYTES);
-#pragma unroll
-                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(xb + i);
-                }
-                if (round > 0 && !stage_is_free()) {
-                    alive = false;
-                    break;
-                }
-                hf_convert_activation_col(sbase + s * HF_STAGE_BYTES, col, cur);
-                publish_and_advance();
-#pragma unroll
-                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
-            }
+            raw_slot = raw_slot == HF_RAW_STAGES - 1 ? 0 : raw_slot + 1;
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
 
-        // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 64 of the 128 weight rows
+        // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 64 of the 128 weight rows,
+        // and turns each 32 x 32 block around in shared memory (the operand stages are free by now) so that a
+        // store instruction writes 128 contiguous bytes of one output row
         if (alive && __all_sync(0xFFFFFFFFu, mbar_wait_bounded(acc_full, 0u, p.fault))) {
             tc_fence_after();
             const int half = warp >> 2;
-            const int row = (warp & 3) * 32 + lane;
             const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 64);
-            const int64_t m = m0 + row;
+            const uint32_t stage_blk = sbase + warp * (32 * HF_OUT_PITCH * 4);
+            const int64_t m_first = m0 + (warp & 3) * 32;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 uint32_t v[32];
                 tmem_ld32_nowait(t_lane + h * 32, v);
                 tmem_ld_wait();
-                if (m < p.M) {
-                    const int64_t n = n0 + half * 64 + h * 32;
-                    float *dst = p.y + m * p.N + n;
-                    const int64_t n_left = p.N - n;
-                    if (n_left >= 32 && ((uintptr_t)dst & 15u) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            reinterpret_cast<float4 *>(dst)[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < n_left) dst[j] = __uint_as_float(v[j]);
-                        }
-                    }
+                for (int j = 0; j < 32; ++j) sts_f32(stage_blk + (lane * HF_OUT_PITCH + j) * 4, __uint_as_float(v[j]));
+                __syncwarp();
+                const int64_t n = n0 + half * 64 + h * 32 + lane;
+#pragma unroll 8
+                for (int rr = 0; rr < 32; ++rr) {
+                    const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
+                    if (m_first + rr < p.M && n < p.N) p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
                 }
+                __syncwarp();
             }
         }
     } else if (lane == 0) {
