@@ -40,10 +40,9 @@ namespace {
 constexpr int HF_BM = 128;    // activation columns per CTA (MMA M, TMEM lanes)
 constexpr int HF_BN = 128;    // weight rows per CTA (MMA N, TMEM columns)
 constexpr int HF_KT = 8;      // operand tiles of 16 values of K per stage
-constexpr int HF_STAGES = 2;  // fp16 operand stages
-constexpr int HF_A_OFF = 0;                           // activations: HF_KT tiles
-constexpr int HF_B_OFF = HF_KT * TC_TILE;             // weights:     HF_KT tiles
-constexpr int HF_ZA_OFF = 2 * HF_KT * TC_TILE;        // fp16 (s8 - d8 * sum q8)[128 columns][16] (4 blocks + 12 zeros)
+constexpr int HF_STAGES = 3;  // fp16 operand stages: weights in shared memory, activations in tensor memory
+constexpr int HF_B_OFF = 0;                           // weights: HF_KT tiles
+constexpr int HF_ZA_OFF = HF_KT * TC_TILE;            // fp16 (s8 - d8 * sum q8)[128 columns][16] (4 blocks + 12 zeros)
 constexpr int HF_ZB_OFF = HF_ZA_OFF + TC_TILE;        // fp16 (-8 * d4)[128 rows][16]
 constexpr int HF_STAGE_BYTES = HF_ZB_OFF + TC_TILE;
 // ring of quantized bytes as they lie in global memory: 128 rows x 72 bytes of weights, then 128 blocks of activations
@@ -61,7 +60,11 @@ constexpr int HF_OUT_PITCH = 33;                      // words per row of a warp
 constexpr int HF_PROD_WARPS = 8;
 constexpr int HF_MMA_WARP = 8;
 constexpr int HF_THREADS = 9 * 32;
-constexpr uint32_t HF_TMEM_COLS = 128;
+// Tensor memory: the fp32 accumulator in columns 0..127, then per stage the activation operand: lane = activation
+// column, 64 columns of two fp16 values = the 128 values of K in order
+constexpr uint32_t HF_TMEM_A_COL = 128, HF_TMEM_A_STAGE_COLS = 64;
+constexpr uint32_t HF_TMEM_COLS = 512;
+static_assert(HF_TMEM_A_COL + HF_STAGES * HF_TMEM_A_STAGE_COLS <= HF_TMEM_COLS, "tensor memory too small");
 static_assert(HF_SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
 static_assert(8 * 32 * HF_OUT_PITCH * 4 <= HF_STAGE_BYTES, "output staging does not fit in an operand stage");
 
@@ -82,13 +85,44 @@ struct HfParams {
     int64_t N, M;
     int K, order, n_super;
     uint32_t row_bytes;
+    unsigned long long *trace;  // tracing aid (or nullptr): SM clock stamps of CTA (0,0), rows of 8
 };
+
+// Tracing aid.  Row c (stage, < 64) of block `who`: 0 = weight warp 0, 1 = activation warp 4, 2 = the MMA thread.
+// Producer columns: 0 loop top, 1 past the barrier, 2 copies of stage c + 2 issued, 3 operand stage free,
+// 4 converted, 5 published.  MMA columns: 0 stage seen full, 1 MMAs and commit issued.
+__device__ __forceinline__ void hf_stamp(const HfParams &p, int who, int c, int slot) {
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && c < 64) {
+        p.trace[((who * 64 + c) * 8) + slot] = (unsigned long long)clock64();
+    }
+}
 
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// registers -> 32 lanes x 32 consecutive 32-bit columns of tensor memory (completion: tcgen05.wait::st)
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+
+// D(fp32, TMEM) (+)= A(fp16, TMEM: lane = row, two values of K per column) x B(fp16 tile in shared memory)^T, K = 16
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
@@ -149,37 +183,41 @@ __device__ __forceinline__ void hf_convert_weight_row(uint32_t st, int r, const 
            make_uint4(as_u32(__hmul2(as_h2(zb[0] | (zb[1] << 16)), m8)), as_u32(__hmul2(as_h2(zb[2] | (zb[3] << 16)), m8)), 0u, 0u));
 }
 
-// One activation column of a stage (a 144-byte block in registers) -> its 128 values q8 * d8 in the
-// eight activation tiles, and the column of the rank-one operand.
-__device__ __forceinline__ void hf_convert_activation_col(uint32_t st, int r, const uint4 (&xv)[9]) {
+// One activation column of a stage (a 144-byte block in registers) -> its 128 values q8 * d8, in K order, in the
+// tensor-memory lane of the column (warp-collective: the 32 lanes are 32 neighbouring columns), and the column of
+// the rank-one operand in shared memory.
+__device__ __forceinline__ void hf_convert_activation_col(uint32_t st, int r, const uint4 (&xv)[9], uint32_t taddr) {
     const uint32_t dsw[4] = {xv[0].x, xv[0].y, xv[0].z, xv[0].w};
     float zc[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t dbits = dsw[j] & 0xFFFFu;
-        const __half2 d2 = as_h2(dbits | (dbits << 16));
-        int isum = 0;
+    for (int jj = 0; jj < 2; ++jj) {  // 64 values of K = 32 columns of tensor memory at a time
+        uint32_t o[32];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {  // values 16h .. 16h + 15 of the block: tile 2j + h
-            const uint4 v = xv[1 + 2 * j + h];
-            const uint32_t wq[4] = {v.x, v.y, v.z, v.w};
-            uint32_t a[8];
+        for (int j2 = 0; j2 < 2; ++j2) {
+            const int j = 2 * jj + j2;
+            const uint32_t dbits = dsw[j] & 0xFFFFu;
+            const __half2 d2 = as_h2(dbits | (dbits << 16));
+            int isum = 0;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                isum = __dp4a((int)wq[t], 0x01010101, isum);
-                const uint32_t wu = wq[t] ^ 0x80808080u;  // q + 128 in 1..255
-                a[2 * t] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4140), H2_1152, d2);
-                a[2 * t + 1] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4342), H2_1152, d2);
+            for (int h = 0; h < 2; ++h) {  // values 16h .. 16h + 15 of the block
+                const uint4 v = xv[1 + 2 * j + h];
+                const uint32_t wq[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    isum = __dp4a((int)wq[t], 0x01010101, isum);
+                    const uint32_t wu = wq[t] ^ 0x80808080u;  // q + 128 in 1..255
+                    o[j2 * 16 + h * 8 + 2 * t] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4140), H2_1152, d2);
+                    o[j2 * 16 + h * 8 + 2 * t + 1] = h2_sub_scale(__byte_perm(wu, H2_MAGIC_BYTES, 0x4342), H2_1152, d2);
+                }
             }
-            const uint32_t tile = st + HF_A_OFF + (2 * j + h) * TC_TILE;
-            sts_v4(tile + tile_off(r, 0), make_uint4(a[0], a[1], a[2], a[3]));
-            sts_v4(tile + tile_off(r, 1), make_uint4(a[4], a[5], a[6], a[7]));
+            // what the stored s differs by from d8 * sum(q8); d8 * isum is exact in fp32
+            zc[j] = fmaf(-half_bits_to_float(dbits), (float)isum, half_bits_to_float(dsw[j] >> 16));
         }
-        // what the stored s differs by from d8 * sum(q8); d8 * isum is exact in fp32
-        zc[j] = fmaf(-half_bits_to_float(dbits), (float)isum, half_bits_to_float(dsw[j] >> 16));
+        tmem_st32_nowait(taddr + jj * 32, o);
     }
     sts_v4(st + HF_ZA_OFF + tile_off(r, 0),
            make_uint4(as_u32(__floats2half2_rn(zc[0], zc[1])), as_u32(__floats2half2_rn(zc[2], zc[3])), 0u, 0u));
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const HfParams p) {
@@ -267,14 +305,19 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
             // Stage c has landed for this thread; after the barrier, for every thread.  The barrier also says that
             // everybody has finished reading stage c - 1, whose slot stage c + 2 is about to overwrite.  A warp that
             // gave up on a wait keeps coming here, so that the barrier always completes.
+            const bool stamps = lane == 0 && (warp & 3) == 0;  // warps 0 and 4
+            if (stamps) hf_stamp(p, warp >> 2, c, 0);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
             named_bar_sync(1, HF_PROD_THREADS);
+            if (stamps) hf_stamp(p, warp >> 2, c, 1);
             issue_stage(c + 2);
+            if (stamps) hf_stamp(p, warp >> 2, c, 2);
             if (alive && round > 0) {
                 // the whole warp takes the same decision, so that its aligned instructions stay convergent
                 const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
                 alive = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
+            if (stamps) hf_stamp(p, warp >> 2, c, 3);
             if (alive) {
                 const uint32_t st = sbase + s * HF_STAGE_BYTES, raw = sbase + HF_RAW_OFF + raw_slot * HF_RAW_BYTES;
                 if (warp < 4) {  // one weight row per thread
@@ -287,11 +330,14 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
                     uint4 v[9];
 #pragma unroll
                     for (int i = 0; i < 9; ++i) v[i] = lds_v4(raw + HF_RAW_X_OFF + col * Q8_BYTES + i * 16);
-                    hf_convert_activation_col(st, col, v);
+                    hf_convert_activation_col(st, col, v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS);
+                    tc_fence_before();
                 }
+                if (stamps) hf_stamp(p, warp >> 2, c, 4);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&stage_full[s]);
+                if (stamps) hf_stamp(p, warp >> 2, c, 5);
             }
             if (++s == HF_STAGES) {
                 s = 0;
@@ -340,12 +386,14 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
             }
             const uint32_t st = sbase + s * HF_STAGE_BYTES;
             tc_fence_after();
+            hf_stamp(p, 2, c, 0);
             tc_mma_f16(tmem, tc_desc(st + HF_ZA_OFF), tc_desc(st + HF_ZB_OFF), idesc, c > 0 ? 1u : 0u);
 #pragma unroll
             for (int t = 0; t < HF_KT; ++t) {
-                tc_mma_f16(tmem, tc_desc(st + HF_A_OFF + t * TC_TILE), tc_desc(st + HF_B_OFF + t * TC_TILE), idesc, 1u);
+                tc_mma_f16_ts(tmem, tmem + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS + t * 8, tc_desc(st + HF_B_OFF + t * TC_TILE), idesc, 1u);
             }
             tc_commit(&stage_empty[s]);  // the stage may be overwritten once these MMAs have read it
+            hf_stamp(p, 2, c, 1);
             if (++s == HF_STAGES) {
                 s = 0;
                 parity ^= 1u;
@@ -387,6 +435,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.order = order;
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
+    p.trace = static_cast<unsigned long long *>(next_trace_slot());
     static thread_local int attr_done_dev = -1;
     int dev = 0;
     JQ_CUDA_TRY(cudaGetDevice(&dev));
