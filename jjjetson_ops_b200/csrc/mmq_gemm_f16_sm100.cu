@@ -31,6 +31,8 @@
 // After the last stage warps 0-7 read the 128 x 128 fp32 accumulator and store it.
 // Every mbarrier wait is a bounded poll; a wait that runs out sets the device fault word, and every
 // warp still reaches the common exit where tensor memory is released.
+#include <cuda.h>
+
 #include "tc_common.cuh"
 
 namespace jq {
@@ -45,21 +47,22 @@ constexpr int HF_B_OFF = 0;                           // weights: HF_KT tiles
 constexpr int HF_ZA_OFF = HF_KT * TC_TILE;            // fp16 (s8 - d8 * sum q8)[128 columns][16] (4 blocks + 12 zeros)
 constexpr int HF_ZB_OFF = HF_ZA_OFF + TC_TILE;        // fp16 (-8 * d4)[128 rows][16]
 constexpr int HF_STAGE_BYTES = HF_ZB_OFF + TC_TILE;
-// ring of quantized bytes as they lie in global memory: 128 rows x 72 bytes of weights, then 128 blocks of activations
-constexpr int HF_RAW_STAGES = 3;
+// Rings of quantized bytes as they lie in global memory, filled by the copy engine (one tensor copy each):
+// activations, one stage per slot: 128 blocks of 144 bytes; weights, two stages per slot: 128 rows x 144 bytes
+constexpr int HF_RAWX_SLOTS = 3, HF_RAWW_SLOTS = 2;
 constexpr int HF_W_CHUNK = 4 * Q4_BYTES;              // 72 bytes of a weight row per stage
-constexpr int HF_RAW_X_OFF = 128 * HF_W_CHUNK;
-constexpr int HF_RAW_BYTES = HF_RAW_X_OFF + 128 * Q8_BYTES;
-constexpr int HF_RAW_OFF = HF_STAGES * HF_STAGE_BYTES;
-constexpr int HF_BAR_OFF = HF_RAW_OFF + HF_RAW_STAGES * HF_RAW_BYTES;
-constexpr int HF_SMEM_BYTES = HF_BAR_OFF + 128;
-constexpr int HF_COPIES = 128 * 9;                    // copies per operand and stage: 8 bytes each for weights, 16 for activations
-constexpr int HF_PROD_THREADS = 256;
-constexpr int HF_COPY_ITERS = (HF_COPIES + HF_PROD_THREADS - 1) / HF_PROD_THREADS;
+constexpr int HF_RAW_SLOT_BYTES = 128 * Q8_BYTES;     // 18432, both rings
+static_assert(2 * HF_W_CHUNK == Q8_BYTES, "a weight slot is two stages of 72 bytes per row");
+constexpr int HF_RAWX_OFF = HF_STAGES * HF_STAGE_BYTES;
+constexpr int HF_RAWW_OFF = HF_RAWX_OFF + HF_RAWX_SLOTS * HF_RAW_SLOT_BYTES;
+constexpr int HF_BAR_OFF = HF_RAWW_OFF + HF_RAWW_SLOTS * HF_RAW_SLOT_BYTES;
+constexpr int HF_SMEM_BYTES = HF_BAR_OFF + 256;
+static_assert(HF_RAWX_OFF % 128 == 0 && HF_RAW_SLOT_BYTES % 128 == 0, "tensor copies land on 128-byte boundaries");
 constexpr int HF_OUT_PITCH = 33;                      // words per row of a warp's 32 x 32 output staging block
 constexpr int HF_PROD_WARPS = 8;
 constexpr int HF_MMA_WARP = 8;
-constexpr int HF_THREADS = 9 * 32;
+constexpr int HF_COPY_WARP = 9;
+constexpr int HF_THREADS = 10 * 32;
 // Tensor memory: the fp32 accumulator in columns 0..127, then per stage the activation operand: lane = activation
 // column, 64 columns of two fp16 values = the 128 values of K in order
 constexpr uint32_t HF_TMEM_A_COL = 128, HF_TMEM_A_STAGE_COLS = 64;
@@ -97,11 +100,13 @@ __device__ __forceinline__ void hf_stamp(const HfParams &p, int who, int c, int 
     }
 }
 
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+// One tiled tensor copy global -> shared: the box of `map` at byte column x, row y; completion counted in bytes on
+// an mbarrier.  x must be a multiple of 16.  Rows past the end of the tensor arrive as zeros (and are counted).
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // registers -> 32 lanes x 32 consecutive 32-bit columns of tensor memory (completion: tcgen05.wait::st)
@@ -220,15 +225,20 @@ __device__ __forceinline__ void hf_convert_activation_col(uint32_t st, int r, co
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const HfParams p) {
+__global__ void __launch_bounds__(HF_THREADS, 1)
+gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + HF_BAR_OFF);
     uint64_t *stage_full = bars;                  // [HF_STAGES] producer warps -> MMA warp
     uint64_t *stage_empty = bars + HF_STAGES;     // [HF_STAGES] MMA completion -> producers
     uint64_t *acc_full = bars + 2 * HF_STAGES;    // all MMAs complete -> epilogue
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
-    static_assert((2 * HF_STAGES + 1) * 8 + 4 <= 128, "barrier block too small");
+    uint64_t *rawx_full = acc_full + 1;               // [HF_RAWX_SLOTS] copy engine -> activation warps
+    uint64_t *rawx_empty = rawx_full + HF_RAWX_SLOTS; // [HF_RAWX_SLOTS] activation warps -> copy warp
+    uint64_t *raww_full = rawx_empty + HF_RAWX_SLOTS; // [HF_RAWW_SLOTS] copy engine -> weight warps
+    uint64_t *raww_empty = raww_full + HF_RAWW_SLOTS; // [HF_RAWW_SLOTS] weight warps -> copy warp
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raww_empty + HF_RAWW_SLOTS);
+    static_assert((2 * HF_STAGES + 1 + 2 * HF_RAWX_SLOTS + 2 * HF_RAWW_SLOTS) * 8 + 4 <= 256, "barrier block too small");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t n0 = (int64_t)blockIdx.x * HF_BN, m0 = (int64_t)blockIdx.y * HF_BM;
@@ -240,6 +250,14 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
             mbar_init(&stage_empty[s], 1);
         }
         mbar_init(acc_full, 1);
+        for (int i = 0; i < HF_RAWX_SLOTS; ++i) {
+            mbar_init(&rawx_full[i], 1);
+            mbar_init(&rawx_empty[i], 4);
+        }
+        for (int i = 0; i < HF_RAWW_SLOTS; ++i) {
+            mbar_init(&raww_full[i], 1);
+            mbar_init(&raww_empty[i], 4);
+        }
         fence_mbar_init();
     }
     if (tid < 128) {
@@ -263,74 +281,51 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
 
     if (warp < HF_PROD_WARPS) {
         // =============================== producers, then epilogue ==============================
-        // Raw ring.  The 1152 8-byte pieces of the weight rows and the 1152 16-byte pieces of the activation blocks
-        // of a stage are dealt to the 256 threads in memory order, so that one warp instruction touches a few
-        // cache lines instead of 32; a stage later, every source lies a fixed step further.
-        const uint8_t *w_src[HF_COPY_ITERS], *x_src[HF_COPY_ITERS];
-        uint32_t w_dst[HF_COPY_ITERS], x_dst[HF_COPY_ITERS];
-#pragma unroll
-        for (int i = 0; i < HF_COPY_ITERS; ++i) {
-            const int idx = min(tid + i * HF_PROD_THREADS, HF_COPIES - 1);
-            const int r = idx / 9, piece = idx - 9 * r;
-            // rows and columns past the end are clamped: their results are never stored
-            w_src[i] = p.w + min(n0 + r, p.N - 1) * (int64_t)p.row_bytes + piece * 8;
-            w_dst[i] = (uint32_t)(r * HF_W_CHUNK + piece * 8);
-            x_src[i] = p.xq + q8_block_index(0, min(m0 + r, p.M - 1), p.n_super, p.M, p.order) * Q8_BYTES + piece * 16;
-            x_dst[i] = (uint32_t)(HF_RAW_X_OFF + r * Q8_BYTES + piece * 16);
-        }
-        const int64_t x_step = (p.order == JQ_ORDER_KSUPER_COL ? p.M : (int64_t)1) * Q8_BYTES;
-        int load_slot = 0;
-        auto issue_stage = [&](int c) {  // stage c -> the next raw slot; always one commit group per call
-            if (c < n_chunks) {
-                const uint32_t raw = sbase + HF_RAW_OFF + load_slot * HF_RAW_BYTES;
-#pragma unroll
-                for (int i = 0; i < HF_COPY_ITERS; ++i) {
-                    if (tid + i * HF_PROD_THREADS < HF_COPIES) {
-                        cp_async8(raw + w_dst[i], w_src[i] + (int64_t)c * HF_W_CHUNK);
-                        cp_async16(raw + x_dst[i], x_src[i] + c * x_step);
-                    }
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            load_slot = load_slot == HF_RAW_STAGES - 1 ? 0 : load_slot + 1;
-        };
-
+        // Warps 0-3 convert one weight row per thread, warps 4-7 one activation column per thread, from the raw rings
+        // the copy warp keeps filled.  All decisions are taken per warp, so that aligned instructions stay convergent.
+        const bool is_w = warp < 4;
+        const int row = tid & 127;  // weight row or activation column inside the tile
         bool alive = true;
-        int s = 0, raw_slot = 0;
-        uint32_t round = 0;  // how often the operand ring has wrapped
-        issue_stage(0);
-        issue_stage(1);
+        int s = 0;
+        uint32_t round = 0;         // how often the operand ring has wrapped
+        int xs = 0;                 // activation slot of stage c, and how often that ring has wrapped
+        uint32_t xround = 0;
 #pragma unroll 1
-        for (int c = 0; c < n_chunks; ++c) {
-            // Stage c has landed for this thread; after the barrier, for every thread.  The barrier also says that
-            // everybody has finished reading stage c - 1, whose slot stage c + 2 is about to overwrite.  A warp that
-            // gave up on a wait keeps coming here, so that the barrier always completes.
+        for (int c = 0; c < n_chunks && alive; ++c) {
             const bool stamps = lane == 0 && (warp & 3) == 0;  // warps 0 and 4
             if (stamps) hf_stamp(p, warp >> 2, c, 0);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-            named_bar_sync(1, HF_PROD_THREADS);
+            const int ws = (c >> 1) & 1;  // weight slot of the stage pair
+            {
+                const bool ok = is_w ? ((c & 1) != 0 || mbar_wait_bounded(&raww_full[ws], (uint32_t)(c >> 2) & 1u, p.fault))
+                                     : mbar_wait_bounded(&rawx_full[xs], xround & 1u, p.fault);
+                alive = __all_sync(0xFFFFFFFFu, ok) != 0;
+            }
             if (stamps) hf_stamp(p, warp >> 2, c, 1);
-            issue_stage(c + 2);
-            if (stamps) hf_stamp(p, warp >> 2, c, 2);
             if (alive && round > 0) {
-                // the whole warp takes the same decision, so that its aligned instructions stay convergent
                 const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
                 alive = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
             if (stamps) hf_stamp(p, warp >> 2, c, 3);
             if (alive) {
-                const uint32_t st = sbase + s * HF_STAGE_BYTES, raw = sbase + HF_RAW_OFF + raw_slot * HF_RAW_BYTES;
-                if (warp < 4) {  // one weight row per thread
+                const uint32_t st = sbase + s * HF_STAGE_BYTES;
+                if (is_w) {
+                    const uint32_t raw = sbase + HF_RAWW_OFF + ws * HF_RAW_SLOT_BYTES + row * Q8_BYTES + (c & 1) * HF_W_CHUNK;
                     uint2 v[9];
 #pragma unroll
-                    for (int i = 0; i < 9; ++i) v[i] = lds_v2(raw + tid * HF_W_CHUNK + i * 8);
-                    hf_convert_weight_row(st, tid, v);
-                } else {  // one activation column per thread
-                    const int col = tid - 128;
+                    for (int i = 0; i < 9; ++i) v[i] = lds_v2(raw + i * 8);
+                    hf_convert_weight_row(st, row, v);
+                    if (c & 1) {  // both halves of the slot have been read and used
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&raww_empty[ws]);
+                    }
+                } else {
+                    const uint32_t raw = sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES + row * Q8_BYTES;
                     uint4 v[9];
 #pragma unroll
-                    for (int i = 0; i < 9; ++i) v[i] = lds_v4(raw + HF_RAW_X_OFF + col * Q8_BYTES + i * 16);
-                    hf_convert_activation_col(st, col, v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS);
+                    for (int i = 0; i < 9; ++i) v[i] = lds_v4(raw + i * 16);
+                    hf_convert_activation_col(st, row, v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&rawx_empty[xs]);
                     tc_fence_before();
                 }
                 if (stamps) hf_stamp(p, warp >> 2, c, 4);
@@ -343,9 +338,11 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
                 s = 0;
                 ++round;
             }
-            raw_slot = raw_slot == HF_RAW_STAGES - 1 ? 0 : raw_slot + 1;
+            if (++xs == HF_RAWX_SLOTS) {
+                xs = 0;
+                ++xround;
+            }
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
 
         // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 64 of the 128 weight rows,
         // and turns each 32 x 32 block around in shared memory (the operand stages are free by now) so that a
@@ -373,8 +370,36 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
                 __syncwarp();
             }
         }
+    } else if (warp == HF_COPY_WARP) {
+        // =============================== copy warp =============================================
+        // One thread keeps both raw rings filled: per stage one tensor copy of the 128 activation blocks, per pair
+        // of stages one of 144 bytes of each of the 128 weight rows.
+        if (lane == 0) {
+            int xs = 0;
+            uint32_t xround = 0;
+            for (int c = 0; c < n_chunks; ++c) {
+                if ((c & 1) == 0) {
+                    const int pair = c >> 1, ws = pair & 1;
+                    if (pair >= HF_RAWW_SLOTS && !mbar_wait_bounded(&raww_empty[ws], (uint32_t)((pair >> 1) - 1) & 1u, p.fault)) break;
+                    mbar_arrive_expect_tx(&raww_full[ws], HF_RAW_SLOT_BYTES);
+                    tma_load_2d(sbase + HF_RAWW_OFF + ws * HF_RAW_SLOT_BYTES, &w_map, pair * Q8_BYTES, (int)n0, &raww_full[ws]);
+                }
+                if (xround > 0 && !mbar_wait_bounded(&rawx_empty[xs], (xround - 1) & 1u, p.fault)) break;
+                mbar_arrive_expect_tx(&rawx_full[xs], HF_RAW_SLOT_BYTES);
+                if (p.order == JQ_ORDER_KSUPER_COL) {  // the tensor is [n_super * M blocks][144 bytes]
+                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, 0, (int)((int64_t)c * p.M + m0), &rawx_full[xs]);
+                } else {                               // the tensor is [M columns][n_super * 144 bytes]
+                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, c * Q8_BYTES, (int)m0, &rawx_full[xs]);
+                }
+                if (++xs == HF_RAWX_SLOTS) {
+                    xs = 0;
+                    ++xround;
+                }
+            }
+        }
     } else if (lane == 0) {
         // =============================== MMA issuer ============================================
+
         const uint32_t idesc = tc_idesc_f16(HF_BM, HF_BN);
         int s = 0;
         uint32_t parity = 0;
@@ -413,9 +438,48 @@ __global__ void __launch_bounds__(HF_THREADS, 1) gemm_q4_0_q8_1_f16_kernel(const
 
 }  // namespace
 
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library does not link against libcuda.
+EncodeTiledFn tensor_map_encoder() {
+    static const EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            f = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// Byte tensor [rows][row_len] with rows `pitch` bytes apart, copied in boxes of 128 rows x 144 bytes.
+int encode_byte_map(CUtensorMap *map, const void *base, uint64_t row_len, uint64_t rows, uint64_t pitch) {
+    const EncodeTiledFn encode = tensor_map_encoder();
+    if (encode == nullptr) return set_error(JQ_ERR_UNSUPPORTED, "the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {row_len, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {(cuuint32_t)Q8_BYTES, 128u};
+    const cuuint32_t elem_strides[2] = {1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(JQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return JQ_OK;
+}
+
+}  // namespace
+
 int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
                     int order) {
-    if (K % SUPER != 0) return set_error(JQ_ERR_UNSUPPORTED, "fp16-operand tcgen05 GEMM needs K %% 128 == 0 (K = %lld)", (long long)K);
+    // a weight row's pitch, K / 32 * 18 bytes, must be a multiple of 16 for the tensor copies
+    if (K % (2 * SUPER) != 0) return set_error(JQ_ERR_UNSUPPORTED, "fp16-operand tcgen05 GEMM needs K %% 256 == 0 (K = %lld)", (long long)K);
     if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
         return set_error(JQ_ERR_UNSUPPORTED, "fp16-operand tcgen05 GEMM needs 16-byte aligned operands");
     if (N == 0 || M == 0) return JQ_OK;
@@ -423,7 +487,8 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     if (int rc = device_caps(&caps)) return rc;
     if (caps.cc / 10 != 10) return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 needs an sm_100-class device");
     const int64_t gx = (N + HF_BN - 1) / HF_BN, gy = (M + HF_BM - 1) / HF_BM;
-    if (gy > 65535 || K > (1 << 24)) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tcgen05 GEMM");
+    if (gy > 65535 || K > (1 << 24) || (K / SUPER) * M >= ((int64_t)1 << 31) || N >= ((int64_t)1 << 31))
+        return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tcgen05 GEMM");
     HfParams p{};
     p.w = static_cast<const uint8_t *>(d_w);
     p.xq = static_cast<const uint8_t *>(d_xq);
@@ -436,6 +501,12 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
+    CUtensorMap w_map, x_map;
+    if (int rc = encode_byte_map(&w_map, d_w, p.row_bytes, (uint64_t)N, p.row_bytes)) return rc;
+    const uint64_t x_row = (uint64_t)p.n_super * Q8_BYTES;
+    if (int rc = order == JQ_ORDER_KSUPER_COL ? encode_byte_map(&x_map, d_xq, Q8_BYTES, (uint64_t)p.n_super * (uint64_t)M, Q8_BYTES)
+                                              : encode_byte_map(&x_map, d_xq, x_row, (uint64_t)M, x_row))
+        return rc;
     static thread_local int attr_done_dev = -1;
     int dev = 0;
     JQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -444,7 +515,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
         attr_done_dev = dev;
     }
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
-    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy), HF_THREADS, HF_SMEM_BYTES, st>>>(p);
+    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy), HF_THREADS, HF_SMEM_BYTES, st>>>(p, w_map, x_map);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }

@@ -50,8 +50,8 @@ def _check(env, wq, x, K, N, M, order, s_mode, rows=None):
     return e_ref
 
 
-@pytest.mark.parametrize("K,N,M", [(128, 32, 9), (256, 64, 9), (512, 200, 33), (1024, 129, 130), (768, 256, 128),
-                                   (4096, 384, 17), (1280, 1, 1), (11008, 50, 40), (384, 300, 257)])
+@pytest.mark.parametrize("K,N,M", [(2560, 40, 20), (256, 64, 9), (512, 200, 33), (1024, 129, 130), (768, 256, 128),
+                                   (4096, 384, 17), (1280, 1, 1), (11008, 50, 40), (1792, 300, 257)])
 @pytest.mark.parametrize("order", [0, 1])
 @pytest.mark.parametrize("s_mode", [0, 1])
 def test_gemm_f16_small_and_ragged_shapes(env, K, N, M, order, s_mode):
@@ -62,6 +62,16 @@ def test_gemm_f16_small_and_ragged_shapes(env, K, N, M, order, s_mode):
         x[:, 5] *= 20.0          # an outlier channel
         x[M // 2, 128:160] = 0.0  # an all-zero group: d = 0
     _check(env, env.O.quantize_q4_0(w), x, K, N, M, order, s_mode)
+
+
+def test_gemm_f16_refuses_odd_super_block_counts(env):
+    """The tensor copies need a weight-row pitch that is a multiple of 16 bytes: K % 256 == 0."""
+    c = env.c
+    w = env.t.zeros(c.q4_0_bytes(8, 384), dtype=env.t.uint8, device=env.dev)
+    xq = env.t.zeros(c.q8_1_bytes(384, 16), dtype=env.t.uint8, device=env.dev)
+    with pytest.raises(c.JqError) as ei:
+        c.mul_mat_q4_0_q8_1(w, xq, 384, 8, 16, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_F16)
+    assert ei.value.status == c.ERR_UNSUPPORTED
 
 
 def test_gemm_f16_prefill_config(env):
