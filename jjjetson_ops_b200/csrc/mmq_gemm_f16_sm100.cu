@@ -59,17 +59,20 @@ constexpr int HF_BAR_OFF = HF_RAWW_OFF + HF_RAWW_SLOTS * HF_RAW_SLOT_BYTES;
 constexpr int HF_SMEM_BYTES = HF_BAR_OFF + 256;
 static_assert(HF_RAWX_OFF % 128 == 0 && HF_RAW_SLOT_BYTES % 128 == 0, "tensor copies land on 128-byte boundaries");
 constexpr int HF_OUT_PITCH = 33;                      // words per row of a warp's 32 x 32 output staging block
-constexpr int HF_PROD_WARPS = 8;
-constexpr int HF_MMA_WARP = 8;
-constexpr int HF_COPY_WARP = 9;
-constexpr int HF_THREADS = 10 * 32;
+constexpr int HF_GROUPS = 2;        // producer groups of 8 warps; group g converts the stages c with c % 2 == g
+constexpr int HF_GROUP_WARPS = 8;
+constexpr int HF_PROD_WARPS = HF_GROUPS * HF_GROUP_WARPS;
+constexpr int HF_MMA_WARP = HF_PROD_WARPS;
+constexpr int HF_COPY_WARP = HF_PROD_WARPS + 1;
+constexpr int HF_THREADS = (HF_PROD_WARPS + 2) * 32;
+static_assert(HF_RAWX_SLOTS == HF_STAGES, "stage c uses slot c % 3 of both the operand ring and the activation ring");
 // Tensor memory: the fp32 accumulator in columns 0..127, then per stage the activation operand: lane = activation
 // column, 64 columns of two fp16 values = the 128 values of K in order
 constexpr uint32_t HF_TMEM_A_COL = 128, HF_TMEM_A_STAGE_COLS = 64;
 constexpr uint32_t HF_TMEM_COLS = 512;
 static_assert(HF_TMEM_A_COL + HF_STAGES * HF_TMEM_A_STAGE_COLS <= HF_TMEM_COLS, "tensor memory too small");
 static_assert(HF_SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
-static_assert(8 * 32 * HF_OUT_PITCH * 4 <= HF_STAGE_BYTES, "output staging does not fit in an operand stage");
+static_assert(HF_PROD_WARPS * 32 * HF_OUT_PITCH * 4 <= HF_STAGES * HF_STAGE_BYTES, "output staging does not fit in the operand stages");
 
 // fp16 constants, two per word
 constexpr uint32_t H2_MAGIC_BYTES = 0x64646464u;  // high byte of 1024 + v for an 8-bit v
@@ -246,7 +249,7 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 
     if (tid == 0) {
         for (int s = 0; s < HF_STAGES; ++s) {
-            mbar_init(&stage_full[s], HF_PROD_WARPS);
+            mbar_init(&stage_full[s], HF_GROUP_WARPS);
             mbar_init(&stage_empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -256,7 +259,7 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
         }
         for (int i = 0; i < HF_RAWW_SLOTS; ++i) {
             mbar_init(&raww_full[i], 1);
-            mbar_init(&raww_empty[i], 4);
+            mbar_init(&raww_empty[i], 4 * HF_GROUPS);  // the four weight warps of each group
         }
         fence_mbar_init();
     }
@@ -281,31 +284,32 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 
     if (warp < HF_PROD_WARPS) {
         // =============================== producers, then epilogue ==============================
-        // Warps 0-3 convert one weight row per thread, warps 4-7 one activation column per thread, from the raw rings
-        // the copy warp keeps filled.  All decisions are taken per warp, so that aligned instructions stay convergent.
-        const bool is_w = warp < 4;
-        const int row = tid & 127;  // weight row or activation column inside the tile
+        // Two groups of eight warps take the stages in turn, so that one group's waits and conversion latencies are
+        // covered by the other's work.  In a group, warps 0-3 convert one weight row per thread and warps 4-7 one
+        // activation column per thread, from the raw rings the copy warp keeps filled.  All decisions are taken per
+        // warp, so that aligned instructions stay convergent.
+        const int group = warp / HF_GROUP_WARPS, gw = warp % HF_GROUP_WARPS;
+        const bool is_w = gw < 4;
+        const int row = (gw & 3) * 32 + lane;  // weight row or activation column inside the tile
+        const bool stamps = lane == 0 && (gw & 3) == 0 && group == 0;
         bool alive = true;
-        int s = 0;
-        uint32_t round = 0;         // how often the operand ring has wrapped
-        int xs = 0;                 // activation slot of stage c, and how often that ring has wrapped
-        uint32_t xround = 0;
 #pragma unroll 1
-        for (int c = 0; c < n_chunks && alive; ++c) {
-            const bool stamps = lane == 0 && (warp & 3) == 0;  // warps 0 and 4
-            if (stamps) hf_stamp(p, warp >> 2, c, 0);
-            const int ws = (c >> 1) & 1;  // weight slot of the stage pair
+        for (int c = group; c < n_chunks && alive; c += HF_GROUPS) {
+            const int s = c % HF_STAGES;                   // slot of the operand ring and of the activation ring
+            const uint32_t round = (uint32_t)(c / HF_STAGES);  // how often those rings have wrapped
+            const int ws = (c >> 1) & 1;                   // weight slot of the stage pair
+            if (stamps) hf_stamp(p, gw >> 2, c, 0);
             {
-                const bool ok = is_w ? ((c & 1) != 0 || mbar_wait_bounded(&raww_full[ws], (uint32_t)(c >> 2) & 1u, p.fault))
-                                     : mbar_wait_bounded(&rawx_full[xs], xround & 1u, p.fault);
+                const bool ok = is_w ? mbar_wait_bounded(&raww_full[ws], (uint32_t)(c >> 2) & 1u, p.fault)
+                                     : mbar_wait_bounded(&rawx_full[s], round & 1u, p.fault);
                 alive = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
-            if (stamps) hf_stamp(p, warp >> 2, c, 1);
+            if (stamps) hf_stamp(p, gw >> 2, c, 1);
             if (alive && round > 0) {
                 const bool ok = mbar_wait_bounded(&stage_empty[s], (round - 1) & 1u, p.fault);
                 alive = __all_sync(0xFFFFFFFFu, ok) != 0;
             }
-            if (stamps) hf_stamp(p, warp >> 2, c, 3);
+            if (stamps) hf_stamp(p, gw >> 2, c, 3);
             if (alive) {
                 const uint32_t st = sbase + s * HF_STAGE_BYTES;
                 if (is_w) {
@@ -314,60 +318,45 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll
                     for (int i = 0; i < 9; ++i) v[i] = lds_v2(raw + i * 8);
                     hf_convert_weight_row(st, row, v);
-                    if (c & 1) {  // both halves of the slot have been read and used
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&raww_empty[ws]);
-                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&raww_empty[ws]);  // this warp's half of the slot has been read and used
                 } else {
-                    const uint32_t raw = sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES + row * Q8_BYTES;
+                    const uint32_t raw = sbase + HF_RAWX_OFF + s * HF_RAW_SLOT_BYTES + row * Q8_BYTES;
                     uint4 v[9];
 #pragma unroll
                     for (int i = 0; i < 9; ++i) v[i] = lds_v4(raw + i * 16);
-                    hf_convert_activation_col(st, row, v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS);
+                    hf_convert_activation_col(st, row, v, tmem + ((uint32_t)((gw & 3) * 32) << 16) + HF_TMEM_A_COL + s * HF_TMEM_A_STAGE_COLS);
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&rawx_empty[xs]);
+                    if (lane == 0) mbar_arrive(&rawx_empty[s]);
                     tc_fence_before();
                 }
-                if (stamps) hf_stamp(p, warp >> 2, c, 4);
+                if (stamps) hf_stamp(p, gw >> 2, c, 4);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&stage_full[s]);
-                if (stamps) hf_stamp(p, warp >> 2, c, 5);
-            }
-            if (++s == HF_STAGES) {
-                s = 0;
-                ++round;
-            }
-            if (++xs == HF_RAWX_SLOTS) {
-                xs = 0;
-                ++xround;
+                if (stamps) hf_stamp(p, gw >> 2, c, 5);
             }
         }
 
-        // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 64 of the 128 weight rows,
-        // and turns each 32 x 32 block around in shared memory (the operand stages are free by now) so that a
-        // store instruction writes 128 contiguous bytes of one output row
+        // epilogue: warp w reads TMEM lanes 32 * (w % 4) .. (activation columns) and 32 of the 128 weight rows, and
+        // turns the 32 x 32 block around in shared memory (the operand stages are free by now) so that a store
+        // instruction writes 128 contiguous bytes of one output row
         if (alive && __all_sync(0xFFFFFFFFu, mbar_wait_bounded(acc_full, 0u, p.fault))) {
             tc_fence_after();
-            const int half = warp >> 2;
-            const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 64);
+            const int cb = warp >> 2;  // which 32 of the 128 weight rows
             const uint32_t stage_blk = sbase + warp * (32 * HF_OUT_PITCH * 4);
             const int64_t m_first = m0 + (warp & 3) * 32;
+            uint32_t v[32];
+            tmem_ld32_nowait(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(cb * 32), v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t v[32];
-                tmem_ld32_nowait(t_lane + h * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) sts_f32(stage_blk + (lane * HF_OUT_PITCH + j) * 4, __uint_as_float(v[j]));
-                __syncwarp();
-                const int64_t n = n0 + half * 64 + h * 32 + lane;
+            for (int j = 0; j < 32; ++j) sts_f32(stage_blk + (lane * HF_OUT_PITCH + j) * 4, __uint_as_float(v[j]));
+            __syncwarp();
+            const int64_t n = n0 + cb * 32 + lane;
 #pragma unroll 8
-                for (int rr = 0; rr < 32; ++rr) {
-                    const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
-                    if (m_first + rr < p.M && n < p.N) p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
-                }
-                __syncwarp();
+            for (int rr = 0; rr < 32; ++rr) {
+                const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
+                if (m_first + rr < p.M && n < p.N) p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
             }
         }
     } else if (warp == HF_COPY_WARP) {
