@@ -465,7 +465,7 @@ def measure_extras(torch, capi, synth, dev, peaks):
     Each is timed like the headline (cold-L2 weight rotation, CUDA graph, CUDA events)."""
     out = {}
 
-    def bench_linear(K, N, M, steps=200, fused=True):
+    def bench_linear(K, N, M, steps=200, fused=True, kernel=None):
         rng = np.random.default_rng(1234)
         wq_bytes = capi.q4_0_bytes(N, K)
         R = max(2, -(-3 * L2_BYTES // wq_bytes) + 1)
@@ -485,7 +485,8 @@ def measure_extras(torch, capi, synth, dev, peaks):
             if fused:
                 capi.linear_q4_0(ws_[i % R], x, N, capi.S_D_SUM_Q, ws=ws, out=y)
             else:  # the multiply alone, activations already in Q8_1 form
-                capi.mul_mat_q4_0_q8_1(ws_[i % R], xq, K, N, M, capi.ORDER_COL_KSUPER, out=y)
+                capi.mul_mat_q4_0_q8_1(ws_[i % R], xq, K, N, M, capi.ORDER_COL_KSUPER,
+                                       capi.KERNEL_AUTO if kernel is None else kernel, out=y)
 
         sec, _ = time_graph_steps(torch, step, steps, 3, lambda: None)
         del ws_, base
@@ -542,6 +543,17 @@ def measure_extras(torch, capi, synth, dev, peaks):
     o = synth.ops(4096, 4096, 512)
     out["cfg3_M512"] = {"us": t * 1e6, "TOPS": o / t / 1e12, "frac_int8_peak": o / t / 1e12 / int8_peak,
                         "int8_peak_tops": int8_peak, "int8_peak_note": "2 x cuBLAS bf16 %s burst" % peaks["source"]}
+    # the opt-in prefill kernel: operands dequantised to fp16, tcgen05.mma.kind::f16; beside the default kernel's
+    # multiply on the same ready-made Q8_1 input
+    try:
+        for name, kern in (("gemm_mma", capi.KERNEL_GEMM_MMA), ("gemm_f16", capi.KERNEL_GEMM_F16)):
+            t = bench_linear(4096, 4096, 512, steps=50, fused=False, kernel=kern)
+            out["cfg3_M512_%s_mul_mat_only" % name] = {"us": t * 1e6, "TOPS": o / t / 1e12,
+                                                       "frac_int8_peak": o / t / 1e12 / int8_peak}
+        out["cfg3_M512_gemm_f16_mul_mat_only"]["note"] = (
+            "selected by name only: scaled operands rounded to fp16, about 3e-4 of max|y| from the reference formula")
+    except Exception as e:  # a secondary number must not take the headline down with it
+        out["cfg3_M512_gemm_f16_mul_mat_only"] = {"error": str(e)}
     return out
 
 
