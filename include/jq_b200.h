@@ -66,7 +66,7 @@ typedef enum jq_kernel {
     JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
     JQ_KERNEL_GEMM_MMA = 4,  /* M > 8: tiled int8 mma.sync GEMM with per-block rescale */
     JQ_KERNEL_GEMM_TC = 5,   /* M > 8, K % 128 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
-    JQ_KERNEL_GEMM_F16 = 6   /* M > 8, K % 128 == 0: operands dequantised to fp16, tcgen05.mma.kind::f16, fp32 accumulation.
+    JQ_KERNEL_GEMM_F16 = 6   /* M > 8, K % 256 == 0: operands dequantised to fp16, tcgen05.mma.kind::f16, fp32 accumulation.
                                 Rounds every scaled operand to fp16 (about 3e-4 of the largest output); never picked
                                 by JQ_KERNEL_AUTO */
 } jq_kernel;
@@ -92,7 +92,11 @@ int jq_get_option(int option, int *value_out);
  * The tcgen05 GEMM uses its slice differently: SM clock stamps of CTA (0,0) for the first 128
  * blocks of K, four groups of 128 rows x 8 columns (accumulator seen complete / previous block
  * accumulated / buffer handed back, one column per drain warp; then MMA issue time in column 0
- * and stage publication per producer warp in columns 1-3). */
+ * and stage publication per producer warp in columns 1-3).  The fp16-operand GEMM stamps SM clocks
+ * of CTA (0,0) for the first 64 stages: rows 0-63 weight warp 0, rows 64-127 activation warp 4 (the
+ * even stages, which the first producer group converts; columns: loop top, raw bytes landed, -,
+ * operand stage free, converted, published), rows 128-191 the MMA thread (stage seen full, MMAs and
+ * commit issued). */
 int jq_trace_enable(void *d_buf, int64_t n_launches);
 
 const char *jq_status_string(int status);

@@ -21,14 +21,27 @@
 // scales whose products are not subnormal (|d| * |q| >= 6.1e-5) keep full precision.
 //
 // A CTA owns a 128 (activation columns) x 128 (weight rows) tile of Y.  K advances in stages of 128
-// values (one Q8_1 block per column, four Q4_0 blocks per row):
-//   warps 0-3   one weight row per thread: 72 bytes loaded one stage ahead into registers, nibbles
-//               turned into fp16 by the magic-number trick (0x6400 | q is 1024 + q), scaled, stored
-//               as eight 128 x 16 operand tiles in the tensor core's canonical K-major layout.
-//   warps 4-7   one activation column per thread: 144 bytes, int8 -> fp16 the same way, scaled.
-//   warp 8      allocates tensor memory and issues, per stage, the rank-one MMA and eight
-//               128 x 128 x 16 MMAs; tcgen05.commit hands the stage back to the producers.
-// After the last stage warps 0-7 read the 128 x 128 fp32 accumulator and store it.
+// values (one Q8_1 block per column, four Q4_0 blocks per row) through three rings:
+//   raw rings       the quantized bytes as they lie in global memory, brought in by the copy engine:
+//                   one tiled tensor copy per stage for the 128 activation blocks (128 rows x 144
+//                   bytes), one per two stages for 144 bytes of each of the 128 weight rows.  A
+//                   per-thread load of "its" row touches 32 cache lines per warp instruction and
+//                   was measured to cost more than the conversion and the MMAs together.
+//   operand ring    three stages.  Weights: eight 128 x 16 fp16 tiles in shared memory in the tensor
+//                   core's canonical K-major layout.  Activations: tensor memory, lane = activation
+//                   column, 64 columns holding the 128 values of K in order; the MMA reads its A
+//                   operand from there, which halves the shared-memory traffic of a stage.
+// Warps:
+//   0-15   two groups of eight that take the stages in turn, so that one group's waits are covered
+//          by the other's work.  In a group, four warps convert one weight row per thread (nibbles
+//          become fp16 by the magic-number trick: 0x6400 | q is 1024 + q; then one exact subtraction
+//          and one rounded multiplication by the scale) and four warps one activation column per
+//          thread (int8 the same way; the 64 packed words go to tensor memory with tcgen05.st).
+//   16     allocates tensor memory; one thread issues, per stage, the rank-one MMA and eight
+//          128 x 128 x 16 MMAs, and tcgen05.commit hands the stage back to the producers.
+//   17     one thread issues the tensor copies.
+// After the last stage the sixteen producer warps read the 128 x 128 fp32 accumulator, turn it
+// around in shared memory and store 128 contiguous bytes of an output row per instruction.
 // Every mbarrier wait is a bounded poll; a wait that runs out sets the device fault word, and every
 // warp still reaches the common exit where tensor memory is released.
 #include <cuda.h>
