@@ -1,5 +1,5 @@
 // Prefill-regime multiply with the block scales folded into the operands: both matrices are
-// dequantised to fp16 on their way into shared memory and multiplied by tcgen05.mma.kind::f16 with
+// dequantised to fp16 on their way to the tensor core and multiplied by tcgen05.mma.kind::f16 with
 // fp32 accumulation in tensor memory, so nothing is drained or rescaled between blocks.
 //
 // Work to replace: q4_0_q8_1_mat_mul_kernel (reference src/cuda/mm_q4_0_q8_1.cu:164-289) for large
