@@ -1,4 +1,5 @@
-/* jq_weights_io.h - Q4_0 tensors in the reference's weight-fixture format: reader and offline quantizer.
+/* jq_weights_io.h - Q4_0 tensors in the reference's two weight formats (fixture directory, safetensors
+ * file): readers, writer and offline quantizer.
  *
  * The reference's loader (src/model/weight_loader.h:12-47) knows one tensor type, F32: a fixture is a
  * directory with config.txt ("key=value" lines), manifest.txt (one line per tensor:
@@ -50,6 +51,22 @@ typedef struct jq_weight_set {
 /* weight_loader_load_fixture (weight_loader.h:40) with the extra tensor type.  Returns JQ_OK or a
  * status from jq_b200.h (message in jq_last_error()); *out is NULL on failure. */
 int jq_weights_load_fixture(const char *dir, jq_weight_set **out);
+
+/* weight_loader_load_safetensors (weight_loader.h:42-47; reader src/model/safetensors_reader.cpp:400-418)
+ * with the extra tensor type.  `path` is one .safetensors file: 8 bytes of little-endian header length,
+ * a JSON header {name: {"dtype", "shape", "data_offsets"}}, then the data.  As in the reference:
+ * "__metadata__" is skipped, names are kept as they are, a config.txt in the file's directory is picked
+ * up when there is one, a file without tensors and a dtype the loader does not know are errors.
+ * F32 tensors are read as the reference reads them.  A Q4_0 tensor "w" is stored under the name
+ * "w.q4_0" with dtype "U8" and shape [rows, K / 32, 18] (one innermost row per block_q4_0), so the
+ * file stays readable by any safetensors tool; it is returned as "w" with dims [rows, K]. */
+int jq_weights_load_safetensors(const char *path, jq_weight_set **out);
+
+/* Writes a set as one .safetensors file in that convention: entries in name order with their data in
+ * the same order (the layout of the reference's writer, tests/fixture_utils.py:30-53), no
+ * "__metadata__", header padded with spaces to a multiple of 8 bytes.  config_text is not written:
+ * config.txt stays a file of its own beside the weights. */
+int jq_weights_save_safetensors(const jq_weight_set *set, const char *path);
 
 /* weight_load_result_destroy / weight_load_result_find (weight_loader.h:34-36). */
 void jq_weight_set_destroy(jq_weight_set *set);

@@ -1,4 +1,5 @@
-// Q4_0 tensors in the reference's weight-fixture format: reader and offline quantizer.
+// Q4_0 tensors in the reference's weight formats: fixture-directory reader and offline quantizer, then
+// (second half of the file) the safetensors reader and writer.
 //
 // Follows weight_loader_load_fixture (reference src/model/weight_loader.cpp:193-260, 330-350): the
 // same config.txt / manifest.txt grammar, the same limits in spirit (every dim positive, file size
@@ -326,4 +327,341 @@ extern "C" int jq_weights_quantize_fixture(const char *src_dir, const char *dst_
     jq_weight_set_destroy(set);
     if (n_quantized) *n_quantized = converted;
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The single-file format: safetensors.
+//
+// Follows weight_loader_load_safetensors and safetensors_read_file (reference
+// src/model/weight_loader.h:42-47, src/model/safetensors_reader.cpp:400-418): 8 bytes of little-endian
+// header length, a JSON header {name: {dtype, shape, data_offsets}}, then the data the offsets point
+// into; "__metadata__" is skipped, names are taken as they are, a config.txt beside the file is picked
+// up when present, and a dtype the loader does not know is an error.  The extra tensor type keeps the
+// file readable by any safetensors tool: a Q4_0 tensor "w" is stored under the name "w.q4_0" as U8
+// with shape [rows, K / 32, 18], one innermost row per block_q4_0.
+namespace {
+
+constexpr size_t kMaxHeaderBytes = 100u << 20;
+
+struct JsonCursor {
+    const char *p, *end;
+    void skip_ws() {
+        while (p < end && (*p == ' ' || *p == '\t' || *p == '\n' || *p == '\r')) ++p;
+    }
+    bool eat(char c) {
+        skip_ws();
+        if (p < end && *p == c) {
+            ++p;
+            return true;
+        }
+        return false;
+    }
+};
+
+void append_utf8(std::string *s, unsigned cp) {
+    if (cp < 0x80) {
+        s->push_back((char)cp);
+    } else if (cp < 0x800) {
+        s->push_back((char)(0xC0 | (cp >> 6)));
+        s->push_back((char)(0x80 | (cp & 0x3F)));
+    } else {
+        s->push_back((char)(0xE0 | (cp >> 12)));
+        s->push_back((char)(0x80 | ((cp >> 6) & 0x3F)));
+        s->push_back((char)(0x80 | (cp & 0x3F)));
+    }
+}
+
+bool json_string(JsonCursor *c, std::string *out) {
+    if (!c->eat('"')) return false;
+    out->clear();
+    while (c->p < c->end) {
+        const char ch = *c->p++;
+        if (ch == '"') return true;
+        if (ch != '\\') {
+            out->push_back(ch);
+            continue;
+        }
+        if (c->p >= c->end) return false;
+        const char e = *c->p++;
+        switch (e) {
+            case '"': case '\\': case '/': out->push_back(e); break;
+            case 'b': out->push_back('\b'); break;
+            case 'f': out->push_back('\f'); break;
+            case 'n': out->push_back('\n'); break;
+            case 'r': out->push_back('\r'); break;
+            case 't': out->push_back('\t'); break;
+            case 'u': {
+                if (c->end - c->p < 4) return false;
+                unsigned cp = 0;
+                for (int i = 0; i < 4; ++i) {
+                    const char h = *c->p++;
+                    cp <<= 4;
+                    if (h >= '0' && h <= '9') cp |= (unsigned)(h - '0');
+                    else if (h >= 'a' && h <= 'f') cp |= (unsigned)(h - 'a' + 10);
+                    else if (h >= 'A' && h <= 'F') cp |= (unsigned)(h - 'A' + 10);
+                    else return false;
+                }
+                append_utf8(out, cp);
+                break;
+            }
+            default: return false;
+        }
+    }
+    return false;
+}
+
+bool json_uint(JsonCursor *c, int64_t *out) {
+    c->skip_ws();
+    if (c->p >= c->end || *c->p < '0' || *c->p > '9') return false;
+    int64_t v = 0;
+    while (c->p < c->end && *c->p >= '0' && *c->p <= '9') {
+        if (v > (INT64_MAX - 9) / 10) return false;
+        v = v * 10 + (*c->p++ - '0');
+    }
+    *out = v;
+    return true;
+}
+
+bool json_uint_array(JsonCursor *c, std::vector<int64_t> *out) {
+    out->clear();
+    if (!c->eat('[')) return false;
+    if (c->eat(']')) return true;
+    for (;;) {
+        int64_t v = 0;
+        if (!json_uint(c, &v)) return false;
+        out->push_back(v);
+        if (c->eat(']')) return true;
+        if (!c->eat(',')) return false;
+    }
+}
+
+// skips one JSON value of any kind (used for "__metadata__" and for keys this reader does not need)
+bool json_skip(JsonCursor *c, int depth = 0) {
+    if (depth > 32) return false;
+    c->skip_ws();
+    if (c->p >= c->end) return false;
+    if (*c->p == '"') {
+        std::string s;
+        return json_string(c, &s);
+    }
+    if (*c->p == '{' || *c->p == '[') {
+        const char close = *c->p == '{' ? '}' : ']';
+        const bool object = *c->p == '{';
+        ++c->p;
+        if (c->eat(close)) return true;
+        for (;;) {
+            if (object) {
+                std::string key;
+                if (!json_string(c, &key) || !c->eat(':')) return false;
+            }
+            if (!json_skip(c, depth + 1)) return false;
+            if (c->eat(close)) return true;
+            if (!c->eat(',')) return false;
+        }
+    }
+    // number, true, false, null
+    const char *start = c->p;
+    while (c->p < c->end && *c->p != ',' && *c->p != '}' && *c->p != ']' && *c->p != ' ' && *c->p != '\n' && *c->p != '\t' &&
+           *c->p != '\r')
+        ++c->p;
+    return c->p > start;
+}
+
+struct StEntry {
+    std::string name, dtype;
+    std::vector<int64_t> shape, offsets;
+};
+
+int parse_st_header(const char *json, size_t n, std::vector<StEntry> *entries) {
+    JsonCursor c{json, json + n};
+    if (!c.eat('{')) return set_error(JQ_ERR_SHAPE, "safetensors header is not a JSON object");
+    if (c.eat('}')) return JQ_OK;
+    for (;;) {
+        StEntry e;
+        if (!json_string(&c, &e.name) || !c.eat(':')) return set_error(JQ_ERR_SHAPE, "safetensors header: expected \"name\":");
+        if (e.name == "__metadata__") {
+            if (!json_skip(&c)) return set_error(JQ_ERR_SHAPE, "safetensors header: malformed __metadata__");
+        } else {
+            if ((int)entries->size() >= kMaxTensors) return set_error(JQ_ERR_TOO_LARGE, "safetensors header: too many tensors");
+            if (!c.eat('{')) return set_error(JQ_ERR_SHAPE, "safetensors header: %s is not an object", e.name.c_str());
+            if (!c.eat('}')) {
+                for (;;) {
+                    std::string key;
+                    if (!json_string(&c, &key) || !c.eat(':')) return set_error(JQ_ERR_SHAPE, "safetensors header: malformed entry %s", e.name.c_str());
+                    bool ok;
+                    if (key == "dtype") ok = json_string(&c, &e.dtype);
+                    else if (key == "shape") ok = json_uint_array(&c, &e.shape);
+                    else if (key == "data_offsets") ok = json_uint_array(&c, &e.offsets);
+                    else ok = json_skip(&c);
+                    if (!ok) return set_error(JQ_ERR_SHAPE, "safetensors header: bad value of %s.%s", e.name.c_str(), key.c_str());
+                    if (c.eat('}')) break;
+                    if (!c.eat(',')) return set_error(JQ_ERR_SHAPE, "safetensors header: malformed entry %s", e.name.c_str());
+                }
+            }
+            if (e.dtype.empty() || e.shape.empty() || e.shape.size() > (size_t)kMaxNdim || e.offsets.size() != 2 ||
+                e.offsets[1] <= e.offsets[0])
+                return set_error(JQ_ERR_SHAPE, "safetensors header: %s needs dtype, a shape of 1..%d dims and data_offsets [begin, end)",
+                                 e.name.c_str(), kMaxNdim);
+            entries->push_back(std::move(e));
+        }
+        if (c.eat('}')) break;
+        if (!c.eat(',')) return set_error(JQ_ERR_SHAPE, "safetensors header: expected ',' or '}'");
+    }
+    return JQ_OK;
+}
+
+std::string json_quote(const char *s) {
+    std::string q = "\"";
+    for (; *s; ++s) {
+        const unsigned char ch = (unsigned char)*s;
+        if (ch == '"' || ch == '\\') {
+            q.push_back('\\');
+            q.push_back((char)ch);
+        } else if (ch < 0x20) {
+            char buf[8];
+            std::snprintf(buf, sizeof(buf), "\\u%04x", ch);
+            q += buf;
+        } else {
+            q.push_back((char)ch);
+        }
+    }
+    q.push_back('"');
+    return q;
+}
+
+std::string dir_of(const std::string &path) {
+    const size_t slash = path.find_last_of('/');
+    return slash == std::string::npos ? std::string(".") : (slash == 0 ? std::string("/") : path.substr(0, slash));
+}
+
+}  // namespace
+
+extern "C" int jq_weights_load_safetensors(const char *path, jq_weight_set **out) {
+    if (!out) return set_error(JQ_ERR_INVALID_ARG, "null out pointer");
+    *out = nullptr;
+    if (!path) return set_error(JQ_ERR_INVALID_ARG, "null path");
+    std::vector<char> file;
+    if (!read_file(path, &file)) return set_error(JQ_ERR_INVALID_ARG, "cannot read %s", path);
+    if (file.size() < 8) return set_error(JQ_ERR_SHAPE, "%s: shorter than the 8-byte header length", path);
+    uint64_t header_len = 0;
+    for (int i = 7; i >= 0; --i) header_len = (header_len << 8) | (unsigned char)file[(size_t)i];
+    if (header_len > kMaxHeaderBytes || header_len > file.size() - 8)
+        return set_error(JQ_ERR_SHAPE, "%s: header length %llu exceeds the file", path, (unsigned long long)header_len);
+    std::vector<StEntry> entries;
+    if (int rc = parse_st_header(file.data() + 8, (size_t)header_len, &entries)) return rc;
+    if (entries.empty()) return set_error(JQ_ERR_SHAPE, "%s: no tensors", path);
+    const char *blob = file.data() + 8 + header_len;
+    const uint64_t blob_size = file.size() - 8 - header_len;
+
+    jq_weight_set *set = static_cast<jq_weight_set *>(std::calloc(1, sizeof(jq_weight_set)));
+    if (!set) return set_error(JQ_ERR_CUDA, "out of host memory");
+    std::vector<char> cfg;
+    read_file(dir_of(path) + "/config.txt", &cfg);  // optional (weight_loader.h:44-45)
+    set->config_text = dup_c(std::string(cfg.begin(), cfg.end()));
+    set->tensors = static_cast<jq_host_tensor *>(std::calloc(entries.size(), sizeof(jq_host_tensor)));
+    if (!set->tensors || !set->config_text) {
+        jq_weight_set_destroy(set);
+        return set_error(JQ_ERR_CUDA, "out of host memory");
+    }
+    for (const StEntry &e : entries) {
+        std::string name = e.name;
+        std::vector<int64_t> dims = e.shape;
+        int dtype = JQ_WEIGHT_F32;
+        int64_t want = 0;
+        bool overflow = false;
+        int64_t numel = 1;
+        for (int64_t d : e.shape) {
+            if (d != 0 && numel > INT64_MAX / 32 / d) overflow = true;
+            numel *= d;
+        }
+        if (e.dtype == "F32") {
+            want = numel * (int64_t)sizeof(float);
+        } else if (e.dtype == "U8" && ends_with(e.name, ".q4_0") && e.name.size() > 5 && e.shape.size() == 3 && e.shape[2] == 18) {
+            dtype = JQ_WEIGHT_Q4_0;
+            name = e.name.substr(0, e.name.size() - 5);
+            dims = {e.shape[0], e.shape[1] * 32};
+            want = numel;
+        } else {
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_UNSUPPORTED, "%s: unsupported dtype %s for tensor %s (F32, or U8 [rows, K/32, 18] named *.q4_0)", path,
+                             e.dtype.c_str(), e.name.c_str());
+        }
+        const uint64_t begin = (uint64_t)e.offsets[0], end = (uint64_t)e.offsets[1];
+        if (overflow || numel <= 0 || end > blob_size || (int64_t)(end - begin) != want) {
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_SHAPE, "%s: tensor %s: data_offsets [%llu, %llu) do not match its shape (%lld bytes) or the file", path,
+                             e.name.c_str(), (unsigned long long)begin, (unsigned long long)end, (long long)want);
+        }
+        jq_host_tensor *t = &set->tensors[set->num_tensors];
+        t->name = dup_c(name);
+        t->dims = static_cast<int64_t *>(std::malloc(dims.size() * sizeof(int64_t)));
+        t->data = std::malloc((size_t)want);
+        if (!t->name || !t->dims || !t->data) {
+            free_tensor(t);
+            jq_weight_set_destroy(set);
+            return set_error(JQ_ERR_CUDA, "out of host memory");
+        }
+        std::memcpy(t->dims, dims.data(), dims.size() * sizeof(int64_t));
+        std::memcpy(t->data, blob + begin, (size_t)want);
+        t->ndim = (int)dims.size();
+        t->dtype = dtype;
+        t->nbytes = (size_t)want;
+        ++set->num_tensors;
+    }
+    *out = set;
+    return JQ_OK;
+}
+
+extern "C" int jq_weights_save_safetensors(const jq_weight_set *set, const char *path) {
+    if (!set || !path) return set_error(JQ_ERR_INVALID_ARG, "null argument");
+    if (set->num_tensors <= 0) return set_error(JQ_ERR_INVALID_ARG, "a safetensors file needs at least one tensor");
+    // entries in name order, data in the same order, as the reference's own writer lays a file out
+    // (tests/fixture_utils.py:30-53)
+    std::vector<int> order((size_t)set->num_tensors);
+    for (int i = 0; i < set->num_tensors; ++i) order[(size_t)i] = i;
+    for (size_t i = 1; i < order.size(); ++i) {  // insertion sort: a handful of tensors per layer
+        const int v = order[i];
+        size_t j = i;
+        while (j > 0 && std::strcmp(set->tensors[order[j - 1]].name, set->tensors[v].name) > 0) {
+            order[j] = order[j - 1];
+            --j;
+        }
+        order[j] = v;
+    }
+    std::string header = "{";
+    uint64_t offset = 0;
+    for (size_t k = 0; k < order.size(); ++k) {
+        const jq_host_tensor &t = set->tensors[order[k]];
+        std::ostringstream e;
+        if (t.dtype == JQ_WEIGHT_Q4_0) {
+            if (t.ndim != 2 || t.dims[1] % 32 != 0 || t.nbytes != jq_q4_0_bytes(t.dims[0], t.dims[1]))
+                return set_error(JQ_ERR_SHAPE, "%s: a Q4_0 tensor needs dims [rows, K] with K %% 32 == 0", t.name);
+            e << json_quote((std::string(t.name) + ".q4_0").c_str()) << ":{\"dtype\":\"U8\",\"shape\":[" << t.dims[0] << "," << t.dims[1] / 32
+              << ",18]";
+        } else if (t.dtype == JQ_WEIGHT_F32) {
+            e << json_quote(t.name) << ":{\"dtype\":\"F32\",\"shape\":[";
+            for (int d = 0; d < t.ndim; ++d) e << (d ? "," : "") << t.dims[d];
+            e << "]";
+        } else {
+            return set_error(JQ_ERR_INVALID_ARG, "%s: unknown dtype %d", t.name, t.dtype);
+        }
+        e << ",\"data_offsets\":[" << offset << "," << offset + t.nbytes << "]}";
+        offset += t.nbytes;
+        header += (k ? "," : "") + e.str();
+    }
+    header += "}";
+    while (header.size() % 8 != 0) header.push_back(' ');  // the data starts on an 8-byte boundary
+    std::ofstream o(path, std::ios::binary | std::ios::trunc);
+    if (!o.is_open()) return set_error(JQ_ERR_INVALID_ARG, "cannot write %s", path);
+    unsigned char len[8];
+    for (int i = 0; i < 8; ++i) len[i] = (unsigned char)((uint64_t)header.size() >> (8 * i));
+    o.write(reinterpret_cast<const char *>(len), 8);
+    o.write(header.data(), (std::streamsize)header.size());
+    for (int idx : order) {
+        const jq_host_tensor &t = set->tensors[idx];
+        if (t.nbytes) o.write(static_cast<const char *>(t.data), (std::streamsize)t.nbytes);
+    }
+    o.flush();
+    if (!o) return set_error(JQ_ERR_INVALID_ARG, "short write to %s", path);
+    return JQ_OK;
 }
