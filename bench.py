@@ -195,6 +195,7 @@ def workload_config(K, N, M, world, shape="cfg2"):
                     "cfg2 decode GEMV: quantize_q8_1 + Q4_0xQ8_1 mul_mat, M=%d, K=%d, N=%d per GPU, seed 1, "
                     "1%% outlier channels x20" % (M, K, N),
         "M": M, "K": K, "N_per_gpu": N, "N_total": N * world,
+        "gather_message_bytes_per_rank": M * N * 4 if world > 1 else 0,
         "parallelism": "single GPU" if world == 1 else "N-sharded x%d, outputs all-gathered along N" % world,
         "l2": "weights rotate through distinct copies totalling > 3x L2 between steps (cold L2)",
         "overlap": "steps are launched with programmatic dependent launch; JQ_OPT_STATIC_WEIGHTS=1 lets a step "
