@@ -33,8 +33,10 @@ CUDA_SOURCES = [
     "jq_capi.cu",
     "ref_compat.cpp",
     "weights_io.cpp",
+    "model_q4_0.cpp",
 ]
-HEADERS = ["jq_common.cuh", "tc_common.cuh", os.path.join(INCLUDE_DIR, "jq_b200.h"), os.path.join(INCLUDE_DIR, "jq_weights_io.h")]
+HEADERS = ["jq_common.cuh", "tc_common.cuh", os.path.join(INCLUDE_DIR, "jq_b200.h"), os.path.join(INCLUDE_DIR, "jq_weights_io.h"),
+           os.path.join(INCLUDE_DIR, "jq_model.h")]
 BINDINGS = {"q8_1_me": "q8_1_binding.cpp", "mm_q4_0_q8_1_me": "mm_q4_0_q8_1_binding.cpp"}
 
 NVCC_FLAGS = [

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared_symbols():
-    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in ("jq_b200.h", "jq_weights_io.h"))
+    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in ("jq_b200.h", "jq_weights_io.h", "jq_model.h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(jq_[a-z0-9_]+)\s*\(", text)))
 
