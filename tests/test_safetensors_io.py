@@ -145,3 +145,43 @@ def test_errors_are_reported(native_lib, tmp_path):
     _raw_file(p, {"w.q4_0": {"dtype": "U8", "shape": [2, 1, 18], "data_offsets": [0, 36]}}, b"\x11" * 36)  # and a good one
     _, got = W.load_safetensors(p)
     assert got["w"].dtype == W.DTYPE_Q4_0 and got["w"].dims == (2, 32) and got["w"].data.shape == (2, 18)
+
+
+def test_random_tensor_sets_round_trip(native_lib, tmp_path):
+    """Seeded random sets of tensors (names with dots, 1 to 4 dims, F32 and Q4_0 mixed) survive
+    writer -> loader through both writers, byte for byte."""
+    import ctypes
+
+    from jjjetson_ops_b200 import weights_io as W
+
+    rng = np.random.default_rng(2024)
+    for case in range(12):
+        tensors = {}
+        for i in range(int(rng.integers(1, 9))):
+            name = "t%d.%s" % (i, "".join(rng.choice(list("abw_q0"), size=int(rng.integers(1, 8)))))
+            if rng.random() < 0.4:
+                rows, K = int(rng.integers(1, 20)), 32 * int(rng.integers(1, 9))
+                raw = rng.integers(0, 256, size=(rows, K // 32 * 18), dtype=np.uint8)
+                tensors[name] = W.Tensor(W.DTYPE_Q4_0, (rows, K), raw)
+            else:
+                shape = tuple(int(d) for d in rng.integers(1, 7, size=int(rng.integers(1, 5))))
+                tensors[name] = rng.standard_normal(shape).astype(np.float32)
+        py_file = str(tmp_path / ("py%d.safetensors" % case))
+        W.write_safetensors(py_file, tensors)
+        _, got = W.load_safetensors(py_file)
+        # the library's own writer, fed with what it just loaded
+        ps = ctypes.POINTER(W._WeightSet)()
+        native_lib.check(W._lib.jq_weights_load_safetensors(py_file.encode(), ctypes.byref(ps)))
+        c_file = str(tmp_path / ("c%d.safetensors" % case))
+        try:
+            native_lib.check(W._lib.jq_weights_save_safetensors(ps, c_file.encode()))
+        finally:
+            W._lib.jq_weight_set_destroy(ps)
+        _, again = W.load_safetensors(c_file)
+        assert set(got) == set(again) == set(tensors)
+        for name, t in tensors.items():
+            exp = t.data if isinstance(t, W.Tensor) else t
+            for loaded in (got[name], again[name]):
+                assert loaded.dims == (t.dims if isinstance(t, W.Tensor) else t.shape)
+                assert loaded.dtype == (W.DTYPE_Q4_0 if isinstance(t, W.Tensor) else W.DTYPE_F32)
+                assert np.array_equal(loaded.data.reshape(-1), np.asarray(exp).reshape(-1))
