@@ -1,7 +1,8 @@
 """B200 (sm_100a) drop-in for the Q4_0 x Q8_1 quantized-linear path of JJJetson_Ops.
 
 The product is ``libjq_b200.so`` (C ABI, ``include/jq_b200.h``) plus the two pybind11 modules the
-reference ships for this path (``q8_1_me`` and ``mm_q4_0_q8_1_me``, under ``python/``).  This
+reference ships for this path (``q8_1_me`` and ``mm_q4_0_q8_1_me``, under ``python/``, where the
+reference-named loader module ``weight_loader_me`` sits too).  This
 package is the thin host-side layer above them: ``capi`` binds the C ABI with ctypes and takes
 torch CUDA tensors as plain device memory, ``synth`` builds the seeded synthetic workloads,
 ``sharded`` runs one linear N-sharded over several GPUs.
