@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <exception>
 #include <fstream>
 #include <sstream>
 #include <string>
@@ -49,14 +50,20 @@ char *dup_c(const std::string &s) {
     return p;
 }
 
+// Whole regular file -> bytes.  A directory opens as a stream too (and reports a nonsense length), so the
+// path is checked first; a file too large for memory is a failed read, not an exception.
 bool read_file(const std::string &path, std::vector<char> *out) {
-    std::ifstream in(path, std::ios::binary | std::ios::ate);
+    struct stat st;
+    if (stat(path.c_str(), &st) != 0 || !S_ISREG(st.st_mode) || st.st_size < 0) return false;
+    std::ifstream in(path, std::ios::binary);
     if (!in.is_open()) return false;
-    const std::streamsize n = in.tellg();
-    if (n < 0) return false;
-    out->resize((size_t)n);
-    in.seekg(0);
-    return n == 0 || (bool)in.read(out->data(), n);
+    const size_t n = (size_t)st.st_size;
+    try {
+        out->resize(n);
+    } catch (const std::exception &) {
+        return false;
+    }
+    return n == 0 || (bool)in.read(out->data(), (std::streamsize)n);
 }
 
 bool write_file(const std::string &path, const void *data, size_t n) {
@@ -106,9 +113,13 @@ int parse_manifest(const std::string &dir, std::vector<ManifestEntry> *entries) 
     return JQ_OK;
 }
 
+// product of the (positive) dims, or -1 when it would not fit a byte count
 int64_t numel_of(const std::vector<int64_t> &dims) {
     int64_t n = 1;
-    for (int64_t d : dims) n *= d;
+    for (int64_t d : dims) {
+        if (d <= 0 || n > (INT64_MAX / 64) / d) return -1;
+        n *= d;
+    }
     return n;
 }
 
@@ -120,10 +131,19 @@ int64_t expected_bytes(const ManifestEntry &e, int *dtype) {
             set_error(JQ_ERR_SHAPE, "%s: a Q4_0 tensor needs dims [rows, K] with K %% 32 == 0", e.name.c_str());
             return -1;
         }
+        if (numel_of(e.dims) < 0) {
+            set_error(JQ_ERR_TOO_LARGE, "%s: dims too large", e.name.c_str());
+            return -1;
+        }
         return (int64_t)jq_q4_0_bytes(e.dims[0], e.dims[1]);
     }
     *dtype = JQ_WEIGHT_F32;
-    return numel_of(e.dims) * (int64_t)sizeof(float);
+    const int64_t n = numel_of(e.dims);
+    if (n < 0) {
+        set_error(JQ_ERR_TOO_LARGE, "%s: dims too large", e.name.c_str());
+        return -1;
+    }
+    return n * (int64_t)sizeof(float);
 }
 
 bool config_lookup(const char *text, const char *key, double *value) {
@@ -571,7 +591,10 @@ extern "C" int jq_weights_load_safetensors(const char *path, jq_weight_set **out
         bool overflow = false;
         int64_t numel = 1;
         for (int64_t d : e.shape) {
-            if (d != 0 && numel > INT64_MAX / 32 / d) overflow = true;
+            if (d != 0 && numel > INT64_MAX / 32 / d) {
+                overflow = true;
+                break;
+            }
             numel *= d;
         }
         if (e.dtype == "F32") {

@@ -54,6 +54,13 @@ def test_fixture_errors_are_reported(native_lib, tmp_path):
     (d / "w.q4_0").write_bytes(b"\0" * 18)
     with pytest.raises(c.JqError):
         W.load_fixture(str(d))
+    (d / "sub").mkdir()
+    (d / "manifest.txt").write_text("w 2 4 8 sub\n")  # a directory where a tensor file should be
+    with pytest.raises(c.JqError):
+        W.load_fixture(str(d))
+    (d / "manifest.txt").write_text("w 3 3037000500 3037000500 3037000500 a.f32\n")  # dims whose product overflows
+    with pytest.raises(c.JqError):
+        W.load_fixture(str(d))
     (d / "manifest.txt").write_text("w 2 4 8 ../escape.f32\n")
     with pytest.raises(c.JqError):
         W.load_fixture(str(d))
