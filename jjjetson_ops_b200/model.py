@@ -154,3 +154,29 @@ class ModelQ4_0:
 def layer_names(i: int) -> List[str]:
     return ["layer%d.%s" % (i, s) for s in ("w_q", "w_k", "w_v", "w_o", "w_gate", "w_up", "w_down", "w_input_layernorm",
                                             "w_post_attention_layernorm")]
+
+
+def main(argv=None) -> int:
+    """``python -m jjjetson_ops_b200.model PATH``: validate a quantized checkpoint (fixture directory or
+    safetensors file) and print its device layout.  Needs no GPU."""
+    import sys
+
+    argv = sys.argv[1:] if argv is None else argv
+    if len(argv) != 1:
+        print(main.__doc__, file=sys.stderr)
+        return 2
+    try:
+        config, slots, total = plan(argv[0])
+    except capi.JqError as e:
+        print("not a loadable quantized model: %s" % e, file=sys.stderr)
+        return 1
+    print(" ".join("%s=%g" % kv for kv in config.items()))
+    print("%-44s %-5s %10s %8s %14s %12s" % ("tensor", "type", "rows", "K", "offset", "bytes"))
+    for s in slots:
+        print("%-44s %-5s %10d %8d %14d %12d" % (s.name, "Q4_0" if s.dtype == _wio.DTYPE_Q4_0 else "F32", s.rows, s.K, s.offset, s.nbytes))
+    print("total %d bytes in one allocation" % total)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

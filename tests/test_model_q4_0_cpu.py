@@ -142,3 +142,17 @@ def test_create_fails_loudly_without_a_device(native_lib, oracle, tmp_path):
     with pytest.raises(native_lib.JqError) as e:
         model.ModelQ4_0(str(tmp_path))
     assert e.value.status == native_lib.ERR_CUDA
+
+
+def test_command_line_prints_the_layout(native_lib, oracle, tmp_path, capsys):
+    from jjjetson_ops_b200 import model, weights_io as W
+
+    cfg = dict(CONFIG, num_layers=1)
+    W.write_fixture(str(tmp_path / "ok"), cfg, _quantized_tensors(oracle, W, cfg))
+    assert model.main([str(tmp_path / "ok")]) == 0
+    out = capsys.readouterr().out
+    assert "layer0.w_down" in out and "Q4_0" in out and "total" in out
+    W.write_fixture(str(tmp_path / "fp32"), cfg, _quantized_tensors(oracle, W, cfg, quantize=False))
+    assert model.main([str(tmp_path / "fp32")]) == 1
+    assert "quantize" in capsys.readouterr().err
+    assert model.main([]) == 2
