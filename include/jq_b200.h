@@ -79,7 +79,13 @@ typedef enum jq_option {
      * draining, before they wait for it; activations and outputs are always ordered normally.
      * 0 (default): the weight stream, too, waits for the previous kernel. */
     JQ_OPT_STATIC_WEIGHTS = 0,
-    JQ_OPT_COUNT_ = 1
+    /* 1: JQ_KERNEL_AUTO may take the fp16-operand tcgen05 GEMM (JQ_KERNEL_GEMM_F16) for batches of 64
+     * activation columns and more when its shape rules hold (K % 256 == 0, 16-byte aligned buffers): about
+     * 2.5x the integer GEMM's throughput, results within about 3e-4 of the largest output of the exact
+     * path instead of 1e-6, activations must fit fp16's range.  0 (default): every automatic choice is an
+     * exact-integer kernel. */
+    JQ_OPT_PREFILL_FP16_OPERANDS = 1,
+    JQ_OPT_COUNT_ = 2
 } jq_option;
 int jq_set_option(int option, int value);
 int jq_get_option(int option, int *value_out);

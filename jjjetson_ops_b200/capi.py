@@ -115,6 +115,7 @@ def check(status: int) -> None:
 
 
 OPT_STATIC_WEIGHTS = 0
+OPT_PREFILL_FP16_OPERANDS = 1
 
 
 def set_option(option: int, value: int) -> None:

@@ -126,6 +126,9 @@ int check_mul_mat_shape(int64_t K, int64_t N, int64_t M) {
     return JQ_OK;
 }
 
+// Smallest batch for which JQ_OPT_PREFILL_FP16_OPERANDS changes the automatic choice: half a 128-column tile.
+constexpr int64_t FP16_OPERANDS_MIN_COLUMNS = 64;
+
 int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N,
                      int64_t M, int order, int kernel) {
     if (N == 0 || M == 0) return JQ_OK;
@@ -159,6 +162,8 @@ int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *
         }
         if (rc != JQ_OK && rc != JQ_ERR_UNSUPPORTED) return rc;
     }
+    if (rc == JQ_ERR_UNSUPPORTED && M >= FP16_OPERANDS_MIN_COLUMNS && option_value(JQ_OPT_PREFILL_FP16_OPERANDS) != 0)
+        rc = launch_gemm_f16(st, d_w, d_xq, d_y, K, N, M, order);  // the caller opted in to its precision
     if (rc == JQ_ERR_UNSUPPORTED && M > 8) rc = launch_gemm_mma(st, d_w, d_xq, d_y, K, N, M, order);
     if (rc == JQ_ERR_UNSUPPORTED) rc = launch_mmq_generic(st, d_w, d_xq, d_y, K, N, M, order);
     if (rc == JQ_OK) t_last_error.clear();

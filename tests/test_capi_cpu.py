@@ -95,3 +95,19 @@ def test_reference_named_modules_import_and_validate(native_lib):
                input_dims=[128, 1, 1, 1], nrows_out=8, ncols_k=128)  # weight buffer too small
     qs, d, s = q8.parse(np.zeros(288, np.uint8), 2)
     assert qs.shape == (2, 128) and d.shape == (2, 4) and s.dtype == np.float32
+
+
+def test_options_round_trip():
+    """Process-wide switches are plain host state: set, read back, reject unknown ones."""
+    from jjjetson_ops_b200 import capi
+
+    for opt in (capi.OPT_STATIC_WEIGHTS, capi.OPT_PREFILL_FP16_OPERANDS):
+        assert capi.get_option(opt) == 0  # both default to off
+        capi.set_option(opt, 1)
+        try:
+            assert capi.get_option(opt) == 1
+        finally:
+            capi.set_option(opt, 0)
+        assert capi.get_option(opt) == 0
+    with pytest.raises(capi.JqError):
+        capi.set_option(99, 1)
