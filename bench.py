@@ -555,6 +555,15 @@ def measure_extras(torch, capi, synth, dev, peaks):
             "selected by name only: scaled operands rounded to fp16, about 3e-4 of max|y| from the reference formula")
     except Exception as e:  # a secondary number must not take the headline down with it
         out["cfg3_M512_gemm_f16_mul_mat_only"] = {"error": str(e)}
+    # the prefill chain once more with the automatic dispatch allowed to take that kernel (opt-in switch of the C ABI)
+    try:
+        capi.set_option(capi.OPT_PREFILL_FP16_OPERANDS, 1)
+        try:
+            out["cfg5_chain_M128_fp16_operands_opt_in"] = bench_layer_chain(torch, capi, synth, dev, peaks, 128)
+        finally:
+            capi.set_option(capi.OPT_PREFILL_FP16_OPERANDS, 0)
+    except Exception as e:
+        out["cfg5_chain_M128_fp16_operands_opt_in"] = {"error": str(e)}
     return out
 
 
