@@ -48,3 +48,11 @@ def test_own_arm_needs_a_gpu():
     r = _run("--steps", "1", "--warmup", "1", "--no-extras", timeout=120)
     assert r.returncode != 0  # fails loudly: there is no CPU path to fall back to
     assert not [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_reference_arm_under_a_launcher_runs_on_rank_zero_only():
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29577")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                       cwd=ROOT, capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert not [ln for ln in r.stdout.splitlines() if ln.startswith("{")]  # the other ranks exit without work
