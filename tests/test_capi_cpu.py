@@ -111,3 +111,16 @@ def test_options_round_trip():
         assert capi.get_option(opt) == 0
     with pytest.raises(capi.JqError):
         capi.set_option(99, 1)
+
+
+def test_public_headers_are_plain_c():
+    """The boundary is a C ABI: every public header compiles as C99 on its own, warnings included."""
+    import subprocess
+
+    inc = os.path.join(ROOT, "include")
+    for h in sorted(os.listdir(inc)):
+        if not h.endswith(".h"):
+            continue
+        r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I", inc, "-x", "c", "-"],
+                           input='#include "%s"\n' % h, capture_output=True, text=True)
+        assert r.returncode == 0, (h, r.stderr)
