@@ -85,7 +85,13 @@ typedef enum jq_option {
      * path instead of 1e-6, activations must fit fp16's range.  0 (default): every automatic choice is an
      * exact-integer kernel. */
     JQ_OPT_PREFILL_FP16_OPERANDS = 1,
-    JQ_OPT_COUNT_ = 2
+    /* Number of polls after which a bounded device-side wait (for a bulk copy, or for the bands of an
+     * all-gather) gives up, sets the fault word read by jq_device_fault() and lets its kernel return.
+     * It applies to the decode kernels' waits and to jq_allgather_wait_device.
+     * 0 (default): 2^22 polls, far beyond any wait of a healthy run.  The value is read when a kernel is
+     * launched.  There is no counterpart in the reference (its kernels never wait on one another). */
+    JQ_OPT_WAIT_POLL_LIMIT = 2,
+    JQ_OPT_COUNT_ = 3
 } jq_option;
 int jq_set_option(int option, int value);
 int jq_get_option(int option, int *value_out);
@@ -253,8 +259,10 @@ int jq_block_sums_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_
  * layout comes from (d = signed max-magnitude / -8, q = min(15, trunc(w/d + 8.5))). */
 int jq_quantize_q4_0_device(void *stream, const float *d_w, void *d_wq, int64_t N, int64_t K);
 
-/* Non-zero after a kernel of this library gave up on a bounded wait on the current device.
- * Synchronises the device.  `clear` != 0 resets it. */
+/* *fault_out is non-zero after a kernel of this library gave up on a bounded wait on the current device
+ * (1: a bulk copy or pipeline stage never completed; 2: the bands of an all-gather never arrived); the call
+ * then returns JQ_ERR_TIMEOUT, else JQ_OK.  The kernel that gave up has returned, its output is not valid,
+ * and the device stays usable.  Synchronises the device.  `clear` != 0 resets the word. */
 int jq_device_fault(int clear, int *fault_out);
 
 /* ---- host entry points (reference-facing) ------------------------------------------------ */

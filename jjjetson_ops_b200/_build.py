@@ -39,7 +39,7 @@ HEADERS = ["jq_common.cuh", "tc_common.cuh", os.path.join(INCLUDE_DIR, "jq_b200.
            os.path.join(INCLUDE_DIR, "jq_model.h")]
 BINDINGS = {"q8_1_me": "q8_1_binding.cpp", "mm_q4_0_q8_1_me": "mm_q4_0_q8_1_binding.cpp"}
 
-NVCC_FLAGS = [
+NVCC_FLAGS = [*os.environ.get("JQ_EXTRA_NVCC_FLAGS", "").split(),
     "-std=c++17",
     "-O3",
     "-gencode",

@@ -116,6 +116,7 @@ def check(status: int) -> None:
 
 OPT_STATIC_WEIGHTS = 0
 OPT_PREFILL_FP16_OPERANDS = 1
+OPT_WAIT_POLL_LIMIT = 2
 
 
 def set_option(option: int, value: int) -> None:
@@ -333,8 +334,12 @@ def quantize_q4_0(w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.
 
 
 def device_fault(clear: bool = True) -> int:
+    """The device's fault word (0: no bounded wait has given up).  A non-zero word comes with status
+    JQ_ERR_TIMEOUT, which is reported through the return value here, not raised."""
     v = ctypes.c_int(0)
-    check(_lib.jq_device_fault(1 if clear else 0, ctypes.byref(v)))
+    rc = _lib.jq_device_fault(1 if clear else 0, ctypes.byref(v))
+    if rc not in (OK, ERR_TIMEOUT):
+        check(rc)
     return int(v.value)
 
 

@@ -8,6 +8,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "jq_common.cuh"
 
@@ -43,6 +44,11 @@ void *next_trace_slot() {
     const long long i = g_trace_next.fetch_add(1);
     if (i >= g_trace_slots.load()) return nullptr;
     return buf + (size_t)i * TRACE_CTAS * 8;
+}
+
+uint32_t wait_poll_limit() {
+    const int v = option_value(JQ_OPT_WAIT_POLL_LIMIT);
+    return v > 0 ? (uint32_t)v : (1u << 22);
 }
 
 int option_value(int option) {
@@ -83,6 +89,35 @@ int device_caps(DeviceCaps *out) {
         d.caps_ok = true;
     }
     *out = d.caps;
+    return JQ_OK;
+}
+
+int ensure_dynamic_smem(const void *kernel, int bytes, bool max_carveout) {
+    struct Entry {
+        const void *fn;
+        int dev, bytes;
+    };
+    static std::vector<Entry> table;
+    static std::mutex table_mutex;
+    int dev = 0;
+    JQ_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(table_mutex);
+    Entry *e = nullptr;
+    for (Entry &t : table) {
+        if (t.fn == kernel && t.dev == dev) {
+            e = &t;
+            break;
+        }
+    }
+    if (e != nullptr && e->bytes >= bytes) return JQ_OK;
+    JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (e == nullptr) {
+        if (max_carveout)
+            JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        table.push_back(Entry{kernel, dev, bytes});
+    } else {
+        e->bytes = bytes;
+    }
     return JQ_OK;
 }
 
@@ -471,6 +506,10 @@ int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *
                                                                        (long long)n_offset, (long long)(n_offset + N_local), (long long)N_total);
     if (M < 1 || N_local < 1 || K < 1) return set_error(JQ_ERR_INVALID_ARG, "empty shape");
     if (M > 2 && d_ws == nullptr) return set_error(JQ_ERR_INVALID_ARG, "M > 2 needs the Q8_1 workspace");
+    // Everything a kernel of this call may refuse is checked before anything is queued: a rank that queued its
+    // flag wait and then returned an error would leave every peer spinning for a band that never comes.
+    if (K % 256 != 0) return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather needs K %% 256 == 0 (K = %lld)", (long long)K);
+    if (((uintptr_t)d_w & 15u) != 0) return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather needs 16-byte aligned weights");
     if (((uintptr_t)d_x & 15u) != 0 || (d_ws && ((uintptr_t)d_ws & 15u) != 0))
         return set_error(JQ_ERR_ALIGN, "activations and workspace must be 16-byte aligned");
     GatherArgs ga;
@@ -586,6 +625,9 @@ int jq_device_fault(int clear, int *fault_out) {
         JQ_CUDA_TRY(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
     }
     if (fault_out) *fault_out = v;
+    if (v != 0)
+        return set_error(JQ_ERR_TIMEOUT, "a kernel gave up on a bounded wait (%s): its results are not valid",
+                         v == 2 ? "bands of an all-gather did not arrive" : "a bulk copy or pipeline stage did not complete");
     return JQ_OK;
 }
 
@@ -785,6 +827,7 @@ const void *jq_weights_device_ptr(const jq_weights *w) { return w ? w->d_w : nul
 int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace, float *y, int64_t M, int s_mode) {
     if (!w) return set_error(JQ_ERR_INVALID_ARG, "null weights handle");
     if (M < 0) return set_error(JQ_ERR_INVALID_ARG, "negative M");
+    if (int rc = check_s_mode(s_mode)) return rc;
     if (M == 0) return JQ_OK;
     if (!x || !y) return set_error(JQ_ERR_INVALID_ARG, "null pointer");
     if (M > w->m_cap) {  // staging buffers grow, never shrink

@@ -45,7 +45,15 @@ struct DeviceCaps {
 };
 int device_caps(DeviceCaps *out);  // for the current device
 
+// Raises a kernel's dynamic shared-memory limit to at least `bytes` on the current device.  The attribute
+// belongs to the function and the device, not to a host thread, so the record of what has been set is
+// process-wide (mutex-protected) and a limit is only ever raised.  `max_carveout` also asks for the largest
+// shared-memory carve-out (kernels that want two CTAs of ~110 KB per SM).
+int ensure_dynamic_smem(const void *kernel, int bytes, bool max_carveout = false);
+
 int option_value(int option);       // process-wide settings of jq_set_option()
+// Polls after which a bounded device-side wait gives up (JQ_OPT_WAIT_POLL_LIMIT; 2^22 by default).
+uint32_t wait_poll_limit();
 // Tracing aid (jq_trace_enable): device address where the next traced launch may write its
 // per-CTA timestamps, or nullptr when tracing is off or the buffer is full.
 void *next_trace_slot();

@@ -509,13 +509,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     if (int rc = order == JQ_ORDER_KSUPER_COL ? encode_byte_map(&x_map, d_xq, Q8_BYTES, (uint64_t)p.n_super * (uint64_t)M, Q8_BYTES)
                                               : encode_byte_map(&x_map, d_xq, x_row, (uint64_t)M, x_row))
         return rc;
-    static thread_local int attr_done_dev = -1;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (attr_done_dev != dev) {
-        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HF_SMEM_BYTES));
-        attr_done_dev = dev;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_f16_kernel), HF_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy), HF_THREADS, HF_SMEM_BYTES, st>>>(p, w_map, x_map);
     JQ_CUDA_TRY(cudaGetLastError());

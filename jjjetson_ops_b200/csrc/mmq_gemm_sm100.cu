@@ -336,15 +336,7 @@ int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
     using Tile = GemmTile<RT, CT>;
     const int64_t gx = (p.N + Tile::BN - 1) / Tile::BN, gy = (p.M + Tile::BM - 1) / Tile::BM;
     if (gy > 65535) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
-    static thread_local int attr_done_dev = -1;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (attr_done_dev != dev) {
-        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_mma_kernel<RT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile::SMEM));
-        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_mma_kernel<RT, CT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
-        attr_done_dev = dev;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_mma_kernel<RT, CT>), Tile::SMEM, true)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     gemm_q4_0_q8_1_mma_kernel<RT, CT><<<dim3((unsigned)gx, (unsigned)gy), GM_THREADS, Tile::SMEM, st>>>(p);
     JQ_CUDA_TRY(cudaGetLastError());

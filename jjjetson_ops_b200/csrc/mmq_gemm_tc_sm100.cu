@@ -487,13 +487,7 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
-    static thread_local int attr_done_dev = -1;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (attr_done_dev != dev) {
-        JQ_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_1_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
-        attr_done_dev = dev;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_tc_kernel), TC_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     gemm_q4_0_q8_1_tc_kernel<<<dim3((unsigned)gx, (unsigned)gy), TC_THREADS, TC_SMEM_BYTES, st>>>(p);
     JQ_CUDA_TRY(cudaGetLastError());

@@ -59,10 +59,15 @@ struct GemvParams {
     int rows_per_stage;
     int prefetch_early;    // the weight stream may start before the preceding kernel in the stream has finished
     int early_stages;      // stages the producer may request before the activations are staged
+    uint32_t x_copy_bytes; // > 0: the producer brings the activations in by bulk copy (fp32 to quantize, or ready
+                           // blocks straight to their place), queued ahead of the rest of the weight stream
+    uint32_t xraw_bytes;   // shared bytes reserved for fp32 activations copied that way
     GatherArgs gather;     // all-gather epilogue (world == 0: plain store to y)
     uint32_t y_bytes;      // shared bytes of the band staging buffer [M][y_rows] (gather only)
     uint32_t y_rows;
     unsigned long long *trace;  // 8 timestamps per CTA of this launch (tracing aid), or nullptr
+    uint32_t poll_limit;        // polls after which a bounded wait gives up
+    uint32_t rows_q, rows_r;    // N = rows_q * grid + rows_r (see cta_row_range)
 };
 
 // matrix that owns row r of the concatenation (n_mats is tiny: a linear scan)
@@ -87,14 +92,26 @@ __device__ __forceinline__ void trace_stamp(const GemvParams &p, int slot) {
     if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
 }
 
+#ifdef JQ_TRACE_FINE
+__device__ __forceinline__ void trace_fine(const GemvParams &p, int slot) {
+    if (p.trace != nullptr) p.trace[(size_t)(blockIdx.x + 256) * 8 + slot] = global_ns();
+}
+#else
+__device__ __forceinline__ void trace_fine(const GemvParams &, int) {}
+#endif
+
 // Programmatic dependent launch: let the next kernel in the stream be scheduled early, and wait
 // for the previous one (and its memory operations) before touching anything it may have written.
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-__device__ __forceinline__ void cta_row_range(int64_t N, int64_t *begin, int64_t *end) {
-    *begin = (int64_t)blockIdx.x * N / gridDim.x;
-    *end = (int64_t)(blockIdx.x + 1) * N / gridDim.x;
+// Rows of this CTA: N = q * grid + r, the first r CTAs own q + 1 rows.  q and r come from the host: a 64-bit
+// division costs a thread several hundred cycles, and this sits between the predecessor's end and the first
+// multiply.
+__device__ __forceinline__ void cta_row_range(const GemvParams &p, int64_t *begin, int64_t *end) {
+    const uint32_t b = blockIdx.x;
+    *begin = (int64_t)b * p.rows_q + min(b, p.rows_r);
+    *end = *begin + p.rows_q + (b < p.rows_r ? 1 : 0);
 }
 
 // The rows of this CTA, stage by stage: one contiguous slab per CTA, full stages of R rows and one
@@ -108,8 +125,8 @@ struct RowWalk {
 __device__ __forceinline__ RowWalk cta_row_walk(const GemvParams &p, int R) {
     RowWalk w;
     int64_t b, e;
-    cta_row_range(p.N, &b, &e);
-    w.n_main = (int)((e - b) / R);
+    cta_row_range(p, &b, &e);
+    w.n_main = (int)((uint32_t)(e - b) / (uint32_t)R);
     w.base = b;
     w.step = R;
     w.tail_begin = b + (int64_t)w.n_main * R;
@@ -135,11 +152,12 @@ __device__ __forceinline__ uint32_t gather_share() {
 
 // Lanes 0..world-1 of one warp poll this rank's arrival counts until all of all-gather number `epoch`
 // has arrived from each sender (counts and the product wrap together modulo 2^32).
-__device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uint32_t epoch, int lane, int *fault) {
+__device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uint32_t epoch, int lane, int *fault,
+                                           uint32_t limit) {
     if (lane < world) {
         const uint32_t expected = epoch * GATHER_UNITS;
         bool seen = false;
-        for (uint32_t spin = 0; spin < (1u << 22) && !seen; ++spin) {
+        for (uint32_t spin = 0; spin < limit && !seen; ++spin) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
             seen = (int32_t)(v - expected) >= 0;
@@ -149,10 +167,11 @@ __device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uin
     __syncwarp();
 }
 
-__global__ void allgather_wait_kernel(const uint32_t *flags, int world, const uint32_t *epoch_ptr, int *fault) {
+__global__ void allgather_wait_kernel(const uint32_t *flags, int world, const uint32_t *epoch_ptr, int *fault,
+                                      uint32_t limit) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(epoch_ptr);
-    if (epoch != 0) wait_flags(flags, world, epoch, (int)threadIdx.x, fault);
+    if (epoch != 0) wait_flags(flags, world, epoch, (int)threadIdx.x, fault, limit);
 }
 
 // Producer: walks the CTA's rows stage by stage.  With one copy per stage a single thread calls it;
@@ -162,21 +181,66 @@ __global__ void allgather_wait_kernel(const uint32_t *flags, int world, const ui
 // When the stream starts ahead of the previous kernel's end (static weights), only `early_stages`
 // stages are requested up front: the activation loads that follow the wait would otherwise queue
 // behind the whole ring's worth of weight traffic on this SM's path to L2.
+// One thread waits until all of all-gather number `epoch` has arrived from every sender.
+__device__ __forceinline__ bool wait_flags_serial(const uint32_t *flags, int world, uint32_t epoch, int *fault, uint32_t limit) {
+    const uint32_t expected = epoch * GATHER_UNITS;
+    for (int q = 0; q < world; ++q) {
+        bool seen = false;
+        for (uint32_t spin = 0; spin < limit && !seen; ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + q) : "memory");
+            seen = (int32_t)(v - expected) >= 0;
+        }
+        if (!seen) {
+            if (fault != nullptr) atomicExch(fault, 2);
+            return false;
+        }
+    }
+    return true;
+}
+
+// The point in the producer's walk where the activations come in (one thread).  Old protocol: the consumer
+// warps load them and the producer only waits until those loads have landed.  With x_copy_bytes the producer
+// itself queues them as bulk copies, ahead of the rest of the weight stream, after it has waited for the
+// previous kernel (and, for an N-sharded layer that consumes a gathered output, for that output's bands).
+__device__ __forceinline__ bool producer_activations(const GemvParams &p, uint64_t *x_ready, uint64_t *x_full, uint8_t *xs,
+                                                     uint8_t *xraw) {
+    if (p.x_copy_bytes == 0) return !p.prefetch_early || mbar_wait_bounded(x_ready, 0u, p.fault, p.poll_limit);
+    if (p.prefetch_early) griddep_wait();
+    if (p.gather.world > 0 && p.gather.wait_previous) {
+        const uint32_t done = *reinterpret_cast<const volatile uint32_t *>(p.gather.epoch_ptr);
+        if (done != 0 && !wait_flags_serial(p.gather.flag_peer[p.gather.rank], p.gather.world, done, p.fault, p.poll_limit)) return false;
+    }
+    mbar_arrive_expect_tx(x_full, p.x_copy_bytes);
+    if (p.x_f32 != nullptr) {
+        bulk_g2s(xraw, p.x_f32, p.x_copy_bytes, x_full);
+    } else {
+        const uint32_t per_row = (uint32_t)p.n_super * Q8_BYTES;
+        for (int m = 0; m < p.M; ++m) bulk_g2s(xs + (size_t)m * p.x_pitch, p.xq + (size_t)m * per_row, per_row, x_full);
+    }
+    return true;
+}
+
 template <bool PER_ROW>
 __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty,
-                                              uint64_t *x_ready, uint8_t *ring, int lane) {
+                                              uint64_t *x_ready, uint8_t *ring, int lane, uint64_t *x_full = nullptr,
+                                              uint8_t *xs = nullptr, uint8_t *xraw = nullptr) {
     const int R = p.rows_per_stage;
     const RowWalk walk = cta_row_walk(p, R);
     const int n_chunks = walk.n_chunks;
+    int s = 0;
+    uint32_t round = 0;
+    bool x_done = false;
     for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % p.stages;
-        const uint32_t round = (uint32_t)(c / p.stages);
         int rows;
         const int64_t r0 = walk_stage(walk, c, R, &rows);
         int ok = 1;
         if (lane == 0) {
-            if (c == p.early_stages && !mbar_wait_bounded(x_ready, 0u, p.fault)) ok = 0;
-            if (ok && round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1u, p.fault)) ok = 0;
+            if (c == p.early_stages) {
+                ok = producer_activations(p, x_ready, x_full, xs, xraw) ? 1 : 0;
+                x_done = true;
+            }
+            if (ok && round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1u, p.fault, p.poll_limit)) ok = 0;
             if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)rows * p.row_bytes);
         }
         if (PER_ROW) {
@@ -211,7 +275,13 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
                 left -= take;
             }
         }
+        if (++s == p.stages) {
+            s = 0;
+            ++round;
+        }
     }
+    // fewer stages than may be requested early: the activations still have to be brought in
+    if (lane == 0 && !x_done && p.x_copy_bytes != 0) producer_activations(p, x_ready, x_full, xs, xraw);
 }
 
 // Prologue of the consumer warps: put the quantized activations into shared memory, laid out
@@ -242,6 +312,7 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // after %1" ::"r"(smem_u32(x_ready)), "f"(touch)
                          : "memory");
         }
+        if (threadIdx.x == 0) trace_fine(p, 0);  // warp 0: x loads landed
     }
     uint32_t qv[U], dsv[U];
 #pragma unroll
@@ -259,6 +330,66 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
                 reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = qv[u];
                 if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = dsv[u];
             }
+        }
+    }
+}
+
+// Two neighbouring 128-value blocks (256 consecutive floats in shared memory) quantized by one warp: lane l owns
+// the values 8l .. 8l+7, a 32-value group is four lanes.  Same results, bit for bit, as quantize_group_q8_1
+// (eight lanes of four values): the maximum and the integer sum do not depend on the order, and the sum of
+// the floats is formed in the reference's order - per four consecutive values left to right, then the
+// partners the reference's xor-4, xor-2 and xor-1 steps pair up (q8_1.cu:62-68).
+__device__ __forceinline__ void quantize_pair_q8_1(uint32_t x_addr, int lane, int s_mode, uint2 *q_out, uint32_t *ds_bits) {
+    const uint4 ua = lds_v4(x_addr + (uint32_t)lane * 32u), ub = lds_v4(x_addr + (uint32_t)lane * 32u + 16u);
+    const float v[8] = {__uint_as_float(ua.x), __uint_as_float(ua.y), __uint_as_float(ua.z), __uint_as_float(ua.w),
+                        __uint_as_float(ub.x), __uint_as_float(ub.y), __uint_as_float(ub.z), __uint_as_float(ub.w)};
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                       fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1, 32));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2, 32));
+    const float d_inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    int q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (int)roundf(v[i] * d_inv);
+    const __half dh = amax > 0.0f ? __float2half(1.0f / d_inv) : __ushort_as_half((unsigned short)0);
+    __half sh;
+    if (s_mode == JQ_S_SUM_X) {
+        float sa = v[0] + v[1] + v[2] + v[3], sb = v[4] + v[5] + v[6] + v[7];
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2, 32);  // the reference's lanes i and i ^ 4
+        sb += __shfl_xor_sync(0xFFFFFFFFu, sb, 2, 32);
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1, 32);  // i and i ^ 2
+        sb += __shfl_xor_sync(0xFFFFFFFFu, sb, 1, 32);
+        sh = __float2half(sa + sb);                      // i and i ^ 1
+    } else {
+        int isum = ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
+        isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1, 32);
+        isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2, 32);
+        sh = __float2half(__half2float(dh) * (float)isum);
+    }
+    *ds_bits = (uint32_t)__half_as_ushort(dh) | ((uint32_t)__half_as_ushort(sh) << 16);
+    q_out->x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    q_out->y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+}
+
+// Prologue of the consumer warps when the producer copied fp32 activations into shared memory: quantize them
+// into the block layout the kernels read, warp w taking the block pairs w, w + NW, ...
+template <int NW>
+__device__ __forceinline__ void quantize_copied_activations(const GemvParams &p, uint8_t *xs, const uint8_t *xraw, int warp, int lane) {
+    const int pairs = p.M * p.n_super / 2;  // n_super is even (K % 256 == 0): a pair never straddles two rows
+    const uint32_t xraw_addr = smem_u32(xraw);
+    for (int pr = warp; pr < pairs; pr += NW) {
+        uint2 qv;
+        uint32_t ds;
+        quantize_pair_q8_1(xraw_addr + (uint32_t)pr * (2u * SUPER * 4u), lane, p.s_mode, &qv, &ds);
+        const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
+        const int m = idx / p.n_super, ks = idx - m * p.n_super;
+        uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+        reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
+        if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+        if (p.xq_out != nullptr && blockIdx.x == 0) {
+            uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+            reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
+            if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
         }
     }
 }
@@ -293,6 +424,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
         __syncwarp();
         if (lane == 0) mbar_arrive(x_ready);
     }
+    if (threadIdx.x == 0) trace_fine(p, 1);  // warp 0: its blocks are in shared memory
     named_bar_sync(1, NW * 32);
 }
 
@@ -306,16 +438,63 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
 // ------------------------------------------------------------------------------------------------
 // dp4a variant: one warp per weight row, one lane per 128-value slice (four Q4_0 blocks = 72
 // bytes, read as nine conflict-free 8-byte shared loads), activations of that slice in registers.
+// A warp works on two rows at a time, one from each of two consecutive stages, so that the loads,
+// the dp4a chains and the reduction of one row fill the latencies of the other.
 // ------------------------------------------------------------------------------------------------
+
+// The four blocks of one lane's slice of one row: acc[m] += d4 * (sumi * d8 - 8 * s8) per block.
+template <int M_T>
+__device__ __forceinline__ void dp4a_slice(const uint32_t (&wv)[18], const int (&xq)[M_T][32], const float (&xd)[M_T][4],
+                                           const float (&xms)[M_T][4], float (&acc)[M_T]) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        // block b starts at byte 18 b of the 72: word 4.5 b
+        uint32_t q[4], dbits;
+        if ((b & 1) == 0) {
+            const int w0 = (b / 2) * 9;
+            dbits = wv[w0] & 0xFFFFu;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) q[t] = __funnelshift_r(wv[w0 + t], wv[w0 + t + 1], 16);
+        } else {
+            const int w0 = (b / 2) * 9 + 4;
+            dbits = wv[w0] >> 16;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) q[t] = wv[w0 + 1 + t];
+        }
+        const float d4 = half_bits_to_float(dbits);
+        // low nibbles as they are, high nibbles left in place (16 x their value, unsigned
+        // bytes): 16 * sumi = 16 * lo + hi16 exactly, and xd carries d8 / 16
+        int lo_acc[M_T], hi_acc[M_T];
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) lo_acc[m] = hi_acc[m] = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t lo = q[t] & MASK4, hi16 = q[t] & (MASK4 << 4);
+#pragma unroll
+            for (int m = 0; m < M_T; ++m) {
+                lo_acc[m] = dp4a_u8s8(lo, xq[m][8 * b + t], lo_acc[m]);
+                hi_acc[m] = dp4a_u8s8(hi16, xq[m][8 * b + t + 4], hi_acc[m]);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) {
+            const int s16 = lo_acc[m] * 16 + hi_acc[m];
+            acc[m] = fmaf(d4, fmaf((float)s16, xd[m][b], xms[m][b]), acc[m]);
+        }
+    }
+}
+
 template <int M_T, int NSB, int NW, int MINB>
 __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + GV_MAX_STAGES;
     uint64_t *x_ready = full + 24;
+    uint64_t *x_full = full + 25;
     float *ybuf = reinterpret_cast<float *>(smem + GV_BAR_BYTES);
     uint8_t *xs = smem + GV_BAR_BYTES + p.y_bytes;
-    uint8_t *ring = xs + p.x_bytes;
+    uint8_t *xraw = xs + p.x_bytes;
+    uint8_t *ring = xraw + p.xraw_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -324,6 +503,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
             mbar_init(&empty[s], NW);
         }
         mbar_init(x_ready, NW);
+        mbar_init(x_full, 1);
         fence_mbar_init();
     }
     __syncthreads();
@@ -334,25 +514,45 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         if (lane == 0) {
             if (!p.prefetch_early) griddep_wait();
             trace_stamp(p, 1);  // weight stream begins
-            gemv_producer<false>(p, full, empty, x_ready, ring, 0);
+            gemv_producer<false>(p, full, empty, x_ready, ring, 0, x_full, xs, xraw);
             trace_stamp(p, 2);  // last copy issued
         }
         return;
     }
+    // everything that does not depend on the previous kernel comes before the wait for it
+    int64_t r_begin, r_end;
+    cta_row_range(p, &r_begin, &r_end);
+    const int R = p.rows_per_stage;
+    const RowWalk walk = cta_row_walk(p, R);
+    const int n_chunks = walk.n_chunks;
+    const uint32_t ring_addr = smem_u32(ring);
+    const bool tracing = p.trace != nullptr && threadIdx.x == 0;
+
     griddep_wait();  // activations may come from, and outputs may be read by, the previous kernel
     uint32_t gather_epoch = 0;  // number of this all-gather (previous ones finished: *epoch_ptr)
     if (p.gather.world > 0) {
         const uint32_t done = *reinterpret_cast<const volatile uint32_t *>(p.gather.epoch_ptr);
         gather_epoch = done + 1;
-        if (p.gather.wait_previous && done != 0) {
+        if (p.x_copy_bytes == 0 && p.gather.wait_previous && done != 0) {
             // the activations are the output of the previous sharded layer: all its bands must be here
-            if (warp == 0) wait_flags(p.gather.flag_peer[p.gather.rank], p.gather.world, done, lane, p.fault);
+            // (when the producer copies the activations in, it has waited for the bands itself)
+            if (warp == 0) wait_flags(p.gather.flag_peer[p.gather.rank], p.gather.world, done, lane, p.fault, p.poll_limit);
             named_bar_sync(1, NW * 32);
         }
     }
     if (threadIdx.x == 0) trace_stamp(p, 3);  // predecessor finished
 
-    stage_activations<NW>(p, xs, x_ready, warp, lane);
+    if (p.x_copy_bytes != 0) {
+        if (!mbar_wait_bounded(x_full, 0u, p.fault, p.poll_limit)) return;
+        if (threadIdx.x == 0) trace_fine(p, 0);  // activations landed in shared memory
+        if (p.x_f32 != nullptr) {
+            quantize_copied_activations<NW>(p, xs, xraw, warp, lane);
+            if (threadIdx.x == 0) trace_fine(p, 1);  // warp 0: its blocks are quantized
+            named_bar_sync(1, NW * 32);
+        }
+    } else {
+        stage_activations<NW>(p, xs, x_ready, warp, lane);
+    }
     if (threadIdx.x == 0) trace_stamp(p, 4);  // activations staged
 
     // This lane's slices of X: slice i covers k in [128*(lane + 32 i), +128).
@@ -388,105 +588,98 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
             }
         }
     }
+    if (threadIdx.x == 0) trace_fine(p, 2 + (xq[0][0][0] == 0x7fffffff ? 1 : 0));  // activations in registers
 
-    int64_t r_begin, r_end;
-    cta_row_range(p.N, &r_begin, &r_end);
-    const int R = p.rows_per_stage;
-    const RowWalk walk = cta_row_walk(p, R);
-    const int n_chunks = walk.n_chunks;
-    const uint32_t ring_addr = smem_u32(ring);
-    const bool tracing = p.trace != nullptr && threadIdx.x == 0;
-
-    // Ring position, phase parity and row offset advance incrementally: with one row per warp and
-    // stage, anything computed per stage is paid per row.
+    // Two stages (A, B) are taken per step, and everything a step needs besides the rows themselves is kept to
+    // a few 32-bit operations: with one row per warp and stage, whatever is computed per stage is paid per row
+    // (halving the number of steps took the fused cfg2 step from 8.4 to 7.2 us).  Rows are counted relative to
+    // the CTA's first row.  When the whole slab has ring slots of its own (n_chunks <= stages) no slot is ever
+    // refilled and nothing is handed back to the producer.
+    const bool resident = n_chunks <= p.stages;
+    const bool single_mat = p.n_mats <= 1;
+    float *const y_cta = p.gather.world > 0 ? ybuf : (single_mat ? p.y + r_begin : nullptr);
+    const size_t y_pitch = p.gather.world > 0 ? (size_t)p.y_rows : (size_t)p.N;
+    const uint32_t row_off = (uint32_t)warp * p.row_bytes + (uint32_t)lane * 72u;
     int s = 0;
     uint32_t parity = 0;
-    uint32_t stage = ring_addr;
-    for (int c = 0; c < n_chunks; ++c) {
-        if (!mbar_wait_bounded(&full[s], parity, p.fault)) return;
+    for (int c = 0; c < n_chunks; c += 2) {
+        const bool two = c + 1 < n_chunks;
+        const int sA = s;
+        if (!mbar_wait_bounded(&full[sA], parity, p.fault, p.poll_limit)) return;
         if (tracing && c == 0) trace_stamp(p, 5);  // first stage landed
-        if (tracing && c == n_chunks - 1) trace_stamp(p, 6);  // last stage landed
-        int rows;
-        const int64_t r0 = walk_stage(walk, c, R, &rows);
-
-        for (int r = warp; r < rows; r += NW) {
-            const uint32_t rowp = stage + (uint32_t)r * p.row_bytes;
-            float acc[M_T];
-#pragma unroll
-            for (int m = 0; m < M_T; ++m) acc[m] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NSB; ++i) {
-                const int sb = lane + 32 * i;
-                if (sb < p.n_super) {
-                    uint32_t wv[18];
-#pragma unroll
-                    for (int j = 0; j < 9; ++j) {
-                        const uint2 v = lds_v2(rowp + (uint32_t)sb * 72u + 8u * j);
-                        wv[2 * j] = v.x;
-                        wv[2 * j + 1] = v.y;
-                    }
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        // block b starts at byte 18 b of the 72: word 4.5 b
-                        uint32_t q[4], dbits;
-                        if ((b & 1) == 0) {
-                            const int w0 = (b / 2) * 9;
-                            dbits = wv[w0] & 0xFFFFu;
-#pragma unroll
-                            for (int t = 0; t < 4; ++t) q[t] = __funnelshift_r(wv[w0 + t], wv[w0 + t + 1], 16);
-                        } else {
-                            const int w0 = (b / 2) * 9 + 4;
-                            dbits = wv[w0] >> 16;
-#pragma unroll
-                            for (int t = 0; t < 4; ++t) q[t] = wv[w0 + 1 + t];
-                        }
-                        const float d4 = half_bits_to_float(dbits);
-                        // low nibbles as they are, high nibbles left in place (16 x their value, unsigned
-                        // bytes): 16 * sumi = 16 * lo + hi16 exactly, and xd carries d8 / 16
-                        int lo_acc[M_T], hi_acc[M_T];
-#pragma unroll
-                        for (int m = 0; m < M_T; ++m) lo_acc[m] = hi_acc[m] = 0;
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const uint32_t lo = q[t] & MASK4, hi16 = q[t] & (MASK4 << 4);
-#pragma unroll
-                            for (int m = 0; m < M_T; ++m) {
-                                lo_acc[m] = dp4a_u8s8(lo, xq[i][m][8 * b + t], lo_acc[m]);
-                                hi_acc[m] = dp4a_u8s8(hi16, xq[i][m][8 * b + t + 4], hi_acc[m]);
-                            }
-                        }
-#pragma unroll
-                        for (int m = 0; m < M_T; ++m) {
-                            const int s16 = lo_acc[m] * 16 + hi_acc[m];
-                            acc[m] = fmaf(d4, fmaf((float)s16, xd[i][m][b], xms[i][m][b]), acc[m]);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < M_T; ++m) {
-                float v = acc[m];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
-                if (lane == 0 && m < p.M) {
-                    if (p.gather.world > 0) {
-                        ybuf[(size_t)m * p.y_rows + (size_t)(r0 + r - r_begin)] = v;
-                    } else {
-                        *y_slot(p, m, r0 + r) = v;
-                    }
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
-        stage += p.stage_bytes;
         if (++s == p.stages) {
             s = 0;
             parity ^= 1u;
-            stage = ring_addr;
         }
+        const int sB = s;
+        if (two) {
+            if (!mbar_wait_bounded(&full[sB], parity, p.fault, p.poll_limit)) return;
+            if (++s == p.stages) {
+                s = 0;
+                parity ^= 1u;
+            }
+        }
+        if (tracing && c + 2 >= n_chunks) trace_stamp(p, 6);  // last stage landed
+        const int rowsA = c < walk.n_main ? R : walk.tail_rows;
+        const int rowsB = !two ? 0 : (c + 1 < walk.n_main ? R : walk.tail_rows);
+        const uint32_t stageA = ring_addr + (uint32_t)sA * p.stage_bytes, stageB = ring_addr + (uint32_t)sB * p.stage_bytes;
+
+        for (int r = warp; r < rowsA || r < rowsB; r += NW) {
+            const bool hasA = r < rowsA, hasB = r < rowsB;  // warp-uniform; a missing row is computed on the other's bytes
+            const uint32_t in_stage = row_off + (uint32_t)(r - warp) * p.row_bytes;
+            const uint32_t rowA = (hasA ? stageA : stageB) + in_stage;
+            const uint32_t rowB = (hasB ? stageB : stageA) + in_stage;
+            float accA[M_T], accB[M_T];
+#pragma unroll
+            for (int m = 0; m < M_T; ++m) accA[m] = accB[m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NSB; ++i) {
+                if (lane + 32 * i < p.n_super) {  // lanes past the end of K hold no activations: their bytes are another row's
+                    uint32_t wA[18], wB[18];
+#pragma unroll
+                    for (int j = 0; j < 9; ++j) {
+                        const uint2 a = lds_v2(rowA + (uint32_t)i * (32u * 72u) + 8u * j);
+                        const uint2 b = lds_v2(rowB + (uint32_t)i * (32u * 72u) + 8u * j);
+                        wA[2 * j] = a.x;
+                        wA[2 * j + 1] = a.y;
+                        wB[2 * j] = b.x;
+                        wB[2 * j + 1] = b.y;
+                    }
+                    dp4a_slice<M_T>(wA, xq[i], xd[i], xms[i], accA);
+                    if (two) dp4a_slice<M_T>(wB, xq[i], xd[i], xms[i], accB);
+                }
+            }
+            // Both rows' lane sums reduced together: the first step leaves row A's halves in lanes 0-15 and row B's
+            // in lanes 16-31, the other four run inside the halves.  Per row this adds the same pairs in the same
+            // order as a plain xor-16, 8, 4, 2, 1 reduction.
+            const bool upper = lane >= 16;
+            const int rel = (upper ? c + 1 : c) * R + r;  // row relative to the CTA's first
+#pragma unroll
+            for (int m = 0; m < M_T; ++m) {
+                const float give = upper ? accA[m] : accB[m];
+                float v = (upper ? accB[m] : accA[m]) + __shfl_xor_sync(0xFFFFFFFFu, give, 16, 32);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
+                if ((lane & 15) == 0 && m < p.M && (upper ? hasB : hasA)) {
+                    if (y_cta != nullptr) {
+                        y_cta[(size_t)m * y_pitch + (size_t)rel] = v;
+                    } else {
+                        *y_slot(p, m, r_begin + rel) = v;
+                    }
+                }
+            }
+        }
+        if (!resident) {
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[sA]);
+                if (two) mbar_arrive(&empty[sB]);
+            }
+        }
+        if (threadIdx.x == 0 && c == 0) trace_fine(p, 4);  // warp 0: first stage pair computed
     }
     if (threadIdx.x == 0) trace_stamp(p, 7);  // warp 0 done
+    if (threadIdx.x == (NW - 1) * 32) trace_fine(p, 5);  // last consumer warp done
 
     if (p.gather.world > 0) {
         // ---- all-gather epilogue: this CTA's rows of the band go to every rank's buffer ----------
@@ -582,7 +775,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
         for (int c = 0; c < n_chunks; ++c) {
             const int slot = c % GV_RED_SLOTS;
             const uint32_t round = (uint32_t)(c / GV_RED_SLOTS);
-            if (!mbar_wait_bounded(&red_full[slot], round & 1u, p.fault)) return;
+            if (!mbar_wait_bounded(&red_full[slot], round & 1u, p.fault, p.poll_limit)) return;
             int rows;
             const int64_t r0 = walk_stage(walk, c, 16, &rows);
             const float *src = red + (size_t)slot * NW * 128;
@@ -643,7 +836,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % p.stages;
         const uint32_t round = (uint32_t)(c / p.stages);
-        if (!mbar_wait_bounded(&full[s], round & 1u, p.fault)) return;
+        if (!mbar_wait_bounded(&full[s], round & 1u, p.fault, p.poll_limit)) return;
         if (threadIdx.x == 0 && c == 0) trace_stamp(p, 5);  // first stage landed
         if (threadIdx.x == 0 && c == n_chunks - 1) trace_stamp(p, 6);  // last stage landed
         const uint32_t stage = ring_addr + (uint32_t)s * p.stage_bytes;
@@ -694,7 +887,7 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
         // hand the partial 16 x 8 tile to the reducer warp
         const int slot = c % GV_RED_SLOTS;
         const uint32_t rround = (uint32_t)(c / GV_RED_SLOTS);
-        if (rround > 0 && !mbar_wait_bounded(&red_empty[slot], (rround - 1) & 1u, p.fault)) return;
+        if (rround > 0 && !mbar_wait_bounded(&red_empty[slot], (rround - 1) & 1u, p.fault, p.poll_limit)) return;
         float *mine = red + ((size_t)slot * NW + warp) * 128;
         *reinterpret_cast<float2 *>(&mine[g * 8 + 2 * t]) = make_float2(acc[0], acc[1]);
         *reinterpret_cast<float2 *>(&mine[(g + 8) * 8 + 2 * t]) = make_float2(acc[2], acc[3]);
@@ -704,29 +897,10 @@ __global__ void __launch_bounds__((NW + 2) * 32, 1) gemv_mma_kernel(const GemvPa
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-// Raises a kernel's dynamic shared-memory limit once per (kernel, device).
+// Raises a kernel's dynamic shared-memory limit and asks for the largest shared-memory carve-out, so that two
+// CTAs of ~110 KB fit one SM.
 int ensure_smem_attr(void (*kernel)(const GemvParams), int bytes) {
-    struct Entry {
-        const void *fn;
-        int dev, bytes;
-    };
-    static thread_local Entry table[32] = {};
-    static thread_local int used = 0;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    for (int i = 0; i < used; ++i) {
-        if (table[i].fn == (const void *)kernel && table[i].dev == dev) {
-            if (table[i].bytes >= bytes) return JQ_OK;
-            JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-            table[i].bytes = bytes;
-            return JQ_OK;
-        }
-    }
-    JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    // ask for the largest shared-memory carve-out so that two CTAs of ~110 KB fit one SM
-    JQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    if (used < 32) table[used++] = Entry{(const void *)kernel, dev, bytes};
-    return JQ_OK;
+    return ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), bytes, true);
 }
 
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
@@ -775,17 +949,19 @@ int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     }
     for (;;) {
         p.stage_bytes = align_up((uint32_t)p.rows_per_stage * p.row_bytes, 128);
-        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes - p.y_bytes;
+        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes - p.y_bytes - p.xraw_bytes;
         p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
         if (p.stages >= 3 || p.rows_per_stage == 1) break;
         p.rows_per_stage = p.rows_per_stage > 2 ? p.rows_per_stage / 2 : 1;
     }
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
-    const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+    const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + (int)p.xraw_bytes + p.stages * (int)p.stage_bytes;
     auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
     const int grid = (int)min((int64_t)caps.sm_count * MINB, max((int64_t)1, want));
+    p.rows_q = (uint32_t)(p.N / grid);
+    p.rows_r = (uint32_t)(p.N % grid);
     return launch_pdl(kernel, grid, (NW + 1) * 32, smem, st, p);
 }
 
@@ -805,6 +981,8 @@ int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + 15) / 16;
     const int grid = (int)min((int64_t)caps.sm_count, max((int64_t)1, want));
+    p.rows_q = (uint32_t)(p.N / grid);
+    p.rows_r = (uint32_t)(p.N % grid);
     return launch_pdl(kernel, grid, (NW + 2) * 32, smem, st, p);
 }
 
@@ -834,6 +1012,8 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
     // stream at the wait instead, where it overlaps the quantization.
     if (d_x_f32 != nullptr) p.prefetch_early = 0;
     p.early_stages = p.prefetch_early ? 2 : (1 << 30);
+    p.poll_limit = wait_poll_limit();
+
     return JQ_OK;
 }
 
@@ -869,7 +1049,7 @@ int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, c
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_wait_kernel, d_flags, world, d_epoch, device_fault_ptr()));
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_wait_kernel, d_flags, world, d_epoch, device_fault_ptr(), wait_poll_limit()));
     return JQ_OK;
 }
 
@@ -886,6 +1066,22 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
     if (gather != nullptr) p.gather = *gather;
     if (int rc = apply_multi(p, multi, gather)) return rc;
+    // The activations come in by bulk copy, queued by the producer ahead of the rest of its weight stream: fp32
+    // values into a staging area the consumer warps quantize from, ready blocks straight to their place (when a
+    // column's blocks are contiguous).  The weight stream may then run ahead of the previous kernel's end by one
+    // or two stages only: what is in flight then delays the activations.
+    if (p.x_f32 != nullptr) {
+        p.x_copy_bytes = (uint32_t)(M * K * sizeof(float));
+        p.xraw_bytes = align_up(p.x_copy_bytes, 128);
+    } else if (order == JQ_ORDER_COL_KSUPER || M == 1) {
+        p.x_copy_bytes = (uint32_t)(M * p.n_super * Q8_BYTES);
+    }
+    if (p.x_copy_bytes != 0) {
+        // measured on cfg2 at M = 1 (cold weights): fp32 activations 7.2 us with one stage ahead, 7.3 with two, 7.4 with
+        // none; ready blocks 6.3 / 5.9 / 7.3 us
+        p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
+        p.early_stages = !p.prefetch_early ? 0 : (p.x_f32 != nullptr ? 1 : 2);
+    }
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {

@@ -191,14 +191,8 @@ int launch_rms_norm_q8_1(cudaStream_t st, float *d_input, float *d_residual, con
     const size_t smem = (size_t)H * sizeof(float);
     if (smem + 1024 > (size_t)caps.smem_optin)
         return set_error(JQ_ERR_TOO_LARGE, "rms_norm: a row of %lld floats does not fit in shared memory", (long long)H);
-    static thread_local int attr_dev = -1;
-    static thread_local size_t attr_bytes = 0;
-    int dev = 0;
-    JQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (smem > 48 * 1024 && (attr_dev != dev || attr_bytes < smem)) {
-        JQ_CUDA_TRY(cudaFuncSetAttribute(rms_norm_q8_1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_dev = dev;
-        attr_bytes = smem;
+    if (smem > 48 * 1024) {
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(rms_norm_q8_1_kernel), (int)smem)) return rc;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)T);

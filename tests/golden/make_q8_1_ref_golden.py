@@ -19,7 +19,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: %s /path/to/JJJetson_Ops" % sys.argv[0])
+    ref_root = sys.argv[1]
     sys.modules["q8_1_me"] = types.ModuleType("q8_1_me")  # only the GPU entry points live there
     spec = importlib.util.spec_from_file_location(
         "ref_test_q8_1", os.path.join(ref_root, "tests", "test_q8_1.py")

@@ -19,7 +19,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: %s /path/to/JJJetson_Ops" % sys.argv[0])
+    ref_root = sys.argv[1]
     sys.modules["rms_norm_fused_add_me"] = types.ModuleType("rms_norm_fused_add_me")  # the GPU entry point lives there
     sys.modules.setdefault("utils", types.ModuleType("utils"))
     spec = importlib.util.spec_from_file_location(

@@ -3,7 +3,9 @@
 On one GPU the kernel runs with world = 1 (its band staging, peer-store loop, completion counter
 and flag logic all execute, with itself as the only peer).  With two or more GPUs a two-rank run
 (one process per GPU, NCCL only for the rendezvous of the IPC handles) checks real peer stores.
-No test makes a rank wait for a peer that never arrives.
+One test lets a bounded wait run out on purpose: a wait for an all-gather that nobody performs, with the poll
+limit set to a few thousand, must give up, report through the fault word and leave the device usable (the
+kernel returns by itself; nothing hangs or faults).
 """
 import os
 import socket
@@ -64,6 +66,37 @@ def test_fused_allgather_refuses_other_shapes(native_lib, cuda_device):
         assert ei.value.status == c.ERR_UNSUPPORTED  # gather with NCCL instead
     finally:
         bands.close()
+
+
+def test_bounded_wait_gives_up_and_reports(native_lib, oracle, cuda_device):
+    """A wait whose bands never arrive: flag word zero, epoch 1, 4096 polls.  The kernel must return, the fault
+    word must read 2 (and 0 after it was cleared), and an ordinary launch afterwards must be right."""
+    import torch
+
+    c = native_lib
+    assert c.device_fault() == 0
+    flags = torch.zeros(64, dtype=torch.int32, device=cuda_device)
+    epoch = torch.ones(1, dtype=torch.int32, device=cuda_device)  # "one all-gather has been started"
+    c.set_option(c.OPT_WAIT_POLL_LIMIT, 4096)
+    try:
+        c.allgather_wait(cuda_device, flags.data_ptr(), 1, epoch)
+        torch.cuda.synchronize()
+        v = c.ctypes.c_int(0)
+        rc = c.lib().jq_device_fault(1, c.ctypes.byref(v))
+        assert rc == c.ERR_TIMEOUT and v.value == 2, (rc, v.value, c.last_error())
+    finally:
+        c.set_option(c.OPT_WAIT_POLL_LIMIT, 0)
+    assert c.device_fault() == 0  # cleared by the read above
+    # the context is intact: a normal multiply gives the right answer
+    K, N, M = 2048, 320, 1
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    wq = oracle.quantize_q4_0(w)
+    y = c.linear_q4_0(torch.from_numpy(wq).to(cuda_device), torch.from_numpy(x).to(cuda_device), N).cpu().numpy()
+    xq = oracle.quantize_q8_1(x, oracle.ORDER_COL_KSUPER, oracle.S_D_SUM_Q)
+    assert oracle.err_max_rel(y, oracle.mul_mat_ref(wq, xq, K, N, M)) <= 1e-5
+    assert c.device_fault() == 0
 
 
 def _free_port() -> int:

@@ -1,14 +1,11 @@
-"""The quantized model container on the GPU: upload, then the layer's fused views through the multiply.
-
-Not yet run on a GPU when it was written (the host-side planning is covered by test_model_q4_0_cpu.py), hence
-the non-strict expected-failure mark: it reports XPASS where the upload works and never turns the suite red.
-"""
+"""The quantized model container on the GPU: upload, then the layer's fused views through the multiply
+(the host-side planning is covered by test_model_q4_0_cpu.py)."""
 import ctypes
 
 import numpy as np
 import pytest
 
-pytestmark = [pytest.mark.gpu, pytest.mark.xfail(strict=False, reason="first GPU run of the model upload")]
+pytestmark = pytest.mark.gpu
 
 CONFIG = {"hidden_size": 256, "intermediate_size": 512, "num_layers": 2, "num_q_heads": 4, "num_kv_heads": 2, "head_dim": 64,
           "vocab_size": 96, "max_seq_len": 32, "freq_base": 10000.0, "rms_norm_epsilon": 1e-6, "tie_word_embeddings": 1}
