@@ -65,10 +65,10 @@ typedef enum jq_kernel {
     JQ_KERNEL_GEMV_DP4A = 2, /* M <= 2: bulk-copy ring, dp4a, warp per row */
     JQ_KERNEL_GEMV_MMA = 3,  /* M <= 8: bulk-copy ring, int8 mma per block, K split over warps */
     JQ_KERNEL_GEMM_MMA = 4,  /* M > 8: tiled int8 mma.sync GEMM with per-block rescale */
-    JQ_KERNEL_GEMM_TC = 5,   /* M > 8, K % 128 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
+    JQ_KERNEL_GEMM_TC = 5,   /* M > 8, K % 256 == 0: tcgen05.mma.kind::i8 GEMM, TMEM accumulators drained per block */
     JQ_KERNEL_GEMM_F16 = 6   /* M > 8, K % 256 == 0: operands dequantised to fp16, tcgen05.mma.kind::f16, fp32 accumulation.
-                                Rounds every scaled operand to fp16 (about 3e-4 of the largest output); never picked
-                                by JQ_KERNEL_AUTO */
+                                Rounds every scaled operand to fp16 (about 2e-4 of the largest output); what
+                                JQ_KERNEL_AUTO takes for 64 columns and more unless JQ_OPT_PREFILL_EXACT is set */
 } jq_kernel;
 
 /* Process-wide switches. */
@@ -79,12 +79,15 @@ typedef enum jq_option {
      * draining, before they wait for it; activations and outputs are always ordered normally.
      * 0 (default): the weight stream, too, waits for the previous kernel. */
     JQ_OPT_STATIC_WEIGHTS = 0,
-    /* 1: JQ_KERNEL_AUTO may take the fp16-operand tcgen05 GEMM (JQ_KERNEL_GEMM_F16) for batches of 64
-     * activation columns and more when its shape rules hold (K % 256 == 0, 16-byte aligned buffers): about
-     * 2.5x the integer GEMM's throughput, results within about 3e-4 of the largest output of the exact
-     * path instead of 1e-6, activations must fit fp16's range.  0 (default): every automatic choice is an
-     * exact-integer kernel. */
-    JQ_OPT_PREFILL_FP16_OPERANDS = 1,
+    /* What JQ_KERNEL_AUTO runs for prefill batches (64 activation columns and more).
+     * 0 (default): the fp16-operand tcgen05 GEMM (JQ_KERNEL_GEMM_F16) when its shape rules hold (K % 256 == 0,
+     * 16-byte aligned buffers), else an exact-integer kernel.  It is 2.5x as fast as the integer GEMMs; every
+     * scaled operand is rounded to fp16 once, so results differ from the reference formula by about 2e-4 of the
+     * largest output (inside the 1e-3 bound against dequantise-then-matmul that the path is held to), and the
+     * activations must fit fp16's range.
+     * 1: every automatic choice is an exact-integer kernel (int32 block sums as the reference forms them, fp32
+     * results within 1e-6 of the reference formula).  Decode batches (fewer than 64 columns) always are. */
+    JQ_OPT_PREFILL_EXACT = 1,
     /* Number of polls after which a bounded device-side wait (for a bulk copy, or for the bands of an
      * all-gather) gives up, sets the fault word read by jq_device_fault() and lets its kernel return.
      * It applies to the decode kernels' waits and to jq_allgather_wait_device.

@@ -115,7 +115,7 @@ def check(status: int) -> None:
 
 
 OPT_STATIC_WEIGHTS = 0
-OPT_PREFILL_FP16_OPERANDS = 1
+OPT_PREFILL_EXACT = 1
 OPT_WAIT_POLL_LIMIT = 2
 
 

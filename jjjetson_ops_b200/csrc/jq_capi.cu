@@ -161,7 +161,7 @@ int check_mul_mat_shape(int64_t K, int64_t N, int64_t M) {
     return JQ_OK;
 }
 
-// Smallest batch for which JQ_OPT_PREFILL_FP16_OPERANDS changes the automatic choice: half a 128-column tile.
+// Smallest batch the automatic choice gives to the fp16-operand GEMM (unless JQ_OPT_PREFILL_EXACT): half a 128-column tile.
 constexpr int64_t FP16_OPERANDS_MIN_COLUMNS = 64;
 
 int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N,
@@ -197,8 +197,8 @@ int dispatch_mul_mat(cudaStream_t st, const void *d_w, const void *d_xq, float *
         }
         if (rc != JQ_OK && rc != JQ_ERR_UNSUPPORTED) return rc;
     }
-    if (rc == JQ_ERR_UNSUPPORTED && M >= FP16_OPERANDS_MIN_COLUMNS && option_value(JQ_OPT_PREFILL_FP16_OPERANDS) != 0)
-        rc = launch_gemm_f16(st, d_w, d_xq, d_y, K, N, M, order);  // the caller opted in to its precision
+    if (rc == JQ_ERR_UNSUPPORTED && M >= FP16_OPERANDS_MIN_COLUMNS && option_value(JQ_OPT_PREFILL_EXACT) == 0)
+        rc = launch_gemm_f16(st, d_w, d_xq, d_y, K, N, M, order);  // refuses shapes outside its rules: the integer GEMM takes those
     if (rc == JQ_ERR_UNSUPPORTED && M > 8) rc = launch_gemm_mma(st, d_w, d_xq, d_y, K, N, M, order);
     if (rc == JQ_ERR_UNSUPPORTED) rc = launch_mmq_generic(st, d_w, d_xq, d_y, K, N, M, order);
     if (rc == JQ_OK) t_last_error.clear();
@@ -362,9 +362,11 @@ int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq,
 }
 
 // The quantizer runs in the multiply kernel's own prologue while the activations are at most this many
-// 128-value blocks: every CTA repeats it and it is bound by instruction issue (about 1 us per 32 blocks),
-// while a quantize launch of its own costs about 2.9 us in a dependent chain whatever the size.
-// (One activation row of K = 8192 is the exception that was measured: 26.2 us fused, 27.3 us as two launches.)
+// 128-value blocks: every CTA repeats it (about 0.8 us per 32 blocks), while a quantize launch of its own
+// costs about 2.8 us in a dependent chain whatever the size.  Measured on cfg2 (cold weights) with the limit at
+// 32 / 64 / 128 / 256 blocks: M = 2 10.4 us whatever the limit, M = 4 11.8 / 11.8 / 13.6 / 13.6 us, M = 8
+// 12.3 / 12.3 / 12.3 / 18.5 us, K = 11008 at M = 1 7.5 / 7.5 / 10.0 / 10.0 us.
+// (One activation row of K = 8192 is the exception: 23.7 us fused, 27 us as two launches.)
 constexpr int64_t FUSE_QUANTIZER_MAX_BLOCKS = 32;
 inline bool fuse_quantizer_pays(int64_t M, int64_t K) {
     const int64_t blocks = M * (K / SUPER);

@@ -260,6 +260,42 @@ __device__ __forceinline__ uint32_t quantize_group_q8_1(float4 xi, int s_mode, u
            ((uint32_t)(q3 & 0xFF) << 24);
 }
 
+// The same quantizer with eight values per lane: lane l of a warp owns the values 8l .. 8l+7 of 256 consecutive
+// ones (two neighbouring 128-value blocks), a 32-value group is four lanes.  Same results, bit for bit, as
+// quantize_group_q8_1: the maximum and the integer sum do not depend on the order, and the sum of the floats is
+// formed in the reference's order - per four consecutive values left to right, then the partners that the
+// reference's xor-4, xor-2 and xor-1 steps pair up (q8_1.cu:62-68).  Half the instructions per value of the
+// four-per-lane form (two shuffle rounds instead of three, scalar work shared by eight values).
+// Every lane of the warp must call it.  q_out: the lane's eight int8 values; ds: (d, s) of its group.
+__device__ __forceinline__ void quantize_8_per_lane_q8_1(const float (&v)[8], int s_mode, uint2 *q_out, uint32_t *ds_bits) {
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                       fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1, 32));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2, 32));
+    const float d_inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    int q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (int)roundf(v[i] * d_inv);
+    const __half dh = amax > 0.0f ? __float2half(1.0f / d_inv) : __ushort_as_half((unsigned short)0);
+    __half sh;
+    if (s_mode == JQ_S_SUM_X) {
+        float sa = v[0] + v[1] + v[2] + v[3], sb = v[4] + v[5] + v[6] + v[7];
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2, 32);  // the reference's lanes i and i ^ 4
+        sb += __shfl_xor_sync(0xFFFFFFFFu, sb, 2, 32);
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1, 32);  // i and i ^ 2
+        sb += __shfl_xor_sync(0xFFFFFFFFu, sb, 1, 32);
+        sh = __float2half(sa + sb);                      // i and i ^ 1
+    } else {
+        int isum = ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
+        isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1, 32);
+        isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2, 32);
+        sh = __float2half(__half2float(dh) * (float)isum);
+    }
+    *ds_bits = (uint32_t)__half_as_ushort(dh) | ((uint32_t)__half_as_ushort(sh) << 16);
+    q_out->x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    q_out->y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+}
+
 #endif  // __CUDACC__
 
 }  // namespace jq

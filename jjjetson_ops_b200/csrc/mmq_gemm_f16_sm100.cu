@@ -44,8 +44,6 @@
 // around in shared memory and store 128 contiguous bytes of an output row per instruction.
 // Every mbarrier wait is a bounded poll; a wait that runs out sets the device fault word, and every
 // warp still reaches the common exit where tensor memory is released.
-#include <cuda.h>
-
 #include "tc_common.cuh"
 
 namespace jq {
@@ -114,15 +112,6 @@ __device__ __forceinline__ void hf_stamp(const HfParams &p, int who, int c, int 
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && c < 64) {
         p.trace[((who * 64 + c) * 8) + slot] = (unsigned long long)clock64();
     }
-}
-
-// One tiled tensor copy global -> shared: the box of `map` at byte column x, row y; completion counted in bytes on
-// an mbarrier.  x must be a multiple of 16.  Rows past the end of the tensor arrive as zeros (and are counted).
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
 }
 
 // registers -> 32 lanes x 32 consecutive 32-bit columns of tensor memory (completion: tcgen05.wait::st)
@@ -440,44 +429,6 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 
 }  // namespace
 
-namespace {
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The driver's tensor-map encoder, looked up through the runtime so that the library does not link against libcuda.
-EncodeTiledFn tensor_map_encoder() {
-    static const EncodeTiledFn fn = [] {
-        void *f = nullptr;
-        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &found) != cudaSuccess ||
-            found != cudaDriverEntryPointSuccess) {
-            (void)cudaGetLastError();
-            f = nullptr;
-        }
-        return reinterpret_cast<EncodeTiledFn>(f);
-    }();
-    return fn;
-}
-
-// Byte tensor [rows][row_len] with rows `pitch` bytes apart, copied in boxes of 128 rows x 144 bytes.
-int encode_byte_map(CUtensorMap *map, const void *base, uint64_t row_len, uint64_t rows, uint64_t pitch) {
-    const EncodeTiledFn encode = tensor_map_encoder();
-    if (encode == nullptr) return set_error(JQ_ERR_UNSUPPORTED, "the driver does not export cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {row_len, rows};
-    const cuuint64_t strides[1] = {pitch};
-    const cuuint32_t box[2] = {(cuuint32_t)Q8_BYTES, 128u};
-    const cuuint32_t elem_strides[2] = {1u, 1u};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(JQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    return JQ_OK;
-}
-
-}  // namespace
-
 int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
                     int order) {
     // a weight row's pitch, K / 32 * 18 bytes, must be a multiple of 16 for the tensor copies
@@ -504,10 +455,11 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
     CUtensorMap w_map, x_map;
-    if (int rc = encode_byte_map(&w_map, d_w, p.row_bytes, (uint64_t)N, p.row_bytes)) return rc;
+    if (int rc = encode_byte_map(&w_map, d_w, p.row_bytes, (uint64_t)N, p.row_bytes, Q8_BYTES, 128)) return rc;
     const uint64_t x_row = (uint64_t)p.n_super * Q8_BYTES;
-    if (int rc = order == JQ_ORDER_KSUPER_COL ? encode_byte_map(&x_map, d_xq, Q8_BYTES, (uint64_t)p.n_super * (uint64_t)M, Q8_BYTES)
-                                              : encode_byte_map(&x_map, d_xq, x_row, (uint64_t)M, x_row))
+    if (int rc = order == JQ_ORDER_KSUPER_COL
+                     ? encode_byte_map(&x_map, d_xq, Q8_BYTES, (uint64_t)p.n_super * (uint64_t)M, Q8_BYTES, Q8_BYTES, 128)
+                     : encode_byte_map(&x_map, d_xq, x_row, (uint64_t)M, x_row, Q8_BYTES, 128))
         return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_f16_kernel), HF_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's

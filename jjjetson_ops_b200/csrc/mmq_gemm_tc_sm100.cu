@@ -8,18 +8,22 @@
 //   warps 0-7   drain warps.  TMEM lane = activation column m, TMEM column = weight row n.  Warp w
 //               owns lanes 32*(w%4).. and columns 64*(w/4)..; per block it reads its 32 x 64 s32
 //               sums with tcgen05.ld, rescales them and adds them to 64 fp32 registers per thread.
-//   warp 8      allocates TMEM and issues the MMAs: per 32-wide block a bias MMA and one
+//   warp 8      allocates TMEM; one thread issues the MMAs: per 32-wide block a bias MMA and one
 //               128 x 128 x 32 tcgen05.mma.kind::i8 (A = activations, s8; B = weight nibbles, u8)
 //               into one of three accumulator buffers, then tcgen05.commit onto an mbarrier.
-//   warps 9-11  producers.  K advances in stages of 128 values (one Q8_1 super-block, four Q4_0
-//               blocks).  The 128 weight rows and 128 activation columns of a stage are 256 tasks
-//               dealt to the 96 producer threads.  A weight task loads 72 bytes one stage ahead
-//               into registers, splits the nibbles and writes four int8 tiles in the tensor core's
-//               canonical K-major layout (8-row x 16-byte core matrices, 128 bytes apart along K,
-//               256 bytes apart along rows) plus the fp32 table of d4.  An activation task sends
-//               the int8 values from global memory straight to their tile positions (cp.async) and
-//               writes the (d8, bias correction) table.  A stage is published one iteration after
-//               it was issued, so the copies have a whole iteration to land.
+//   warp 9      one thread issues the tiled tensor copies (cp.async.bulk.tensor, no multicast).  K advances in
+//               stages of 128 values (one Q8_1 super-block, four Q4_0 blocks).  The activations' int8 values
+//               go straight into the tensor core's operand layout: eight copies of 16 bytes x 128 columns per
+//               stage, each landing as one 2 KB slab of core matrices (8 columns x 16 bytes), so no thread ever
+//               touches them; one more copy brings the 128 block headers (scales).  The weights come as raw
+//               bytes, 144 bytes of each of the 128 rows per two stages.
+//   warps 10-13 conversion.  Thread r splits the nibbles of weight row r (72 raw bytes per stage) into four
+//               int8 tiles in the canonical K-major layout (8-row x 16-byte core matrices) and writes the fp32
+//               table of d4 and the row's fp16 zero-point operand.
+//   warps 14-15 from the headers of two activation columns per thread: the (d8, bias correction) table and
+//               the columns' zero-point operands.
+//               (Earlier the producers loaded "their" row per thread from global memory: a warp-wide load of
+//               32 rows touches 32 cache lines, and those loads cost more than conversion and MMAs together.)
 //
 // Exact per-block scaling without integer or conversion work in the drain.  Every accumulator is
 // first set to 2^17 by an MMA of a constant tile with itself (32 * 64 * 64), more than the largest
@@ -51,27 +55,43 @@ constexpr int TC_BM = 128;   // activation columns per CTA (MMA M, TMEM lanes)
 constexpr int TC_BN = 128;   // weight rows per CTA (MMA N, TMEM columns)
 constexpr int TC_KB = 4;     // 32-wide blocks per pipeline stage (one Q8_1 super-block of K)
 constexpr int TC_KB_LOG2 = 2;
-constexpr int TC_STAGES = 4;
-constexpr int TC_A_OFF = 0;                        // activations: TC_KB tiles
+constexpr int TC_STAGES = 3;
+constexpr int TC_A_OFF = 0;                        // activations: 8 slabs [128 columns][16 bytes], slab c = values 16c..16c+15
+constexpr int TC_A_SLAB = 128 * 16;                //   (block j = slabs 2j, 2j+1: K-chunks 2048 bytes apart, 8-column groups 128)
 constexpr int TC_B_OFF = TC_KB * TC_TILE;          // weights:     TC_KB tiles
 constexpr int TC_ZA_OFF = 2 * TC_KB * TC_TILE;     // fp16 s8[128 columns][16] (4 blocks + 12 zeros), canonical layout
 constexpr int TC_ZB_OFF = TC_ZA_OFF + TC_TILE;     // fp16 -8*d4[128 rows][16], canonical layout
 constexpr int TC_D4_OFF = TC_ZB_OFF + TC_TILE;     // float (d4 * 2^49)[TC_KB][128]
 constexpr int TC_XS_OFF = TC_D4_OFF + TC_KB * 128 * 4;   // float2 (d8 * 2^100, -2^17 * d8 * 2^-49)[TC_KB][128]
-constexpr int TC_STAGE_BYTES = TC_XS_OFF + TC_KB * 128 * 8;
-constexpr int TC_BIAS_OFF = TC_STAGES * TC_STAGE_BYTES;   // one operand tile with every byte = TC_BIAS_BYTE
+constexpr int TC_XH_OFF = TC_XS_OFF + TC_KB * 128 * 8;   // raw block headers [128 columns][16 bytes] as copied
+constexpr int TC_STAGE_BYTES = TC_XH_OFF + 128 * 16;
+constexpr int TC_X_TX_BYTES = 8 * TC_A_SLAB + 128 * 16;  // bytes the copies of one stage's activations deliver
+constexpr int TC_RAWW_SLOTS = 2;                          // raw weights: 128 rows x 144 bytes = two stages per slot
+constexpr int TC_RAWW_SLOT_BYTES = 128 * Q8_BYTES;
+constexpr int TC_W_CHUNK = TC_KB * Q4_BYTES;              // 72 bytes of a weight row per stage
+static_assert(2 * TC_W_CHUNK == Q8_BYTES, "a weight slot is two stages of 72 bytes per row");
+constexpr int TC_RAWW_OFF = TC_STAGES * TC_STAGE_BYTES;
+constexpr int TC_BIAS_OFF = TC_RAWW_OFF + TC_RAWW_SLOTS * TC_RAWW_SLOT_BYTES;   // one operand tile with every byte = TC_BIAS_BYTE
 constexpr int TC_BAR_OFF = TC_BIAS_OFF + TC_TILE;
-constexpr int TC_SMEM_BYTES = TC_BAR_OFF + 128;
+constexpr int TC_SMEM_BYTES = TC_BAR_OFF + 256;
+static_assert(TC_STAGE_BYTES % 128 == 0 && TC_RAWW_OFF % 128 == 0, "tensor copies land on 128-byte boundaries");
+static_assert(TC_SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
 constexpr int TC_DRAIN_WARPS = 8;
 constexpr int TC_MMA_WARP = 8;
-constexpr int TC_PROD_WARP0 = 9;
-constexpr int TC_PROD_THREADS = 96;
-constexpr int TC_THREADS = 12 * 32;
-// Registers per thread after setmaxnreg.  The CTA starts with 168 x 384 = 64512 registers and the two settings
-// must not ask for more than that in total, or the second setmaxnreg.inc never returns.
+constexpr int TC_COPY_WARP = 9;
+constexpr int TC_CONV_WARP0 = 10;
+constexpr int TC_CONV_WARPS = 4;                   // weight rows: one per thread
+constexpr int TC_HDR_WARP0 = TC_CONV_WARP0 + TC_CONV_WARPS;
+constexpr int TC_HDR_WARPS = 2;                    // activation headers: two columns per thread
+constexpr int TC_THREADS = (TC_HDR_WARP0 + TC_HDR_WARPS) * 32;   // 512: four warps on each of the SM's four schedulers
+// Registers per thread after setmaxnreg.  A CTA of 512 threads starts with 128 registers per thread, and the
+// register file is one quarter per scheduler: warp w lives on scheduler w % 4, so each scheduler holds two drain
+// warps and two of the others and has 4 x 128 registers per lane to hand out.  The two settings must stay within
+// that, or the drain warps' setmaxnreg.inc never returns.
 constexpr int TC_DRAIN_REGS = 208;
-constexpr int TC_PROD_REGS = 88;
-static_assert(8 * TC_DRAIN_REGS + 4 * TC_PROD_REGS <= 12 * 168, "setmaxnreg budget exceeds the CTA's allocation");
+constexpr int TC_OTHER_REGS = 48;
+static_assert(TC_DRAIN_WARPS == 8 && TC_THREADS == 512 && 2 * TC_DRAIN_REGS + 2 * TC_OTHER_REGS <= 4 * 128,
+              "setmaxnreg budget exceeds a scheduler's share of the CTA's allocation");
 constexpr int TC_ACC_BUFS = 3;                     // integer accumulator buffers of 128 columns
 constexpr uint32_t TC_ZP_COL = TC_ACC_BUFS * TC_BN;  // fp32 zero-point accumulator, 128 columns
 constexpr uint32_t TC_TMEM_COLS = 512;
@@ -98,7 +118,7 @@ struct TcParams {
 
 // Tracing aid.  Rows 0-127: per block, when each drain warp saw the accumulator complete; rows
 // 128-255: when it had added the previous block; rows 256-383: when it handed the buffer back;
-// rows 384-511: column 0 = when the MMA of the block was issued, columns 1-3 = when each producer
+// rows 384-511: column 0 = when the MMA of the block was issued, columns 1-4 = when each conversion
 // warp published the stage that starts with the block.
 __device__ __forceinline__ void tc_stamp(const TcParams &p, int g, int kind, int slot) {
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && g < 128) {
@@ -113,10 +133,6 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
         : "l"(reinterpret_cast<const uint64_t &>(a)), "l"(reinterpret_cast<const uint64_t &>(b)),
           "l"(reinterpret_cast<const uint64_t &>(c)));
     return d;
-}
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -163,16 +179,9 @@ __device__ __forceinline__ void tc_unpack_weight_row(uint32_t st, int r, const u
     sts_v4(st + TC_ZB_OFF + tile_off(r, 0), make_uint4(zw[0], zw[1], 0u, 0u));
 }
 
-// One activation task of a stage: the column's 128 int8 values go from global memory straight
-// into the four tiles; the scales (already in registers) become the drain's table and the fp16
-// zero-point operand.
-__device__ __forceinline__ void tc_stage_activation_col(uint32_t st, int r, const uint8_t *xb, uint4 ds) {
-#pragma unroll
-    for (int j = 0; j < TC_KB; ++j) {
-        const uint32_t tile = st + TC_A_OFF + j * TC_TILE;
-        cp_async16(tile + tile_off(r, 0), xb + Q8_QS_OFFSET + 32 * j);
-        cp_async16(tile + tile_off(r, 1), xb + Q8_QS_OFFSET + 32 * j + 16);
-    }
+// One activation column of a stage: its block header (four (d, s) pairs, already in registers) becomes the
+// drain's table and the fp16 zero-point operand.  The int8 values themselves were placed by the copy engine.
+__device__ __forceinline__ void tc_stage_activation_header(uint32_t st, int r, uint4 ds) {
     const uint32_t dsw[4] = {ds.x, ds.y, ds.z, ds.w};
 #pragma unroll
     for (int j = 0; j < TC_KB; ++j) {
@@ -185,16 +194,20 @@ __device__ __forceinline__ void tc_stage_activation_col(uint32_t st, int r, cons
     sts_v4(st + TC_ZA_OFF + tile_off(r, 0), make_uint4(s01, s23, 0u, 0u));
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_q4_0_q8_1_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_BAR_OFF);
-    uint64_t *stage_full = bars;                          // [TC_STAGES] producers -> MMA warp and drain warps
-    uint64_t *stage_empty = bars + TC_STAGES;             // [TC_STAGES] drain warps -> producers
+    uint64_t *stage_full = bars;                          // [TC_STAGES] conversion warps -> MMA warp and drain warps
+    uint64_t *stage_empty = bars + TC_STAGES;             // [TC_STAGES] drain warps -> copy warp (and, through it, conversion)
     uint64_t *acc_full = bars + 2 * TC_STAGES;            // [TC_ACC_BUFS] MMA completion -> drain warps
     uint64_t *acc_empty = acc_full + TC_ACC_BUFS;         // [TC_ACC_BUFS] drain warps (buffer read out) -> MMA warp
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + TC_ACC_BUFS);
-    static_assert((2 * TC_STAGES + 2 * TC_ACC_BUFS) * 8 + 4 <= 128, "barrier block too small");
+    uint64_t *x_full = acc_empty + TC_ACC_BUFS;           // [TC_STAGES] copy engine (activation slabs + headers) -> conversion, MMA
+    uint64_t *raww_full = x_full + TC_STAGES;             // [TC_RAWW_SLOTS] copy engine -> conversion warps
+    uint64_t *raww_empty = raww_full + TC_RAWW_SLOTS;     // [TC_RAWW_SLOTS] conversion warps -> copy warp
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raww_empty + TC_RAWW_SLOTS);
+    static_assert((3 * TC_STAGES + 2 * TC_ACC_BUFS + 2 * TC_RAWW_SLOTS) * 8 + 4 <= 256, "barrier block too small");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t n0 = (int64_t)blockIdx.x * TC_BN, m0 = (int64_t)blockIdx.y * TC_BM;
@@ -202,8 +215,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const 
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&stage_full[s], TC_PROD_THREADS / 32);
+            mbar_init(&stage_full[s], TC_CONV_WARPS + TC_HDR_WARPS);
             mbar_init(&stage_empty[s], TC_DRAIN_WARPS);
+            mbar_init(&x_full[s], 1);
+        }
+        for (int i = 0; i < TC_RAWW_SLOTS; ++i) {
+            mbar_init(&raww_full[i], 1);
+            mbar_init(&raww_empty[i], TC_CONV_WARPS);
         }
         for (int b = 0; b < TC_ACC_BUFS; ++b) {
             mbar_init(&acc_full[b], 1);
@@ -353,7 +371,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const 
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         }
     } else {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_PROD_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_OTHER_REGS));
         if (warp == TC_MMA_WARP) {
             // =============================== MMA issuer =====================================
             if (lane == 0) {
@@ -365,7 +383,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const 
                 bool alive = true;
                 for (int c = 0; c < n_chunks && alive; ++c) {
                     const int s = c % TC_STAGES;
-                    if (!mbar_wait_bounded(&stage_full[s], (uint32_t)(c / TC_STAGES) & 1u, p.fault)) break;
+                    const uint32_t par = (uint32_t)(c / TC_STAGES) & 1u;
+                    // the conversion warps' tiles and tables, and the activation slabs the copy engine placed
+                    if (!mbar_wait_bounded(&stage_full[s], par, p.fault) || !mbar_wait_bounded(&x_full[s], par, p.fault)) break;
                     const uint32_t st = sbase + s * TC_STAGE_BYTES;
                     tc_fence_after();
                     asm volatile(
@@ -384,72 +404,70 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const 
                         tc_stamp(p, g, 3, 0);
                         // accumulator = bias (overwriting), then += activations x nibbles
                         tc_mma_i8(tmem + buf * TC_BN, dbias, dbias, idesc, 0u);
-                        tc_mma_i8(tmem + buf * TC_BN, tc_desc(st + TC_A_OFF + kb * TC_TILE), tc_desc(st + TC_B_OFF + kb * TC_TILE), idesc, 1u);
+                        tc_mma_i8(tmem + buf * TC_BN, tc_desc_strided(st + TC_A_OFF + kb * 2 * TC_A_SLAB, TC_A_SLAB, 128u),
+                                  tc_desc(st + TC_B_OFF + kb * TC_TILE), idesc, 1u);
                         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                          smem_u32(&acc_full[buf]))
                                      : "memory");
                     }
                 }
             }
-        } else {
-            // =============================== producers ======================================
-            // Tasks of a stage: t < 128 is weight row t, t >= 128 is activation column t - 128;
-            // this thread takes t = pt0, pt0 + 96 and pt0 + 192 (< 256).  Every branch is warp-uniform.
-            const int pt0 = tid - TC_PROD_WARP0 * 32;  // 0..95
-            const bool has_w1 = pt0 < 32;               // second weight row pt0 + 96
-            const bool has_xa = pt0 >= 32;              // activation column pt0 - 32
-            const bool has_xb = pt0 < 64;               // activation column pt0 + 64
-            const int col_a = pt0 - 32, col_b = pt0 + 64;
-            // rows / columns past the end are clamped: their results are never stored
-            const uint8_t *w0p = p.w + min(n0 + pt0, p.N - 1) * (int64_t)p.row_bytes;
-            const uint8_t *w1p = p.w + min(n0 + pt0 + 96, p.N - 1) * (int64_t)p.row_bytes;
-            const int64_t m_a = min(m0 + col_a, p.M - 1), m_b = min(m0 + col_b, p.M - 1);
-            uint2 wv0[9], wv1[9];
-            uint4 ds_a = make_uint4(0u, 0u, 0u, 0u), ds_b = make_uint4(0u, 0u, 0u, 0u);
-            const uint8_t *xb_a = nullptr, *xb_b = nullptr;
-            auto load_chunk = [&](int c) {  // global -> registers, one stage ahead of its use
-#pragma unroll
-                for (int i = 0; i < 9; ++i) wv0[i] = __ldg(reinterpret_cast<const uint2 *>(w0p + (size_t)c * (TC_KB * Q4_BYTES)) + i);
-                if (has_w1) {
-#pragma unroll
-                    for (int i = 0; i < 9; ++i) wv1[i] = __ldg(reinterpret_cast<const uint2 *>(w1p + (size_t)c * (TC_KB * Q4_BYTES)) + i);
-                }
-                if (has_xa) {
-                    xb_a = p.xq + q8_block_index(c, m_a, p.n_super, p.M, p.order) * Q8_BYTES;
-                    ds_a = __ldg(reinterpret_cast<const uint4 *>(xb_a));
-                }
-                if (has_xb) {
-                    xb_b = p.xq + q8_block_index(c, m_b, p.n_super, p.M, p.order) * Q8_BYTES;
-                    ds_b = __ldg(reinterpret_cast<const uint4 *>(xb_b));
-                }
-            };
-            load_chunk(0);
-            bool dead = false;
-            for (int c = 0; c <= n_chunks; ++c) {  // one extra iteration publishes the last stage
-                if (c < n_chunks) {
+        } else if (warp == TC_COPY_WARP) {
+            // =============================== copy warp ======================================
+            // One thread keeps the rings filled.  Activations of stage c: slab i (the 16 values 16 i .. 16 i + 15 of the
+            // stage for all 128 columns) is one box of 16 bytes x 128 rows at byte 16 + 16 i of the columns' block;
+            // the headers are the box at byte 0.  Weights: 144 bytes of each of the 128 rows per two stages.
+            if (lane == 0) {
+                for (int c = 0; c < n_chunks; ++c) {
                     const int s = c % TC_STAGES;
-                    if (c >= TC_STAGES && !mbar_wait_bounded(&stage_empty[s], (uint32_t)(c / TC_STAGES - 1) & 1u, p.fault)) {
-                        dead = true;
-                        break;
+                    if ((c & 1) == 0) {
+                        const int pair = c >> 1, ws = pair % TC_RAWW_SLOTS;
+                        if (pair >= TC_RAWW_SLOTS && !mbar_wait_bounded(&raww_empty[ws], (uint32_t)(pair / TC_RAWW_SLOTS - 1) & 1u, p.fault)) break;
+                        mbar_arrive_expect_tx(&raww_full[ws], TC_RAWW_SLOT_BYTES);
+                        tma_load_2d(sbase + TC_RAWW_OFF + ws * TC_RAWW_SLOT_BYTES, &w_map, pair * Q8_BYTES, (int)n0, &raww_full[ws]);
                     }
+                    // the slot's previous tiles have been multiplied and its tables read
+                    if (c >= TC_STAGES && !mbar_wait_bounded(&stage_empty[s], (uint32_t)(c / TC_STAGES - 1) & 1u, p.fault)) break;
                     const uint32_t st = sbase + s * TC_STAGE_BYTES;
-                    if (has_xa) tc_stage_activation_col(st, col_a, xb_a, ds_a);
-                    if (has_xb) tc_stage_activation_col(st, col_b, xb_b, ds_b);
-                    tc_unpack_weight_row(st, pt0, wv0);
-                    if (has_w1) tc_unpack_weight_row(st, pt0 + 96, wv1);
-                    if (c + 1 < n_chunks) load_chunk(c + 1);
-                }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                if (c >= 1) {
-                    // stage c-1: its copies (all but the newest group) have landed, its stores are older still
-                    asm volatile("cp.async.wait_group 1;" ::: "memory");
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&stage_full[(c - 1) % TC_STAGES]);
-                    if (lane == 0 && ((c - 1) * TC_KB) < 128) tc_stamp(p, (c - 1) * TC_KB, 3, 1 + warp - TC_PROD_WARP0);
+                    mbar_arrive_expect_tx(&x_full[s], TC_X_TX_BYTES);
+                    // JQ_ORDER_KSUPER_COL: the tensor is [n_super * M blocks][144 bytes]; else [M columns][n_super * 144 bytes]
+                    const int bx = p.order == JQ_ORDER_KSUPER_COL ? 0 : c * Q8_BYTES;
+                    const int by = p.order == JQ_ORDER_KSUPER_COL ? (int)((int64_t)c * p.M + m0) : (int)m0;
+                    tma_load_2d(st + TC_XH_OFF, &x_map, bx, by, &x_full[s]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) tma_load_2d(st + TC_A_OFF + i * TC_A_SLAB, &x_map, bx + Q8_QS_OFFSET + 16 * i, by, &x_full[s]);
                 }
             }
-            if (dead) asm volatile("cp.async.wait_all;" ::: "memory");
+        } else {
+            // =============================== conversion warps ===============================
+            // Seeing a stage's activation copies complete also means its slot is free: the copy warp issued them only
+            // after the drain warps had handed the slot back.
+            const bool weights = warp < TC_HDR_WARP0;
+            const int r = weights ? tid - TC_CONV_WARP0 * 32 : tid - TC_HDR_WARP0 * 32;  // weight row 0..127 / column pair 0..63
+            for (int c = 0; c < n_chunks; ++c) {
+                const int s = c % TC_STAGES, ws = (c >> 1) % TC_RAWW_SLOTS;
+                bool ok = mbar_wait_bounded(&x_full[s], (uint32_t)(c / TC_STAGES) & 1u, p.fault);
+                if (weights) ok = ok && mbar_wait_bounded(&raww_full[ws], (uint32_t)((c >> 1) / TC_RAWW_SLOTS) & 1u, p.fault);
+                if (!__all_sync(0xFFFFFFFFu, ok)) break;
+                const uint32_t st = sbase + s * TC_STAGE_BYTES;
+                if (weights) {
+                    const uint32_t raw = sbase + TC_RAWW_OFF + ws * TC_RAWW_SLOT_BYTES + r * Q8_BYTES + (c & 1) * TC_W_CHUNK;
+                    uint2 wv[9];
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) wv[i] = lds_v2(raw + i * 8);
+                    tc_unpack_weight_row(st, r, wv);
+                } else {
+                    tc_stage_activation_header(st, r, lds_v4(st + TC_XH_OFF + r * 16));
+                    tc_stage_activation_header(st, r + 64, lds_v4(st + TC_XH_OFF + (r + 64) * 16));
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tiles are read by the tensor core
+                __syncwarp();
+                if (lane == 0) {
+                    if (weights && (c & 1)) mbar_arrive(&raww_empty[ws]);  // both halves of the slot have been read
+                    mbar_arrive(&stage_full[s]);
+                    if (weights && (c * TC_KB) < 128) tc_stamp(p, c * TC_KB, 3, 1 + warp - TC_CONV_WARP0);
+                }
+            }
         }
     }
 
@@ -466,7 +484,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_0_q8_1_tc_kernel(const 
 
 int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
                    int order) {
-    if (K % (TC_KB * QK) != 0) return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 GEMM needs K %% 128 == 0 (K = %lld)", (long long)K);
+    // a weight row's pitch, K / 32 * 18 bytes, must be a multiple of 16 for the tensor copies
+    if (K % (2 * SUPER) != 0) return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 GEMM needs K %% 256 == 0 (K = %lld)", (long long)K);
     if (((uintptr_t)d_w & 15u) != 0 || ((uintptr_t)d_xq & 15u) != 0)
         return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 GEMM needs 16-byte aligned operands");
     if (N == 0 || M == 0) return JQ_OK;
@@ -474,7 +493,8 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
     if (int rc = device_caps(&caps)) return rc;
     if (caps.cc / 10 != 10) return set_error(JQ_ERR_UNSUPPORTED, "tcgen05 needs an sm_100-class device");
     const int64_t gx = (N + TC_BN - 1) / TC_BN, gy = (M + TC_BM - 1) / TC_BM;
-    if (gy > 65535 || K > (1 << 24)) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tcgen05 GEMM");
+    if (gy > 65535 || K > (1 << 24) || (K / SUPER) * M >= ((int64_t)1 << 31) || N >= ((int64_t)1 << 31))
+        return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tcgen05 GEMM");
     TcParams p{};
     p.w = static_cast<const uint8_t *>(d_w);
     p.xq = static_cast<const uint8_t *>(d_xq);
@@ -489,7 +509,13 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_tc_kernel), TC_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
-    gemm_q4_0_q8_1_tc_kernel<<<dim3((unsigned)gx, (unsigned)gy), TC_THREADS, TC_SMEM_BYTES, st>>>(p);
+    CUtensorMap w_map, x_map;
+    if (int rc = encode_byte_map(&w_map, d_w, p.row_bytes, (uint64_t)N, p.row_bytes, Q8_BYTES, 128)) return rc;
+    const uint64_t x_row = (uint64_t)p.n_super * Q8_BYTES;
+    if (int rc = order == JQ_ORDER_KSUPER_COL ? encode_byte_map(&x_map, d_xq, Q8_BYTES, (uint64_t)p.n_super * (uint64_t)M, Q8_BYTES, 16, 128)
+                                              : encode_byte_map(&x_map, d_xq, x_row, (uint64_t)M, x_row, 16, 128))
+        return rc;
+    gemm_q4_0_q8_1_tc_kernel<<<dim3((unsigned)gx, (unsigned)gy), TC_THREADS, TC_SMEM_BYTES, st>>>(p, w_map, x_map);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }

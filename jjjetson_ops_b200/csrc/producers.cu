@@ -66,14 +66,35 @@ rms_norm_q8_1_kernel(float *input, float *residual, const float *__restrict__ we
         const float4 *in4 = reinterpret_cast<const float4 *>(input + base);
         float4 *res4 = reinterpret_cast<float4 *>(residual != nullptr ? residual + base : nullptr);
         float4 *row4 = reinterpret_cast<float4 *>(row);
-        for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
-            float4 z = in4[i];
-            if (res4 != nullptr) {
-                const float4 r = res4[i];
-                z = make_float4(z.x + r.x, z.y + r.y, z.z + r.z, z.w + r.w);
-                res4[i] = z;
+        // four 16-byte loads of each operand in flight per thread before anything is stored (the buffers may alias
+        // one another, so the compiler cannot hoist loads over stores by itself): a CTA spends half its life in the
+        // reduction and quantization phases, and what is in flight during its load phase has to cover for that
+        const int n4 = H >> 2, stride = blockDim.x;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * stride) {
+            float4 z[4], r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * stride;
+                z[u] = i < n4 ? in4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            row4[i] = z;
+            if (res4 != nullptr) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * stride;
+                    r[u] = i < n4 ? res4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * stride;
+                if (i < n4) {
+                    if (res4 != nullptr) {
+                        z[u] = make_float4(z[u].x + r[u].x, z[u].y + r[u].y, z[u].z + r[u].z, z[u].w + r[u].w);
+                        res4[i] = z[u];
+                    }
+                    row4[i] = z[u];
+                }
+            }
         }
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -117,6 +138,22 @@ rms_norm_q8_1_kernel(float *input, float *residual, const float *__restrict__ we
     if (xq == nullptr) return;
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    if ((n_super & 1) == 0) {
+        // whole pairs of blocks: a warp takes two neighbouring blocks, a lane eight consecutive values (half the
+        // instructions per value of the four-per-lane form, same bits)
+        for (int pr = warp; pr < (n_super >> 1); pr += n_warps) {
+            const float4 a = *reinterpret_cast<const float4 *>(row + pr * (2 * SUPER) + lane * 8);
+            const float4 b = *reinterpret_cast<const float4 *>(row + pr * (2 * SUPER) + lane * 8 + 4);
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            uint2 q;
+            uint32_t ds;
+            quantize_8_per_lane_q8_1(v, s_mode, &q, &ds);
+            uint8_t *blk = xq + q8_block_index(2 * pr + (lane >> 4), token, n_super, T, order) * Q8_BYTES;
+            reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = q;
+            if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+        }
+        return;
+    }
     for (int ks = warp; ks < n_super; ks += n_warps) {
         const float4 v = *reinterpret_cast<const float4 *>(row + ks * SUPER + lane * 4);
         uint32_t ds;
@@ -147,6 +184,31 @@ swiglu_q8_1_kernel(const float *gate, const float *up, float *mid, uint8_t *__re
     const IDX warp0 = (IDX)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     const IDX n_warps = (IDX)(((int64_t)gridDim.x * blockDim.x) >> 5);
     const IDX total = (IDX)(T * n_super_);
+    if ((n_super_ & 1) == 0) {
+        // whole pairs of blocks per row: a warp takes two neighbouring blocks, a lane eight consecutive values
+        const IDX pairs_row = n_super >> 1, pairs = total >> 1;
+        for (IDX p = warp0; p < pairs; p += n_warps) {
+            const IDX t = p / pairs_row, pr = p - t * pairs_row;
+            const int64_t off = (int64_t)t * I + (int64_t)pr * (2 * SUPER) + lane * 8;
+            const float4 g0 = *reinterpret_cast<const float4 *>(gate + off), g1 = *reinterpret_cast<const float4 *>(gate + off + 4);
+            const float4 u0 = *reinterpret_cast<const float4 *>(up + off), u1 = *reinterpret_cast<const float4 *>(up + off + 4);
+            const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                                silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+            if (mid != nullptr) {
+                *reinterpret_cast<float4 *>(mid + off) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4 *>(mid + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+            if (xq != nullptr) {
+                uint2 q;
+                uint32_t ds;
+                quantize_8_per_lane_q8_1(v, s_mode, &q, &ds);
+                uint8_t *blk = xq + q8_block_index(2 * (int64_t)pr + (lane >> 4), t, n_super_, T, order) * Q8_BYTES;
+                reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = q;
+                if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+            }
+        }
+        return;
+    }
     for (IDX b = warp0; b < total; b += n_warps) {
         const IDX t = b / n_super, ks = b - t * n_super;
         const int64_t off = (int64_t)t * I + (int64_t)ks * SUPER + lane * 4;

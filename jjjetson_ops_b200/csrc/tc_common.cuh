@@ -2,11 +2,61 @@
 // matrix descriptor of the unswizzled K-major operand layout, and the stores that build such tiles.
 #pragma once
 
+#include <cuda.h>
+
 #include "jq_common.cuh"
+
+namespace jq {
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library does not link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn tensor_map_encoder() {
+    static const EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            f = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// Byte tensor [rows][row_len] with rows `pitch` bytes apart, copied in boxes of box_rows rows x box_bytes bytes
+// (box_bytes a multiple of 16, at most 256; box_rows at most 256).  No swizzle: a box lands row after row.
+inline int encode_byte_map(CUtensorMap *map, const void *base, uint64_t row_len, uint64_t rows, uint64_t pitch, uint32_t box_bytes,
+                           uint32_t box_rows) {
+    const EncodeTiledFn encode = tensor_map_encoder();
+    if (encode == nullptr) return set_error(JQ_ERR_UNSUPPORTED, "the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {row_len, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t elem_strides[2] = {1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(JQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return JQ_OK;
+}
+
+}  // namespace jq
 
 #ifdef __CUDACC__
 
 namespace jq {
+
+// One tiled tensor copy global -> shared: the box of `map` at byte column x, row y; completion counted in bytes on
+// an mbarrier.  x must be a multiple of 16.  Rows past the end of the tensor arrive as zeros (and are counted).
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 
 // One operand tile is 128 rows x 32 bytes (32 int8 or 16 fp16 values of K) in the tensor core's
 // canonical K-major layout without swizzle: 8-row x 16-byte core matrices, the two 16-byte chunks of
@@ -19,11 +69,12 @@ __device__ __forceinline__ uint32_t tile_off(int r, int kc) {
     return (uint32_t)((r >> 3) * TC_SBO + kc * TC_LBO + (r & 7) * 16);
 }
 
-// shared-memory matrix descriptor of a tile: K-major, no swizzle, version 1
-__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(TC_LBO >> 4) << 16) | ((uint64_t)(TC_SBO >> 4) << 32) |
-           ((uint64_t)1 << 46);
+// shared-memory matrix descriptor of a tile: K-major, no swizzle, version 1; `lbo` bytes between the 16-byte K-chunks
+// of a row, `sbo` bytes between groups of 8 rows
+__device__ __forceinline__ uint64_t tc_desc_strided(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
 }
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) { return tc_desc_strided(smem_addr, TC_LBO, TC_SBO); }
 
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");

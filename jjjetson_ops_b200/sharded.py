@@ -89,7 +89,10 @@ class PeerBands:
 
     FLAG_BYTES = 256
 
-    def __init__(self, M_max: int, N_total: int, device: torch.device, group=None):
+    def __init__(self, M_max: int, N_total: int, device: torch.device, group=None, share_with: "Optional[PeerBands]" = None):
+        """``share_with``: another ``PeerBands`` whose arrival counts and step counter this one uses too.  The
+        layers of a chain share them, so that all-gathers are numbered across the chain and a layer's
+        ``wait_previous`` waits for the bands of the layer before it."""
         from . import capi
 
         self._capi = capi
@@ -101,6 +104,7 @@ class PeerBands:
             raise ValueError("the fused all-gather handles up to 8 ranks")
         self.M_max, self.N_total = M_max, N_total
         self.y_bytes = (M_max * N_total * 4 + 255) // 256 * 256
+        self._shared = share_with
         with torch.cuda.device(device):
             self.local_ptr, handle = capi.peer_alloc(2 * self.y_bytes + self.FLAG_BYTES)
         handles = [handle]
@@ -111,12 +115,20 @@ class PeerBands:
         with torch.cuda.device(device):
             for q in range(self.world):
                 self.ptrs.append(self.local_ptr if q == self.rank else capi.peer_open(handles[q]))
-        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)  # finished all-gathers, kept on the device
+        if share_with is None:
+            self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+            self.epoch = torch.zeros(1, dtype=torch.int32, device=device)  # finished all-gathers, kept on the device
+            self.flag_ptrs = [p + 2 * self.y_bytes for p in self.ptrs]
+        else:
+            self.counter, self.epoch, self.flag_ptrs = share_with.counter, share_with.epoch, share_with.flag_ptrs
         self._views = [capi.tensor_from_ptr(self.local_ptr + b * self.y_bytes, (M_max, N_total), torch.float32, device)
                        for b in range(2)]
         if self.world > 1:
             dist.barrier(group=group)  # everyone has mapped everyone before the first store
+
+    def view(self, parity: int) -> torch.Tensor:
+        """The ``[M, N_total]`` buffer that all-gathers of this parity (number & 1) fill."""
+        return self._views[parity & 1]
 
     def linear(self, w_shard: torch.Tensor, x: torch.Tensor, ws: torch.Tensor, n_offset: int, N_local: int,
                s_mode: Optional[int] = None) -> None:
@@ -127,14 +139,14 @@ class PeerBands:
         if M != self.M_max:
             raise ValueError("PeerBands was sized for M = %d" % self.M_max)
         y_peers = list(self.ptrs)
-        flag_peers = [p + 2 * self.y_bytes for p in self.ptrs]
+        flag_peers = list(self.flag_ptrs)
         capi.linear_q4_0_allgather(w_shard, x, ws, N_local, capi.S_D_SUM_Q if s_mode is None else s_mode, y_peers,
                                    flag_peers, self.world, self.rank, n_offset, self.N_total, self.y_bytes, True,
                                    self.epoch, self.counter)
 
     def wait(self) -> None:
         """Queue a wait (on the current stream) for the bands of the latest step from every rank."""
-        self._capi.allgather_wait(self.device, self.local_ptr + 2 * self.y_bytes, self.world, self.epoch)
+        self._capi.allgather_wait(self.device, self.flag_ptrs[self.rank], self.world, self.epoch)
 
     def latest(self) -> torch.Tensor:
         """After ``wait()``: the gathered ``[M, N_total]`` output of the latest step (synchronises to

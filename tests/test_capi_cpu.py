@@ -101,7 +101,7 @@ def test_options_round_trip():
     """Process-wide switches are plain host state: set, read back, reject unknown ones."""
     from jjjetson_ops_b200 import capi
 
-    for opt in (capi.OPT_STATIC_WEIGHTS, capi.OPT_PREFILL_FP16_OPERANDS):
+    for opt in (capi.OPT_STATIC_WEIGHTS, capi.OPT_PREFILL_EXACT):
         assert capi.get_option(opt) == 0  # both default to off
         capi.set_option(opt, 1)
         try:

@@ -86,7 +86,18 @@ def test_multiply_matches_reference_kernel(ref, native_lib, oracle, cuda_device,
     # the oracle restates the kernel's arithmetic and accumulation order: same bits expected
     assert oracle.err_max_rel(y_orc, y_ref) <= 1e-7, "oracle drifted from the reference kernel"
     y = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER).cpu().numpy()
-    assert oracle.err_max_rel(y, y_ref) <= 1e-5
+    if M >= 64:
+        # the automatic choice for 64 columns and more rounds the scaled operands to fp16: 1e-3; the exact-integer
+        # kernels behind JQ_OPT_PREFILL_EXACT meet the same bar as the decode kernels
+        assert oracle.err_max_rel(y, y_ref) <= 1e-3
+        c.set_option(c.OPT_PREFILL_EXACT, 1)
+        try:
+            y_exact = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER).cpu().numpy()
+        finally:
+            c.set_option(c.OPT_PREFILL_EXACT, 0)
+        assert oracle.err_max_rel(y_exact, y_ref) <= 1e-5
+    else:
+        assert oracle.err_max_rel(y, y_ref) <= 1e-5
     # drop-in symbol with the reference's own name and signature
     lib = c.lib()
     lib.mat_mul_q4_0_q8_1_device.restype = None

@@ -70,25 +70,31 @@ def test_upload_and_fused_views(native_lib, oracle, cuda_device, tmp_path):
 
 
 def test_prefill_option_routes_the_automatic_choice(native_lib, oracle, cuda_device):
-    """With JQ_OPT_PREFILL_FP16_OPERANDS the automatic dispatch gives the fp16-operand kernel's result for a
-    prefill batch (and the exact path's for a small one); the switch is put back whatever happens."""
+    """The automatic dispatch gives the fp16-operand kernel's result for a prefill batch and an exact-integer
+    kernel's with JQ_OPT_PREFILL_EXACT (and for a small batch either way); the switch is put back whatever happens."""
     import torch
 
     c, O = native_lib, oracle
     rng = np.random.default_rng(5)
     K, N = 512, 256
     w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
-    d_w = torch.from_numpy(O.quantize_q4_0(w)).to(cuda_device)
+    wq = O.quantize_q4_0(w)
+    d_w = torch.from_numpy(wq).to(cuda_device)
     for M in (128, 16):
         x = rng.standard_normal((M, K), dtype=np.float32)
-        d_xq = torch.from_numpy(O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)).to(cuda_device)
-        exact = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_AUTO).cpu().numpy()
+        xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+        d_xq = torch.from_numpy(xq).to(cuda_device)
+        auto = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_AUTO).cpu().numpy()
         named = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_F16).cpu().numpy()
-        c.set_option(c.OPT_PREFILL_FP16_OPERANDS, 1)
+        c.set_option(c.OPT_PREFILL_EXACT, 1)
         try:
-            opted = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_AUTO).cpu().numpy()
+            exact = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_AUTO).cpu().numpy()
         finally:
-            c.set_option(c.OPT_PREFILL_FP16_OPERANDS, 0)
-        assert np.array_equal(opted, named if M >= 64 else exact)
-        assert O.err_max_rel(opted, exact) <= 1e-3
-    assert c.get_option(c.OPT_PREFILL_FP16_OPERANDS) == 0 and c.device_fault(clear=True) == 0
+            c.set_option(c.OPT_PREFILL_EXACT, 0)
+        ref = O.mul_mat_ref(wq, xq, K, N, M)
+        assert O.err_max_rel(exact, ref) <= 1e-5
+        if M >= 64:
+            assert np.array_equal(auto, named) and O.err_max_rel(auto, ref) <= 1e-3
+        else:
+            assert np.array_equal(auto, exact)
+    assert c.get_option(c.OPT_PREFILL_EXACT) == 0 and c.device_fault(clear=True) == 0

@@ -41,7 +41,8 @@ def test_noalloc_entry_matches_workspace_entry_twice_in_a_row(native_lib, oracle
         assert np.array_equal(got, want)  # same kernels on the same inputs: in fact the same bits
         # and against the CPU oracle, like every other parity test
         xq = oracle.quantize_q8_1(x, oracle.ORDER_COL_KSUPER, oracle.S_D_SUM_Q)
-        assert oracle.err_max_rel(got, oracle.mul_mat_ref(d_w.cpu().numpy(), xq, K, N, M)) <= 1e-5
+        # (64 columns and more take the fp16-operand GEMM, which the other tests hold to 1e-3 against the formula)
+        assert oracle.err_max_rel(got, oracle.mul_mat_ref(d_w.cpu().numpy(), xq, K, N, M)) <= (1e-3 if M >= 64 else 1e-5)
     assert c.device_fault() == 0
 
 
