@@ -1136,6 +1136,85 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
             "launches_per_pass": "5 linears (+1 slice copy)", "weight_copies": R}
 
 
+def run_case(args) -> None:
+    """One kernel of the path on its benchmark workload, a few launches and nothing else: the command the ncu
+    summaries under profiles/ are captured on.  Prints one JSON line with the CUDA-event time per launch."""
+    import torch
+
+    from jjjetson_ops_b200 import capi, synth
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    capi.set_option(capi.OPT_STATIC_WEIGHTS, 1)
+    rng = np.random.default_rng(11)
+    steps = args.steps if args.steps != 4096 else 8
+
+    def weights(N, K, copies):
+        base = torch.from_numpy(rng.integers(0, 256, size=capi.q4_0_bytes(N, K), dtype=np.uint8)).to(dev).view(N, -1)
+        blk = base.view(N, K // 32, 18)
+        blk[:, :, 0] = 0
+        blk[:, :, 1] = 0x20
+        return [base] + [torch.roll(base, shifts=32 * r, dims=0).contiguous() for r in range(1, copies)]
+
+    name = args.case
+    if name in ("gemv_dp4a", "gemv_dp4a_mul_only", "gemv_mma"):
+        K, N, M = 4096, 11008, 8 if name == "gemv_mma" else 1
+        ws_ = weights(N, K, 17)
+        x = torch.from_numpy(rng.standard_normal((M, K), dtype=np.float32)).to(dev)
+        xq = capi.quantize_q8_1(x, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q)
+        scratch = torch.zeros(capi.q8_1_bytes(K, M), dtype=torch.uint8, device=dev)
+        y = torch.zeros((M, N), dtype=torch.float32, device=dev)
+        if name == "gemv_dp4a":
+            fn = lambda i: capi.linear_q4_0(ws_[i % 17], x, N, capi.S_D_SUM_Q, ws=scratch, out=y)
+        else:
+            fn = lambda i: capi.mul_mat_q4_0_q8_1(ws_[i % 17], xq, K, N, M, capi.ORDER_COL_KSUPER, out=y)
+        nbytes = synth.algorithmic_bytes(K, N, M, fused_quantize=name == "gemv_dp4a")
+    elif name in ("gemm_f16", "gemm_tc", "gemm_mma"):
+        K, N, M = 4096, 4096, 512
+        ws_ = weights(N, K, 2)
+        x = torch.from_numpy(rng.standard_normal((M, K), dtype=np.float32)).to(dev)
+        xq = capi.quantize_q8_1(x, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q)
+        y = torch.zeros((M, N), dtype=torch.float32, device=dev)
+        kern = {"gemm_f16": capi.KERNEL_GEMM_F16, "gemm_tc": capi.KERNEL_GEMM_TC, "gemm_mma": capi.KERNEL_GEMM_MMA}[name]
+        fn = lambda i: capi.mul_mat_q4_0_q8_1(ws_[i % 2], xq, K, N, M, capi.ORDER_COL_KSUPER, kern, out=y)
+        nbytes = synth.algorithmic_bytes(K, N, M, fused_quantize=False)
+    elif name == "quantize":
+        M, K = 8192, 8192  # 344 MB per launch: above L2 size
+        x = torch.from_numpy(rng.standard_normal((M, K), dtype=np.float32)).to(dev)
+        out = torch.zeros(capi.q8_1_bytes(K, M), dtype=torch.uint8, device=dev)
+        fn = lambda i: capi.quantize_q8_1(x, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q, out=out)
+        nbytes = M * K * 4 + M * (K // 128) * 144
+    elif name == "rms_norm":
+        T, H = 4096, 4096
+        x = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
+        res = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
+        w = torch.ones(H, dtype=torch.float32, device=dev)
+        xq = torch.zeros(capi.q8_1_bytes(H, T), dtype=torch.uint8, device=dev)
+        fn = lambda i: capi.rms_norm_q8_1(x, w, 1e-6, residual=res, xq=xq)
+        nbytes = T * H * 4 * 3 + H * 4 + T * (H // 128) * 144
+    elif name == "swiglu":
+        T, I = 2048, 11008
+        g = torch.from_numpy(rng.standard_normal((T, I), dtype=np.float32)).to(dev)
+        u = torch.from_numpy(rng.standard_normal((T, I), dtype=np.float32)).to(dev)
+        mq = torch.zeros(capi.q8_1_bytes(I, T), dtype=torch.uint8, device=dev)
+        fn = lambda i: capi.swiglu_q8_1(g, u, xq=mq)
+        nbytes = T * I * 4 * 2 + T * (I // 128) * 144
+    else:
+        raise SystemExit("unknown case %r" % name)
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        fn(i)
+    end.record()
+    torch.cuda.synchronize()
+    t = start.elapsed_time(end) / 1e3 / steps
+    print(json.dumps({"case": name, "launches": steps, "us_per_launch_direct_launches": t * 1e6, "algorithmic_bytes": nbytes,
+                      "GB/s": nbytes / t / 1e9, "device_fault": capi.device_fault()}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1152,7 +1231,13 @@ def main() -> None:
                     help="N > 1: all-gather fused into the multiply kernel (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-overlap", action="store_true",
                     help="do not let a step's weight stream start before the previous step has finished")
+    ap.add_argument("--case", default=None,
+                    help="run a few launches of one kernel on its benchmark workload and exit (the command of the ncu summaries "
+                         "under profiles/): gemv_dp4a, gemv_dp4a_mul_only, gemv_mma, gemm_f16, gemm_tc, gemm_mma, quantize, rms_norm, swiglu")
     args = ap.parse_args()
+    if args.case is not None:
+        run_case(args)
+        return
     if args.impl == "reference":
         if args.steps == 4096:
             args.steps = 200

@@ -231,12 +231,16 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
     int s = 0;
     uint32_t round = 0;
     bool x_done = false;
+    // A sharded layer that consumes a gathered output waits several microseconds for the bands before its
+    // activations can come in: with static weights the whole ring is requested first, it lands during that wait.
+    const int early_stages =
+        p.x_copy_bytes != 0 && p.prefetch_early && p.gather.world > 1 && p.gather.wait_previous ? p.stages : p.early_stages;
     for (int c = 0; c < n_chunks; ++c) {
         int rows;
         const int64_t r0 = walk_stage(walk, c, R, &rows);
         int ok = 1;
         if (lane == 0) {
-            if (c == p.early_stages) {
+            if (c == early_stages) {
                 ok = producer_activations(p, x_ready, x_full, xs, xraw) ? 1 : 0;
                 x_done = true;
             }

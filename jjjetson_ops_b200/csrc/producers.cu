@@ -45,7 +45,7 @@ __device__ __forceinline__ float block_sum_reference_order(float v, float *warp_
 // the per-thread partial sums of squares, the block tree and rsqrtf give the same inverse RMS bit
 // for bit.  The normalised row is staged in shared memory and quantized from there warp by warp
 // (one warp per 128-value block, one lane four consecutive values: the quantizer's own mapping).
-__global__ void __launch_bounds__(RMS_THREADS)
+__global__ void __launch_bounds__(RMS_THREADS, 5)
 rms_norm_q8_1_kernel(float *input, float *residual, const float *__restrict__ weight, float *normed_out,
                      uint8_t *__restrict__ xq, int H, int T, float epsilon, int n_super, int order, int s_mode) {
     // input, residual and normed_out carry no __restrict__: normed_out may be input itself (the reference's
