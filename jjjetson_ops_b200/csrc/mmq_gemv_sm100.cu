@@ -59,9 +59,8 @@ struct GemvParams {
     int rows_per_stage;
     int prefetch_early;    // the weight stream may start before the preceding kernel in the stream has finished
     int early_stages;      // stages the producer may request before the activations are staged
-    uint32_t x_copy_bytes; // > 0: the producer brings the activations in by bulk copy (fp32 to quantize, or ready
-                           // blocks straight to their place), queued ahead of the rest of the weight stream
-    uint32_t xraw_bytes;   // shared bytes reserved for fp32 activations copied that way
+    uint32_t x_copy_bytes; // > 0: the producer brings ready Q8_1 blocks in by bulk copy, straight to their place,
+                           // queued ahead of the rest of the weight stream
     GatherArgs gather;     // all-gather epilogue (world == 0: plain store to y)
     uint32_t y_bytes;      // shared bytes of the band staging buffer [M][y_rows] (gather only)
     uint32_t y_rows;
@@ -201,10 +200,9 @@ __device__ __forceinline__ bool wait_flags_serial(const uint32_t *flags, int wor
 
 // The point in the producer's walk where the activations come in (one thread).  Old protocol: the consumer
 // warps load them and the producer only waits until those loads have landed.  With x_copy_bytes the producer
-// itself queues them as bulk copies, ahead of the rest of the weight stream, after it has waited for the
-// previous kernel (and, for an N-sharded layer that consumes a gathered output, for that output's bands).
-__device__ __forceinline__ bool producer_activations(const GemvParams &p, uint64_t *x_ready, uint64_t *x_full, uint8_t *xs,
-                                                     uint8_t *xraw) {
+// itself queues the ready blocks as bulk copies, ahead of the rest of the weight stream, after it has waited for
+// the previous kernel (and, for an N-sharded layer that consumes a gathered output, for that output's bands).
+__device__ __forceinline__ bool producer_activations(const GemvParams &p, uint64_t *x_ready, uint64_t *x_full, uint8_t *xs) {
     if (p.x_copy_bytes == 0) return !p.prefetch_early || mbar_wait_bounded(x_ready, 0u, p.fault, p.poll_limit);
     if (p.prefetch_early) griddep_wait();
     if (p.gather.world > 0 && p.gather.wait_previous) {
@@ -212,19 +210,15 @@ __device__ __forceinline__ bool producer_activations(const GemvParams &p, uint64
         if (done != 0 && !wait_flags_serial(p.gather.flag_peer[p.gather.rank], p.gather.world, done, p.fault, p.poll_limit)) return false;
     }
     mbar_arrive_expect_tx(x_full, p.x_copy_bytes);
-    if (p.x_f32 != nullptr) {
-        bulk_g2s(xraw, p.x_f32, p.x_copy_bytes, x_full);
-    } else {
-        const uint32_t per_row = (uint32_t)p.n_super * Q8_BYTES;
-        for (int m = 0; m < p.M; ++m) bulk_g2s(xs + (size_t)m * p.x_pitch, p.xq + (size_t)m * per_row, per_row, x_full);
-    }
+    const uint32_t per_row = (uint32_t)p.n_super * Q8_BYTES;
+    for (int m = 0; m < p.M; ++m) bulk_g2s(xs + (size_t)m * p.x_pitch, p.xq + (size_t)m * per_row, per_row, x_full);
     return true;
 }
 
 template <bool PER_ROW>
 __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty,
                                               uint64_t *x_ready, uint8_t *ring, int lane, uint64_t *x_full = nullptr,
-                                              uint8_t *xs = nullptr, uint8_t *xraw = nullptr) {
+                                              uint8_t *xs = nullptr) {
     const int R = p.rows_per_stage;
     const RowWalk walk = cta_row_walk(p, R);
     const int n_chunks = walk.n_chunks;
@@ -241,7 +235,7 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
         int ok = 1;
         if (lane == 0) {
             if (c == early_stages) {
-                ok = producer_activations(p, x_ready, x_full, xs, xraw) ? 1 : 0;
+                ok = producer_activations(p, x_ready, x_full, xs) ? 1 : 0;
                 x_done = true;
             }
             if (ok && round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1u, p.fault, p.poll_limit)) ok = 0;
@@ -285,7 +279,7 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
         }
     }
     // fewer stages than may be requested early: the activations still have to be brought in
-    if (lane == 0 && !x_done && p.x_copy_bytes != 0) producer_activations(p, x_ready, x_full, xs, xraw);
+    if (lane == 0 && !x_done && p.x_copy_bytes != 0) producer_activations(p, x_ready, x_full, xs);
 }
 
 // Prologue of the consumer warps: put the quantized activations into shared memory, laid out
@@ -338,43 +332,63 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
     }
 }
 
-// Two neighbouring 128-value blocks (256 consecutive floats in shared memory) quantized by one warp, eight values
-// per lane (quantize_8_per_lane_q8_1).
-__device__ __forceinline__ void quantize_pair_q8_1(uint32_t x_addr, int lane, int s_mode, uint2 *q_out, uint32_t *ds_bits) {
-    const uint4 ua = lds_v4(x_addr + (uint32_t)lane * 32u), ub = lds_v4(x_addr + (uint32_t)lane * 32u + 16u);
-    const float v[8] = {__uint_as_float(ua.x), __uint_as_float(ua.y), __uint_as_float(ua.z), __uint_as_float(ua.w),
-                        __uint_as_float(ub.x), __uint_as_float(ub.y), __uint_as_float(ub.z), __uint_as_float(ub.w)};
-    quantize_8_per_lane_q8_1(v, s_mode, q_out, ds_bits);
-}
-
-// Prologue of the consumer warps when the producer copied fp32 activations into shared memory: quantize them
-// into the block layout the kernels read, warp w taking the block pairs w, w + NW, ...
-template <int NW>
-__device__ __forceinline__ void quantize_copied_activations(const GemvParams &p, uint8_t *xs, const uint8_t *xraw, int warp, int lane) {
-    const int pairs = p.M * p.n_super / 2;  // n_super is even (K % 256 == 0): a pair never straddles two rows
-    const uint32_t xraw_addr = smem_u32(xraw);
-    for (int pr = warp; pr < pairs; pr += NW) {
-        uint2 qv;
-        uint32_t ds;
-        quantize_pair_q8_1(xraw_addr + (uint32_t)pr * (2u * SUPER * 4u), lane, p.s_mode, &qv, &ds);
-        const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
-        const int m = idx / p.n_super, ks = idx - m * p.n_super;
-        uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-        reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
-        if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
-        if (p.xq_out != nullptr && blockIdx.x == 0) {
-            uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-            reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
-            if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
-        }
-    }
-}
-
 template <int NW>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, uint64_t *x_ready, int warp,
                                                   int lane) {
     const int total = p.M * p.n_super;
-    if (p.x_f32 != nullptr) {
+    bool arrived = false;  // this warp has told the producer that its first loads have landed
+    if (p.x_f32 != nullptr && (p.n_super & 1) == 0) {
+        // Whole pairs of blocks (K % 256 == 0): warp w takes the pairs w, w + NW, ..., eight values per lane
+        // (half the instructions per value of the four-per-lane form below, same bits).  All of a warp's loads
+        // are issued before the first pair is quantized.
+        const int pairs = total >> 1;
+        constexpr int MAXP = 4;  // pairs per warp held in registers at once
+        for (int p0 = warp; p0 < pairs; p0 += NW * MAXP) {
+            float4 xa[MAXP], xb[MAXP];
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u) {
+                const int pr = p0 + u * NW;
+                xa[u] = xb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (pr < pairs) {
+                    const float4 *src = reinterpret_cast<const float4 *>(p.x_f32 + (size_t)pr * (2 * SUPER)) + 2 * lane;
+                    xa[u] = __ldg(src);
+                    xb[u] = __ldg(src + 1);
+                }
+            }
+            if (!arrived) {
+                float touch = 0.0f;
+#pragma unroll
+                for (int u = 0; u < MAXP; ++u) touch += xa[u].x + xb[u].x;
+                touch = __shfl_xor_sync(0xFFFFFFFFu, touch, 1, 32);
+                if (lane == 0) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // after %1" ::"r"(smem_u32(x_ready)), "f"(touch)
+                                 : "memory");
+                }
+                arrived = true;
+                if (threadIdx.x == 0) trace_fine(p, 0);  // warp 0: x loads landed
+            }
+#pragma unroll
+            for (int u = 0; u < MAXP; ++u) {
+                const int pr = p0 + u * NW;  // uniform across the warp
+                if (pr >= pairs) break;
+                const float v[8] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w, xb[u].x, xb[u].y, xb[u].z, xb[u].w};
+                uint2 qv;
+                uint32_t ds;
+                quantize_8_per_lane_q8_1(v, p.s_mode, &qv, &ds);
+                const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
+                const int m = idx / p.n_super, ks = idx - m * p.n_super;
+                uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+                reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
+                if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+                if (p.xq_out != nullptr && blockIdx.x == 0) {
+                    uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+                    reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
+                    if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
+                }
+            }
+        }
+    } else if (p.x_f32 != nullptr) {
+        arrived = warp < total;  // quantize_batch arrives for the warps that have a block
         // The prologue is bound by instruction issue (every CTA repeats it, ~100 instructions per block and
         // lane): a warp takes exactly the blocks it has to, two at a time when that covers them all
         // (one activation row of K = 4096 over 16 warps), else four at a time.
@@ -395,7 +409,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
                 __ldg(reinterpret_cast<const uint4 *>(g) + part);
         }
     }
-    if (p.x_f32 == nullptr || warp >= total) {
+    if (!arrived) {
         // copies issued above were consumed by their stores; warps without a group arrive at once
         __syncwarp();
         if (lane == 0) mbar_arrive(x_ready);
@@ -469,8 +483,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     uint64_t *x_full = full + 25;
     float *ybuf = reinterpret_cast<float *>(smem + GV_BAR_BYTES);
     uint8_t *xs = smem + GV_BAR_BYTES + p.y_bytes;
-    uint8_t *xraw = xs + p.x_bytes;
-    uint8_t *ring = xraw + p.xraw_bytes;
+    uint8_t *ring = xs + p.x_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -490,7 +503,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         if (lane == 0) {
             if (!p.prefetch_early) griddep_wait();
             trace_stamp(p, 1);  // weight stream begins
-            gemv_producer<false>(p, full, empty, x_ready, ring, 0, x_full, xs, xraw);
+            gemv_producer<false>(p, full, empty, x_ready, ring, 0, x_full, xs);
             trace_stamp(p, 2);  // last copy issued
         }
         return;
@@ -520,12 +533,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
 
     if (p.x_copy_bytes != 0) {
         if (!mbar_wait_bounded(x_full, 0u, p.fault, p.poll_limit)) return;
-        if (threadIdx.x == 0) trace_fine(p, 0);  // activations landed in shared memory
-        if (p.x_f32 != nullptr) {
-            quantize_copied_activations<NW>(p, xs, xraw, warp, lane);
-            if (threadIdx.x == 0) trace_fine(p, 1);  // warp 0: its blocks are quantized
-            named_bar_sync(1, NW * 32);
-        }
+        if (threadIdx.x == 0) trace_fine(p, 0);  // the blocks have landed in shared memory
     } else {
         stage_activations<NW>(p, xs, x_ready, warp, lane);
     }
@@ -925,13 +933,13 @@ int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     }
     for (;;) {
         p.stage_bytes = align_up((uint32_t)p.rows_per_stage * p.row_bytes, 128);
-        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes - p.y_bytes - p.xraw_bytes;
+        const int64_t avail = budget - GV_BAR_BYTES - p.x_bytes - p.y_bytes;
         p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
         if (p.stages >= 3 || p.rows_per_stage == 1) break;
         p.rows_per_stage = p.rows_per_stage > 2 ? p.rows_per_stage / 2 : 1;
     }
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
-    const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + (int)p.xraw_bytes + p.stages * (int)p.stage_bytes;
+    const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
     auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
@@ -984,8 +992,8 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
     p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
     // Ahead of the previous kernel's end only two stages are requested (more would delay the
-    // activation loads that follow the wait); a kernel that quantizes in its prologue starts its
-    // stream at the wait instead, where it overlaps the quantization.
+    // activation loads that follow the wait).  The mma variant, when it quantizes in its prologue, starts its
+    // stream at the wait instead (the dp4a launcher sets its own policy, measured there).
     if (d_x_f32 != nullptr) p.prefetch_early = 0;
     p.early_stages = p.prefetch_early ? 2 : (1 << 30);
     p.poll_limit = wait_poll_limit();
@@ -1042,28 +1050,24 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
     if (gather != nullptr) p.gather = *gather;
     if (int rc = apply_multi(p, multi, gather)) return rc;
-    // The activations come in by bulk copy, queued by the producer ahead of the rest of its weight stream: fp32
-    // values into a staging area the consumer warps quantize from, ready blocks straight to their place (when a
-    // column's blocks are contiguous).  The weight stream may then run ahead of the previous kernel's end by one
-    // or two stages only: what is in flight then delays the activations.
-    if (p.x_f32 != nullptr) {
-        p.x_copy_bytes = (uint32_t)(M * K * sizeof(float));
-        p.xraw_bytes = align_up(p.x_copy_bytes, 128);
-    } else if (order == JQ_ORDER_COL_KSUPER || M == 1) {
-        p.x_copy_bytes = (uint32_t)(M * p.n_super * Q8_BYTES);
-    }
-    if (p.x_copy_bytes != 0) {
-        // measured on cfg2 at M = 1 (cold weights): fp32 activations 7.2 us with one stage ahead, 7.3 with two, 7.4 with
-        // none; ready blocks 6.3 / 5.9 / 7.3 us
-        p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
-        p.early_stages = !p.prefetch_early ? 0 : (p.x_f32 != nullptr ? 1 : 2);
-    }
+    // Ready Q8_1 blocks whose columns are contiguous come in by bulk copy, queued by the producer thread ahead of
+    // the rest of its weight stream, straight to their place in shared memory.  fp32 activations are loaded by
+    // the consumer warps themselves (each its own pair of blocks, quantized in registers): their loads take the
+    // load/store path and overtake the weight copies already queued, a bulk copy behind two stages of weights
+    // does not.  Medians of 7 x 128 graph-replayed steps, cold weights, stages requested ahead of the previous
+    // kernel's end 0 / 1 / 2 / 3: cfg2 fused, loads by the warps 7.19 / 6.88 / 6.19 / 6.66 us, by bulk copy
+    // 7.16 / 7.39 / 7.36 / 7.41 us; cfg2 ready blocks by bulk copy 7.01 / 6.25 / 6.03 / 6.41 us; K = 11008 ready
+    // blocks, bulk copy 9.34 / 8.18 / 7.63 / 7.98 us, loads by the warps 10.45 / 9.89 / 8.85 / 8.83 us.
+    if (p.x_f32 == nullptr && (order == JQ_ORDER_COL_KSUPER || M == 1)) p.x_copy_bytes = (uint32_t)(M * p.n_super * Q8_BYTES);
+    p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
+    p.early_stages = p.prefetch_early ? 2 : (p.x_copy_bytes != 0 ? 0 : (1 << 30));
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {
             case 1:
                 // Quantizing in the prologue is repeated by every CTA: one CTA of 16 warps per SM halves
                 // that cost.  With ready-made Q8_1 input two CTAs of 8 warps per SM overlap better.
+                // (20 consumer warps instead of 16 fit the register file and change nothing: 6.22 us either way)
                 if (p.x_f32 != nullptr) return run_dp4a<1, 1, 16, 1>(st, p, caps);
                 return run_dp4a<1, 1, 8, 2>(st, p, caps);
             case 2: return run_dp4a<1, 2, 8, 1>(st, p, caps);
