@@ -361,16 +361,15 @@ int jq_mul_mat_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_xq,
     return jq_mul_mat_q4_0_q8_1_device_ex(stream, d_w, d_xq, d_y, K, N, M, order, JQ_KERNEL_AUTO);
 }
 
-// The quantizer runs in the multiply kernel's own prologue while the activations are at most this many
-// 128-value blocks: every CTA repeats it (about 0.8 us per 32 blocks), while a quantize launch of its own
-// costs about 2.8 us in a dependent chain whatever the size.  Measured on cfg2 (cold weights) with the limit at
-// 32 / 64 / 128 / 256 blocks: M = 2 10.4 us whatever the limit, M = 4 11.8 / 11.8 / 13.6 / 13.6 us, M = 8
-// 12.3 / 12.3 / 12.3 / 18.5 us, K = 11008 at M = 1 7.5 / 7.5 / 10.0 / 10.0 us.
-// (One activation row of K = 8192 is the exception: 23.7 us fused, 27 us as two launches.)
-constexpr int64_t FUSE_QUANTIZER_MAX_BLOCKS = 32;
+// The quantizer runs in the multiply kernel's own prologue (every CTA quantizes all the activations, its warps
+// taking a pair of 128-value blocks each, about 0.5 us per 32 blocks) instead of a launch of its own (about 2.8 us
+// in a dependent chain whatever the size) for up to four activation rows of K <= 4096 and one row of K <= 8192.
+// Measured on cfg2 (cold weights), fused against two launches: M = 2 9.4 against 10.3 us, M = 4 10.8 against
+// 11.8 us, M = 8 13.2 against 12.3 us; one row of K = 8192 22.4 against 27 us; one row of K = 11008 (seven
+// consumer warps) 9.1 against 7.4 us.
 inline bool fuse_quantizer_pays(int64_t M, int64_t K) {
-    const int64_t blocks = M * (K / SUPER);
-    return blocks <= FUSE_QUANTIZER_MAX_BLOCKS || (M == 1 && blocks <= 2 * FUSE_QUANTIZER_MAX_BLOCKS);
+    const int64_t n_super = K / SUPER, blocks = M * n_super;
+    return (n_super <= 32 && blocks <= 128) || (n_super <= 64 && blocks <= 64);
 }
 
 int jq_linear_q4_0_device(void *stream, const void *d_w, const float *d_x, void *d_ws, float *d_y, int64_t K,
