@@ -982,26 +982,26 @@ def bench_producers(torch, capi, dev, peaks):
     """The two producer kernels alone on prefill-sized inputs (HBM-bound streaming kernels)."""
     out = {}
     rng = np.random.default_rng(8)
-    T, H, I = 4096, 4096, 11008
+    T, H, I = 8192, 4096, 11008  # T = 4096 leaves a third of the rows in L2 from one launch to the next
     x = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
     res = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
     w = torch.ones(H, dtype=torch.float32, device=dev)
     xq = torch.zeros(capi.q8_1_bytes(H, T), dtype=torch.uint8, device=dev)
     sec, _ = time_graph_steps(torch, lambda i: capi.rms_norm_q8_1(x, w, 1e-6, residual=res, xq=xq), 20, 3, lambda: None)
     b = T * H * 4 * 3 + H * 4 + T * (H // 128) * 144  # read input and residual, write residual and the blocks
-    out["rms_norm_fused_add_q8_1_T4096_H4096"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
+    out["rms_norm_fused_add_q8_1_T8192_H4096"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
                                                   "frac_hbm": b * 20 / sec / 1e9 / peaks["hbm_gbs"],
-                                                  "bytes": b, "note": "201 MB per launch: larger than L2"}
+                                                  "bytes": b, "note": "440 MB per launch, 306 MB resident: well above L2 size"}
     del x, res, xq
-    Ts = 2048
+    Ts = 4096
     g = torch.from_numpy(rng.standard_normal((Ts, I), dtype=np.float32)).to(dev)
     u = torch.from_numpy(rng.standard_normal((Ts, I), dtype=np.float32)).to(dev)
     mq = torch.zeros(capi.q8_1_bytes(I, Ts), dtype=torch.uint8, device=dev)
     sec, _ = time_graph_steps(torch, lambda i: capi.swiglu_q8_1(g, u, xq=mq), 20, 3, lambda: None)
     b = Ts * I * 4 * 2 + Ts * (I // 128) * 144
-    out["swiglu_q8_1_T2048_I11008"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
+    out["swiglu_q8_1_T4096_I11008"] = {"us": sec / 20 * 1e6, "GB/s": b * 20 / sec / 1e9,
                                        "frac_hbm": b * 20 / sec / 1e9 / peaks["hbm_gbs"], "bytes": b,
-                                       "note": "206 MB per launch: larger than L2"}
+                                       "note": "411 MB per launch: well above L2 size"}
     del g, u, mq
     torch.cuda.empty_cache()
     return out
@@ -1119,8 +1119,12 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
     def step(i):
         w = layers[i % R]
         capi.linear_q4_0(w[0], x0, 12288, capi.S_D_SUM_Q, ws=scratch, out=y_qkv)
-        o_in.copy_(y_qkv[:, :4096])
-        capi.linear_q4_0(w[1], o_in, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_o)
+        if M == 1:
+            o_src = y_qkv[:, :4096]  # one row: its first 4096 columns are contiguous, no copy needed
+        else:
+            o_in.copy_(y_qkv[:, :4096])
+            o_src = o_in
+        capi.linear_q4_0(w[1], o_src, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_o)
         capi.linear_q4_0(w[2], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_gate)
         capi.linear_q4_0(w[3], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_up)
         capi.linear_q4_0(w[4], xdown, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_down)
@@ -1133,7 +1137,7 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
     del layers
     torch.cuda.empty_cache()
     return {"us": t * 1e6, "GB/s": alg / t / 1e9, "frac_hbm": alg / t / 1e9 / peaks["hbm_gbs"], "TOPS": ops / t / 1e12,
-            "launches_per_pass": "5 linears (+1 slice copy)", "weight_copies": R}
+            "launches_per_pass": "5 linears" + ("" if M == 1 else " (+1 slice copy)"), "weight_copies": R}
 
 
 def run_case(args) -> None:
@@ -1185,7 +1189,7 @@ def run_case(args) -> None:
         fn = lambda i: capi.quantize_q8_1(x, capi.ORDER_COL_KSUPER, capi.S_D_SUM_Q, out=out)
         nbytes = M * K * 4 + M * (K // 128) * 144
     elif name == "rms_norm":
-        T, H = 4096, 4096
+        T, H = 8192, 4096
         x = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
         res = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(dev)
         w = torch.ones(H, dtype=torch.float32, device=dev)
@@ -1193,7 +1197,7 @@ def run_case(args) -> None:
         fn = lambda i: capi.rms_norm_q8_1(x, w, 1e-6, residual=res, xq=xq)
         nbytes = T * H * 4 * 3 + H * 4 + T * (H // 128) * 144
     elif name == "swiglu":
-        T, I = 2048, 11008
+        T, I = 4096, 11008
         g = torch.from_numpy(rng.standard_normal((T, I), dtype=np.float32)).to(dev)
         u = torch.from_numpy(rng.standard_normal((T, I), dtype=np.float32)).to(dev)
         mq = torch.zeros(capi.q8_1_bytes(I, T), dtype=torch.uint8, device=dev)

@@ -109,15 +109,54 @@ rms_norm_q8_1_kernel(float *input, float *residual, const float *__restrict__ we
     __syncthreads();
     // sum of squares in the reference's order: thread t takes elements t, t + blockDim, ...
     float sum_square = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float z = row[i];
-        sum_square = __fmaf_rn(z, z, sum_square);
+    {
+        int i = threadIdx.x;
+        const int stride = blockDim.x;
+        for (; i + 3 * stride < H; i += 4 * stride) {  // same elements in the same order, four loads in flight
+            const float z0 = row[i], z1 = row[i + stride], z2 = row[i + 2 * stride], z3 = row[i + 3 * stride];
+            sum_square = __fmaf_rn(z0, z0, sum_square);
+            sum_square = __fmaf_rn(z1, z1, sum_square);
+            sum_square = __fmaf_rn(z2, z2, sum_square);
+            sum_square = __fmaf_rn(z3, z3, sum_square);
+        }
+        for (; i < H; i += stride) {
+            const float z = row[i];
+            sum_square = __fmaf_rn(z, z, sum_square);
+        }
     }
     sum_square = block_sum_reference_order(sum_square, warp_partial);
     if (threadIdx.x == 0) inverse_rms = rsqrtf(sum_square / (float)H + epsilon);
     __syncthreads();
     const float inv = inverse_rms;
-    if (vec && ((uintptr_t)weight & 15u) == 0 && (normed_out == nullptr || ((uintptr_t)(normed_out + base) & 15u) == 0)) {
+    const bool vec_out = vec && ((uintptr_t)weight & 15u) == 0 && (normed_out == nullptr || ((uintptr_t)(normed_out + base) & 15u) == 0);
+    if (vec_out && xq != nullptr && (n_super & 1) == 0) {
+        // Normalisation and quantization in one pass over the row: a warp takes a pair of neighbouring blocks, a lane
+        // its eight consecutive values, (z * inv) * w goes to the fp32 output (if wanted) and into the quantizer
+        // straight from registers.  Same products, same bits as normalising the row first; it saves the row's second
+        // trip through shared memory, one block-wide barrier and a quarter of the kernel's instructions.
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+        for (int pr = warp; pr < (n_super >> 1); pr += n_warps) {
+            const int e0 = pr * (2 * SUPER) + lane * 8;
+            const float4 z0 = *reinterpret_cast<const float4 *>(row + e0), z1 = *reinterpret_cast<const float4 *>(row + e0 + 4);
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(weight + e0)), w1 = __ldg(reinterpret_cast<const float4 *>(weight + e0 + 4));
+            const float v[8] = {__fmul_rn(__fmul_rn(z0.x, inv), w0.x), __fmul_rn(__fmul_rn(z0.y, inv), w0.y),
+                                __fmul_rn(__fmul_rn(z0.z, inv), w0.z), __fmul_rn(__fmul_rn(z0.w, inv), w0.w),
+                                __fmul_rn(__fmul_rn(z1.x, inv), w1.x), __fmul_rn(__fmul_rn(z1.y, inv), w1.y),
+                                __fmul_rn(__fmul_rn(z1.z, inv), w1.z), __fmul_rn(__fmul_rn(z1.w, inv), w1.w)};
+            if (normed_out != nullptr) {
+                *reinterpret_cast<float4 *>(normed_out + base + e0) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4 *>(normed_out + base + e0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+            uint2 q;
+            uint32_t ds;
+            quantize_8_per_lane_q8_1(v, s_mode, &q, &ds);
+            uint8_t *blk = xq + q8_block_index(2 * pr + (lane >> 4), token, n_super, T, order) * Q8_BYTES;
+            reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = q;
+            if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+        }
+        return;
+    }
+    if (vec_out) {
         float4 *row4 = reinterpret_cast<float4 *>(row);
         const float4 *w4 = reinterpret_cast<const float4 *>(weight);
         float4 *out4 = reinterpret_cast<float4 *>(normed_out != nullptr ? normed_out + base : nullptr);
