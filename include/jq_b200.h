@@ -234,6 +234,35 @@ int jq_linear_q4_0_allgather_device(void *stream, const void *d_w, const float *
  * i.e. until the bands of this rank's latest all-gather have arrived from every rank. */
 int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const unsigned *d_epoch);
 
+/* The decode form of the fused all-gather (M <= 2), built for latency instead of flags: every output value
+ * travels as one 8-byte word {fp32 bits, number of its all-gather} in a single store, which arrives whole.
+ * The consumer polls the words it needs until they carry the number it expects: no arrival count, no
+ * release and no acknowledgement round trip lies between a rank's last store and a peer's first use.
+ *   word_peers[q]  : rank q's pair of [M][N_total] buffers of 8-byte words as mapped on this device (zero
+ *                    before the first call); the second buffer starts y_stride_bytes after the first
+ *   d_ticket       : a local 64-bit count, zero before the first call.  Every launch adds 65536 to it; the
+ *                    launch that finds t is all-gather number e = (t >> 16) + 1, tags its words with e and
+ *                    stores into buffer (e & 1).  Layers of a chain share one count.
+ *   d_x            : plain fp32 activations [M][K]; or NULL and
+ *   d_x_words      : this rank's own pair of word buffers whose all-gather number t >> 16 (the one launched
+ *                    just before this call on every rank) is this call's input: row m, activation k is word
+ *                    m * x_row_words + (k / x_seg_len) * x_seg_stride + k % x_seg_len of buffer ((t >> 16) & 1).
+ *                    x_seg_len = K takes the first K words of a row; K / world words from the start of every
+ *                    rank's band make the call depend on all ranks.
+ * A call that consumes words needs no other ordering.  A call with plain d_x that follows other tagged calls
+ * must come after a jq_allgather_tagged_read_device (or a stream synchronisation after one) so that no rank
+ * overwrites a buffer another rank still reads.  All ranks make the same sequence of calls.  Waits are bounded
+ * (JQ_OPT_WAIT_POLL_LIMIT); a wait that runs out sets jq_device_fault() to 2 and the kernel goes on. */
+int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const float *d_x, const void *d_x_words,
+                                           size_t x_stride_bytes, int64_t x_row_words, int64_t x_seg_len,
+                                           int64_t x_seg_stride, int64_t K, int64_t N_local, int64_t M, int s_mode,
+                                           void *const *word_peers, int world, int rank, int64_t n_offset,
+                                           int64_t N_total, size_t y_stride_bytes, unsigned long long *d_ticket);
+/* Waits (bounded) for every word of the all-gather numbered *d_ticket >> 16 in this rank's pair of word
+ * buffers and writes the values as plain fp32 [M][N_total] to d_out. */
+int jq_allgather_tagged_read_device(void *stream, const void *d_words, size_t stride_bytes, int64_t M,
+                                    int64_t N_total, const unsigned long long *d_ticket, float *d_out);
+
 /* No counterpart in the reference.  jq_linear_q4_0_device() without the d_ws argument, for callers
  * that must not allocate device memory and have no spare buffer to lend: an inference server that
  * handed the whole device to its own arena at start-up (a later cudaMalloc fails or fragments),

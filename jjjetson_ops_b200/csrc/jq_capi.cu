@@ -547,6 +547,63 @@ int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const
     return launch_allgather_wait(static_cast<cudaStream_t>(stream), static_cast<const uint32_t *>(d_flags), world, d_epoch);
 }
 
+int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const float *d_x, const void *d_x_words,
+                                           size_t x_stride_bytes, int64_t x_row_words, int64_t x_seg_len, int64_t x_seg_stride,
+                                           int64_t K, int64_t N_local, int64_t M, int s_mode, void *const *word_peers, int world,
+                                           int rank, int64_t n_offset, int64_t N_total, size_t y_stride_bytes,
+                                           unsigned long long *d_ticket) {
+    if (int rc = check_mul_mat_shape(K, N_local, M)) return rc;
+    if (int rc = check_s_mode(s_mode)) return rc;
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return set_error(JQ_ERR_INVALID_ARG, "world must be 1..%d and rank inside it (world=%d rank=%d)", MAX_PEERS, world, rank);
+    if (!word_peers || !d_ticket || !d_w || (d_x == nullptr) == (d_x_words == nullptr))
+        return set_error(JQ_ERR_INVALID_ARG, "null pointer, or not exactly one of d_x and d_x_words");
+    if (n_offset < 0 || n_offset + N_local > N_total) return set_error(JQ_ERR_INVALID_ARG, "band [%lld, %lld) outside N_total = %lld",
+                                                                       (long long)n_offset, (long long)(n_offset + N_local), (long long)N_total);
+    if (M < 1 || N_local < 1 || K < 1) return set_error(JQ_ERR_INVALID_ARG, "empty shape");
+    if (M > 2) return set_error(JQ_ERR_UNSUPPORTED, "the tagged all-gather is the decode form: M <= 2 (M = %lld)", (long long)M);
+    if (K % 256 != 0) return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather needs K %% 256 == 0 (K = %lld)", (long long)K);
+    if (((uintptr_t)d_w & 15u) != 0) return set_error(JQ_ERR_UNSUPPORTED, "the fused all-gather needs 16-byte aligned weights");
+    if (d_x && ((uintptr_t)d_x & 15u) != 0) return set_error(JQ_ERR_ALIGN, "activations must be 16-byte aligned");
+    if ((n_offset & 1) != 0 || (N_total & 1) != 0 || (y_stride_bytes & 15u) != 0)
+        return set_error(JQ_ERR_ALIGN, "band offset and N_total must be even, the buffers 16-byte aligned");
+    GatherArgs ga;
+    for (int q = 0; q < MAX_PEERS; ++q) {
+        ga.y_peer[q] = q < world ? static_cast<float *>(word_peers[q]) : nullptr;
+        if (q < world && (!ga.y_peer[q] || ((uintptr_t)ga.y_peer[q] & 15u) != 0))
+            return set_error(JQ_ERR_INVALID_ARG, "null or misaligned peer pointer %d", q);
+    }
+    if (d_x_words) {
+        if (x_seg_len < 8 || x_seg_len % 8 != 0 || K % x_seg_len != 0 || x_seg_stride < 0 || (x_seg_stride & 1) != 0 ||
+            (x_row_words & 1) != 0 || ((uintptr_t)d_x_words & 15u) != 0 || (x_stride_bytes & 15u) != 0 ||
+            (K / x_seg_len - 1) * x_seg_stride + x_seg_len > x_row_words)
+            return set_error(JQ_ERR_INVALID_ARG, "activation words: segments of %lld every %lld words do not tile K = %lld inside a row of %lld",
+                             (long long)x_seg_len, (long long)x_seg_stride, (long long)K, (long long)x_row_words);
+        ga.x_words = static_cast<const unsigned long long *>(d_x_words);
+        ga.x_stride_bytes = x_stride_bytes;
+        ga.x_row_words = x_row_words;
+        ga.x_seg_len = (int)x_seg_len;
+        ga.x_seg_stride = x_seg_stride;
+    }
+    ga.world = world;
+    ga.rank = rank;
+    ga.n_offset = n_offset;
+    ga.N_total = N_total;
+    ga.y_stride_bytes = y_stride_bytes;
+    ga.ticket = d_ticket;
+    return launch_gemv_dp4a(static_cast<cudaStream_t>(stream), d_w, nullptr, d_x, nullptr, nullptr, K, N_local, M, JQ_ORDER_COL_KSUPER,
+                            s_mode, &ga);
+}
+
+int jq_allgather_tagged_read_device(void *stream, const void *d_words, size_t stride_bytes, int64_t M, int64_t N_total,
+                                    const unsigned long long *d_ticket, float *d_out) {
+    if (!d_words || !d_ticket || !d_out || M < 1 || N_total < 2 || (N_total & 1) != 0 || ((uintptr_t)d_words & 15u) != 0 ||
+        ((uintptr_t)d_out & 7u) != 0 || (stride_bytes & 15u) != 0)
+        return set_error(JQ_ERR_INVALID_ARG, "jq_allgather_tagged_read_device: bad pointer, size or alignment");
+    return launch_allgather_tagged_read(static_cast<cudaStream_t>(stream), static_cast<const unsigned long long *>(d_words), stride_bytes,
+                                        M, N_total, d_ticket, d_out);
+}
+
 // ---- the entry point that allocates nothing ---------------------------------------------------------
 // Scratch for the quantized activations, part of the library image (see include/jq_b200.h).  In host
 // code this name is only a handle for the runtime: the kernels must be given the device address that

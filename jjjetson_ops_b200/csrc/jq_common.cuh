@@ -90,10 +90,26 @@ struct GatherArgs {
     uint64_t y_stride_bytes = 0;     // distance between the two output buffers of a rank
     int wait_previous = 0;           // wait until all flags here have reached *epoch_ptr before reading x
     int *counter = nullptr;          // local int, zero before the first call (the kernel re-zeroes it)
+    // Tagged-word form (M <= 2): an output value travels as one 8-byte word {fp32 bits, number of its all-gather},
+    // the consumer polls the words it needs and no flag, release or acknowledgement is on the path.  y_peer then
+    // holds each rank's pair of [M][N_total] word buffers; flag_peer, epoch_ptr, counter, wait_previous are unused.
+    unsigned long long *ticket = nullptr;         // local 64-bit count, zero before the first call; non-null selects this
+                                                  // form.  Every launch adds 65536 (in shares, one per CTA): the launch
+                                                  // that finds t is all-gather number (t >> 16) + 1.
+    const unsigned long long *x_words = nullptr;  // this rank's pair of word buffers whose latest all-gather (number
+                                                  // t >> 16) is this launch's input, or nullptr: plain fp32 input
+    uint64_t x_stride_bytes = 0;                  // distance between the two buffers of that pair
+    int64_t x_row_words = 0;                      // words per row there (that all-gather's N_total)
+    int x_seg_len = 0;                            // activation k of a row is word (k / x_seg_len) * x_seg_stride +
+    int64_t x_seg_stride = 0;                     // k % x_seg_len of that row (x_seg_len a multiple of 8)
 };
 
 // Waits (bounded) on the stream until all `world` flags have reached *d_epoch.
 int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, const uint32_t *d_epoch);
+// Tagged-word form: waits (bounded) for every word of the all-gather numbered *d_ticket >> 16 in this rank's pair
+// of word buffers and writes the values as plain fp32 [M][N_total].
+int launch_allgather_tagged_read(cudaStream_t st, const unsigned long long *d_words, uint64_t stride_bytes, int64_t M,
+                                 int64_t N_total, const unsigned long long *d_ticket, float *d_out);
 
 // Streaming GEMV family.  d_x_f32 != nullptr fuses the activation quantizer into the prologue
 // (d_xq then receives the quantized blocks in JQ_ORDER_COL_KSUPER order, may be nullptr).

@@ -166,6 +166,37 @@ __device__ __forceinline__ void wait_flags(const uint32_t *flags, int world, uin
     __syncwarp();
 }
 
+// ---- tagged words: {fp32 bits, number of the all-gather} in one 8-byte store, which arrives whole ----------
+__device__ __forceinline__ void st_word(unsigned long long *dst, float v, uint32_t tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+}
+// two neighbouring words (16-byte aligned): x, z their values, y, w their tags
+__device__ __forceinline__ uint4 ld_words2(const unsigned long long *src) {
+    uint4 r;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(src) : "memory");
+    return r;
+}
+
+// Every word of all-gather number *ticket >> 16 -> plain fp32, each thread waiting (bounded) for its own words.
+__global__ void __launch_bounds__(256) allgather_tagged_read_kernel(const unsigned long long *words, uint64_t stride_bytes,
+                                                                    int64_t n_words, const unsigned long long *ticket,
+                                                                    float *out, int *fault, uint32_t limit) {
+    const uint32_t tag = (uint32_t)(*reinterpret_cast<const volatile unsigned long long *>(ticket) >> 16);
+    const unsigned long long *src =
+        reinterpret_cast<const unsigned long long *>(reinterpret_cast<const uint8_t *>(words) + (size_t)(tag & 1u) * stride_bytes);
+    for (int64_t i = 2 * ((int64_t)blockIdx.x * blockDim.x + threadIdx.x); i < n_words; i += 2 * (int64_t)gridDim.x * blockDim.x) {
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        bool ok = false;
+        for (uint32_t spin = 0; spin < limit && !ok; ++spin) {
+            w = ld_words2(src + i);
+            ok = w.y == tag && w.w == tag;
+        }
+        if (!ok && fault != nullptr) atomicExch(fault, 2);
+        *reinterpret_cast<float2 *>(out + i) = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
+    }
+}
+
 __global__ void allgather_wait_kernel(const uint32_t *flags, int world, const uint32_t *epoch_ptr, int *fault,
                                       uint32_t limit) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -332,12 +363,62 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
     }
 }
 
+// A pair of quantized blocks (eight values per lane) to its place in shared memory, and to the workspace by CTA 0.
+__device__ __forceinline__ void store_pair_blocks(const GemvParams &p, uint8_t *xs, int pr, int lane, uint2 qv, uint32_t ds) {
+    const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
+    const int m = idx / p.n_super, ks = idx - m * p.n_super;
+    uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
+    reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
+    if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
+    if (p.xq_out != nullptr && blockIdx.x == 0) {
+        uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
+        reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
+        if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
+    }
+}
+
 template <int NW>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *xs, uint64_t *x_ready, int warp,
-                                                  int lane) {
+                                                  int lane, uint32_t x_tag = 0u) {
     const int total = p.M * p.n_super;
     bool arrived = false;  // this warp has told the producer that its first loads have landed
-    if (p.x_f32 != nullptr && (p.n_super & 1) == 0) {
+    if (p.gather.x_words != nullptr) {
+        // The activations are the output of all-gather number x_tag, arriving as tagged words from every rank:
+        // a lane polls its own eight words until all carry that number (they are the synchronisation: nothing
+        // else is waited for), then the pair of blocks is quantized as below.
+        const GatherArgs &ga = p.gather;
+        const unsigned long long *xw = reinterpret_cast<const unsigned long long *>(
+            reinterpret_cast<const uint8_t *>(ga.x_words) + (size_t)(x_tag & 1u) * ga.x_stride_bytes);
+        const int pairs = total >> 1;
+        for (int pr = warp; pr < pairs; pr += NW) {
+            const int e = pr * (2 * SUPER) + 8 * lane;  // element of the [M][K] activations
+            const int m = e / p.K, k = e - m * p.K;
+            const int seg = k / ga.x_seg_len, j = k - seg * ga.x_seg_len;
+            const unsigned long long *src = xw + (size_t)m * ga.x_row_words + (size_t)seg * ga.x_seg_stride + j;
+            uint4 w[4];
+            bool ok = false;
+            for (uint32_t spin = 0; spin < p.poll_limit && !ok; ++spin) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) w[u] = ld_words2(src + 2 * u);
+                ok = true;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) ok = ok && w[u].y == x_tag && w[u].w == x_tag;
+            }
+            if (!ok && p.fault != nullptr) atomicExch(p.fault, 2);
+            __syncwarp();
+            if (!arrived) {
+                if (lane == 0) mbar_arrive(x_ready);
+                arrived = true;
+                if (threadIdx.x == 0) trace_fine(p, 0);  // warp 0: its words have arrived
+            }
+            const float v[8] = {__uint_as_float(w[0].x), __uint_as_float(w[0].z), __uint_as_float(w[1].x), __uint_as_float(w[1].z),
+                                __uint_as_float(w[2].x), __uint_as_float(w[2].z), __uint_as_float(w[3].x), __uint_as_float(w[3].z)};
+            uint2 qv;
+            uint32_t ds;
+            quantize_8_per_lane_q8_1(v, p.s_mode, &qv, &ds);
+            store_pair_blocks(p, xs, pr, lane, qv, ds);
+        }
+    } else if (p.x_f32 != nullptr && (p.n_super & 1) == 0) {
         // Whole pairs of blocks (K % 256 == 0): warp w takes the pairs w, w + NW, ..., eight values per lane
         // (half the instructions per value of the four-per-lane form below, same bits).  All of a warp's loads
         // are issued before the first pair is quantized.
@@ -375,16 +456,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
                 uint2 qv;
                 uint32_t ds;
                 quantize_8_per_lane_q8_1(v, p.s_mode, &qv, &ds);
-                const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
-                const int m = idx / p.n_super, ks = idx - m * p.n_super;
-                uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-                reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
-                if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
-                if (p.xq_out != nullptr && blockIdx.x == 0) {
-                    uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-                    reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
-                    if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
-                }
+                store_pair_blocks(p, xs, pr, lane, qv, ds);
             }
         }
     } else if (p.x_f32 != nullptr) {
@@ -481,6 +553,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     uint64_t *empty = full + GV_MAX_STAGES;
     uint64_t *x_ready = full + 24;
     uint64_t *x_full = full + 25;
+    unsigned long long *ticket_slot = reinterpret_cast<unsigned long long *>(full + 26);
     float *ybuf = reinterpret_cast<float *>(smem + GV_BAR_BYTES);
     uint8_t *xs = smem + GV_BAR_BYTES + p.y_bytes;
     uint8_t *ring = xs + p.x_bytes;
@@ -494,6 +567,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         mbar_init(x_ready, NW);
         mbar_init(x_full, 1);
         fence_mbar_init();
+        // Tagged all-gather: this launch's number comes from a count that every launch raises by 65536, a share per
+        // CTA.  The next launch in the stream starts only after every CTA of this one has passed the trigger below,
+        // i.e. has its share in: all CTAs of a launch read values in the same 65536-wide window.
+        if (p.gather.ticket != nullptr) *ticket_slot = atomicAdd(p.gather.ticket, (unsigned long long)gather_share());
     }
     __syncthreads();
 
@@ -517,9 +594,17 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     const uint32_t ring_addr = smem_u32(ring);
     const bool tracing = p.trace != nullptr && threadIdx.x == 0;
 
-    griddep_wait();  // activations may come from, and outputs may be read by, the previous kernel
+    // Activations may come from, and outputs may be read by, the previous kernel.  Activations that arrive as
+    // tagged words order themselves: that kernel does not wait for its predecessor before its last instruction.
+    const bool tagged = p.gather.ticket != nullptr;
+    const bool x_tagged = tagged && p.gather.x_words != nullptr;
+    if (!x_tagged) griddep_wait();
     uint32_t gather_epoch = 0;  // number of this all-gather (previous ones finished: *epoch_ptr)
-    if (p.gather.world > 0) {
+    uint32_t x_tag = 0;
+    if (tagged) {
+        x_tag = (uint32_t)(*ticket_slot >> 16);
+        gather_epoch = x_tag + 1u;
+    } else if (p.gather.world > 0) {
         const uint32_t done = *reinterpret_cast<const volatile uint32_t *>(p.gather.epoch_ptr);
         gather_epoch = done + 1;
         if (p.x_copy_bytes == 0 && p.gather.wait_previous && done != 0) {
@@ -535,7 +620,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         if (!mbar_wait_bounded(x_full, 0u, p.fault, p.poll_limit)) return;
         if (threadIdx.x == 0) trace_fine(p, 0);  // the blocks have landed in shared memory
     } else {
-        stage_activations<NW>(p, xs, x_ready, warp, lane);
+        stage_activations<NW>(p, xs, x_ready, warp, lane, x_tag);
     }
     if (threadIdx.x == 0) trace_stamp(p, 4);  // activations staged
 
@@ -665,7 +750,24 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     if (threadIdx.x == 0) trace_stamp(p, 7);  // warp 0 done
     if (threadIdx.x == (NW - 1) * 32) trace_fine(p, 5);  // last consumer warp done
 
-    if (p.gather.world > 0) {
+    if (tagged) {
+        // ---- all-gather epilogue, tagged words: each value and the number of this all-gather in one 8-byte store
+        // to every rank's buffer.  Nothing follows the stores: no flag, no release, nobody waits here.
+        const GatherArgs &ga = p.gather;
+        named_bar_sync(1, NW * 32);  // the band of this CTA is complete in shared memory
+        const int rows_cta = (int)(r_end - r_begin);
+        for (int idx = warp; idx < ga.world * p.M; idx += NW) {
+            const int hop = idx / p.M, m = idx - hop * p.M;
+            const int q = (ga.rank + 1 + hop) % ga.world;  // the ranks start on different peers; the local copy comes last
+            unsigned long long *dst = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ga.y_peer[q]) +
+                                                                             (size_t)(gather_epoch & 1u) * ga.y_stride_bytes) +
+                                      (size_t)m * ga.N_total + ga.n_offset + r_begin;
+            const float *src = ybuf + (size_t)m * p.y_rows;
+            for (int i = lane; i < rows_cta; i += 32) st_word(dst + i, src[i], gather_epoch);
+        }
+        if (threadIdx.x == 0) trace_fine(p, 6);  // warp 0: its stores are issued
+        griddep_wait();  // a launch never ends before the one ahead of it
+    } else if (p.gather.world > 0) {
         // ---- all-gather epilogue: this CTA's rows of the band go to every rank's buffer ----------
         const GatherArgs &ga = p.gather;
         named_bar_sync(1, NW * 32);  // the band of this CTA is complete in shared memory
@@ -1035,6 +1137,18 @@ int launch_allgather_wait(cudaStream_t st, const uint32_t *d_flags, int world, c
     return JQ_OK;
 }
 
+int launch_allgather_tagged_read(cudaStream_t st, const unsigned long long *d_words, uint64_t stride_bytes, int64_t M,
+                                 int64_t N_total, const unsigned long long *d_ticket, float *d_out) {
+    const int64_t n_words = M * N_total;
+    DeviceCaps caps;
+    if (int rc = device_caps(&caps)) return rc;
+    const int grid = (int)max((int64_t)1, min((int64_t)caps.sm_count * 4, (n_words / 2 + 255) / 256));
+    allgather_tagged_read_kernel<<<grid, 256, 0, st>>>(d_words, stride_bytes, n_words, d_ticket, d_out, device_fault_ptr(),
+                                                       wait_poll_limit());
+    JQ_CUDA_TRY(cudaGetLastError());
+    return JQ_OK;
+}
+
 int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const float *d_x_f32, void *d_xq_out,
                      float *d_y, int64_t K, int64_t N, int64_t M, int order, int s_mode, const GatherArgs *gather,
                      const MultiMat *multi) {
@@ -1056,9 +1170,13 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     // kernel's end 0 / 1 / 2 / 3: cfg2 fused, loads by the warps 7.19 / 6.88 / 6.19 / 6.66 us, by bulk copy
     // 7.16 / 7.39 / 7.36 / 7.41 us; cfg2 ready blocks by bulk copy 7.01 / 6.25 / 6.03 / 6.41 us; K = 11008 ready
     // blocks, bulk copy 9.34 / 8.18 / 7.63 / 7.98 us, loads by the warps 10.45 / 9.89 / 8.85 / 8.83 us.
-    if (p.x_f32 == nullptr && (order == JQ_ORDER_COL_KSUPER || M == 1)) p.x_copy_bytes = (uint32_t)(M * p.n_super * Q8_BYTES);
+    const bool x_words = p.gather.ticket != nullptr && p.gather.x_words != nullptr;
+    if (p.x_f32 == nullptr && !x_words && (order == JQ_ORDER_COL_KSUPER || M == 1)) p.x_copy_bytes = (uint32_t)(M * p.n_super * Q8_BYTES);
     p.prefetch_early = option_value(JQ_OPT_STATIC_WEIGHTS) != 0;
     p.early_stages = p.prefetch_early ? 2 : (p.x_copy_bytes != 0 ? 0 : (1 << 30));
+    // activations that arrive as tagged words from the other ranks take microseconds to come: the whole ring is
+    // requested first and lands during that wait
+    if (x_words) p.early_stages = 1 << 30;
     const int nsb = (p.n_super + 31) / 32;
     if (M == 1) {
         switch (nsb) {
@@ -1066,7 +1184,7 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
                 // Quantizing in the prologue is repeated by every CTA: one CTA of 16 warps per SM halves
                 // that cost.  With ready-made Q8_1 input two CTAs of 8 warps per SM overlap better.
                 // (20 consumer warps instead of 16 fit the register file and change nothing: 6.22 us either way)
-                if (p.x_f32 != nullptr) return run_dp4a<1, 1, 16, 1>(st, p, caps);
+                if (p.x_f32 != nullptr || x_words) return run_dp4a<1, 1, 16, 1>(st, p, caps);
                 return run_dp4a<1, 1, 8, 2>(st, p, caps);
             case 2: return run_dp4a<1, 2, 8, 1>(st, p, caps);
             case 3: return run_dp4a<1, 3, 7, 1>(st, p, caps);  // 7 + 1 warps: 255 registers per thread

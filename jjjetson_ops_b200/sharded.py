@@ -168,3 +168,96 @@ class PeerBands:
         with torch.cuda.device(self.device):
             self._capi.peer_free(self.local_ptr)
         self.local_ptr = None
+
+
+class TaggedBands:
+    """Output buffers of the decode form of the fused all-gather (``jq_linear_q4_0_allgather_tagged_device``).
+
+    Every output value travels as one 8-byte word ``{fp32 bits, number of its all-gather}``; the next sharded
+    layer polls the words it needs, so nothing but the flight of the stores lies between one rank's last store
+    and another rank's first use.  Every rank allocates one block of peer-mappable memory with two
+    ``[M, N_total]`` word buffers (used alternately) and maps the blocks of all other ranks.  The all-gathers
+    are numbered by a 64-bit count on the device, which the layers of a chain share (``share_with``).
+    """
+
+    def __init__(self, M: int, N_total: int, device: torch.device, group=None, share_with: "Optional[TaggedBands]" = None):
+        from . import capi
+
+        self._capi = capi
+        self.group = group
+        self.device = device
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("the fused all-gather handles up to 8 ranks")
+        if M > 2:
+            raise ValueError("the tagged form is the decode form: M <= 2")
+        self.M, self.N_total = M, N_total
+        self.y_bytes = (M * N_total * 8 + 255) // 256 * 256
+        with torch.cuda.device(device):
+            self.local_ptr, handle = capi.peer_alloc(2 * self.y_bytes)
+        handles = [handle]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+        self.ptrs = []
+        with torch.cuda.device(device):
+            for q in range(self.world):
+                self.ptrs.append(self.local_ptr if q == self.rank else capi.peer_open(handles[q]))
+        self.ticket = torch.zeros(1, dtype=torch.int64, device=device) if share_with is None else share_with.ticket
+        self._out: Optional[torch.Tensor] = None
+        if self.world > 1:
+            dist.barrier(group=group)  # everyone has mapped everyone before the first store
+
+    def linear(self, w_shard: torch.Tensor, K: int, n_offset: int, N_local: int, x: Optional[torch.Tensor] = None,
+               source: "Optional[TaggedBands]" = None, seg_len: Optional[int] = None, seg_stride: int = 0,
+               s_mode: Optional[int] = None) -> None:
+        """Queue one fused step.  The activations are the plain tensor ``x``, or the latest all-gather of
+        ``source`` (the one queued just before this call): activation ``k`` is word
+        ``(k // seg_len) * seg_stride + k % seg_len`` of its row (``seg_len`` defaults to ``K``: the first
+        ``K`` words)."""
+        capi = self._capi
+        if (x is None) == (source is None):
+            raise ValueError("exactly one of x and source")
+        if x is not None and tuple(x.shape) != (self.M, K):
+            raise ValueError("x must be [%d, %d]" % (self.M, K))
+        if source is not None and source.M != self.M:
+            raise ValueError("the source all-gather has a different M")
+        capi.linear_q4_0_allgather_tagged(
+            w_shard, x, 0 if source is None else source.local_ptr, 0 if source is None else source.y_bytes,
+            0 if source is None else source.N_total, K if seg_len is None else seg_len, seg_stride, K, N_local, self.M,
+            capi.S_D_SUM_Q if s_mode is None else s_mode, list(self.ptrs), self.world, self.rank, n_offset, self.N_total,
+            self.y_bytes, self.ticket)
+
+    def read(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Queue (on the current stream) a wait for every word of the latest all-gather, which must be this
+        object's, and their conversion to a plain fp32 ``[M, N_total]`` tensor."""
+        if out is None:
+            if self._out is None:
+                self._out = torch.empty((self.M, self.N_total), dtype=torch.float32, device=self.device)
+            out = self._out
+        self._capi.allgather_tagged_read(self.device, self.local_ptr, self.y_bytes, self.M, self.N_total, self.ticket, out)
+        return out
+
+    def close(self) -> None:
+        if self.local_ptr is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody is still storing into anybody
+        with torch.cuda.device(self.device):
+            for q, p in enumerate(self.ptrs):
+                if q != self.rank:
+                    self._capi.peer_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            self._capi.peer_free(self.local_ptr)
+        self.local_ptr = None
+
+
+def segments_of(gathered: torch.Tensor, K: int, seg_len: int, seg_stride: int) -> torch.Tensor:
+    """The ``[M, K]`` activations that a layer reading ``gathered`` (``[M, N_total]``) with
+    (``seg_len``, ``seg_stride``) sees: ``K / seg_len`` runs of ``seg_len`` columns, ``seg_stride`` apart."""
+    parts = [gathered[:, q * seg_stride: q * seg_stride + seg_len] for q in range(K // seg_len)]
+    return torch.cat(parts, dim=1).contiguous()

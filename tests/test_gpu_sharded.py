@@ -99,6 +99,77 @@ def test_bounded_wait_gives_up_and_reports(native_lib, oracle, cuda_device):
     assert c.device_fault() == 0
 
 
+@pytest.mark.parametrize("K,N,M,K2,seg", [(4096, 11008, 1, 4096, None), (2048, 4096, 2, 1024, 256), (4096, 2080, 1, 2048, 512),
+                                          (8192, 8192, 1, 8192, None)])
+def test_tagged_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M, K2, seg):
+    """The decode form on one GPU (world = 1: ticket, tagged stores, polling loads and the reader all run,
+    with itself as the only peer).  Layer 1 takes plain activations; layer 2 takes its activations from
+    layer 1's tagged words (first K2 words, or runs of ``seg`` words spread over the row), three passes, so
+    that both buffers of each pair and increasing tags are used."""
+    import torch
+
+    from jjjetson_ops_b200.sharded import TaggedBands, segments_of
+
+    c = native_lib
+    rng = np.random.default_rng(K + N + M)
+    N2 = 512 + 32
+    wq1 = oracle.quantize_q4_0((rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32))
+    wq2 = oracle.quantize_q4_0((rng.standard_normal((N2, K2), dtype=np.float32) * np.float32(0.02)).astype(np.float32))
+    d_w1, d_w2 = torch.from_numpy(wq1).to(cuda_device), torch.from_numpy(wq2).to(cuda_device)
+    seg_len = K2 if seg is None else seg
+    seg_stride = 0 if seg is None else (N - seg_len) // (K2 // seg_len - 1) // 32 * 32
+    a = TaggedBands(M, N, cuda_device)
+    b = TaggedBands(M, N2, cuda_device, share_with=a)
+    try:
+        for step in range(3):
+            x = rng.standard_normal((M, K), dtype=np.float32)
+            a.linear(d_w1, K, 0, N, x=torch.from_numpy(x).to(cuda_device))
+            y1 = a.read().cpu().numpy()
+            xq = oracle.quantize_q8_1(x, oracle.ORDER_COL_KSUPER, oracle.S_D_SUM_Q)
+            assert oracle.err_max_rel(y1, oracle.mul_mat_ref(wq1, xq, K, N, M)) <= 1e-5
+            b.linear(d_w2, K2, 0, N2, source=a, seg_len=seg_len, seg_stride=seg_stride)
+            y2 = b.read().cpu().numpy()
+            x2 = segments_of(torch.from_numpy(y1), K2, seg_len, seg_stride).numpy()
+            xq2 = oracle.quantize_q8_1(x2, oracle.ORDER_COL_KSUPER, oracle.S_D_SUM_Q)
+            assert oracle.err_max_rel(y2, oracle.mul_mat_ref(wq2, xq2, K2, N2, M)) <= 1e-5
+            # the same bits as the single-GPU entry on the same activations
+            y2_single = c.linear_q4_0(d_w2, torch.from_numpy(x2).to(cuda_device), N2).cpu().numpy()
+            assert np.array_equal(y2, y2_single)
+            # the same pair back to back: nothing orders the second layer after the first but the words
+            a.linear(d_w1, K, 0, N, x=torch.from_numpy(x).to(cuda_device))
+            b.linear(d_w2, K2, 0, N2, source=a, seg_len=seg_len, seg_stride=seg_stride)
+            assert np.array_equal(b.read().cpu().numpy(), y2)
+            assert int(a.ticket.item()) == 4 * (step + 1) << 16
+        assert c.device_fault() == 0
+    finally:
+        b.close()
+        a.close()
+
+
+def test_tagged_read_gives_up_and_reports(native_lib, cuda_device):
+    """Words that never arrive: the count says one all-gather was launched, the buffers are still zero.  With a
+    limit of a few thousand polls the reader must return by itself and report through the fault word."""
+    import torch
+
+    from jjjetson_ops_b200.sharded import TaggedBands
+
+    c = native_lib
+    assert c.device_fault() == 0
+    bands = TaggedBands(1, 64, cuda_device)
+    c.set_option(c.OPT_WAIT_POLL_LIMIT, 2048)
+    try:
+        bands.ticket.fill_(1 << 16)
+        bands.read()
+        torch.cuda.synchronize()
+        v = c.ctypes.c_int(0)
+        rc = c.lib().jq_device_fault(1, c.ctypes.byref(v))
+        assert rc == c.ERR_TIMEOUT and v.value == 2, (rc, v.value, c.last_error())
+    finally:
+        c.set_option(c.OPT_WAIT_POLL_LIMIT, 0)
+        bands.close()
+    assert c.device_fault() == 0
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -152,6 +223,36 @@ def _two_rank_worker(rank: int, world: int, port: int, q):
             xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
             ok = ok and O.err_max_rel(y, O.mul_mat_ref(wq2, xq, K, N2, M2)) <= 1e-5
         bands2.close()
+        # the decode form: tagged words, a chain of two sharded layers, the second fed by the first one's words
+        # (K3 / world words from every rank's band), with no wait between them but the words themselves
+        from jjjetson_ops_b200.sharded import TaggedBands, segments_of
+
+        K3, N3 = 2048, 1024 + 64
+        w3 = (rng.standard_normal((N3, K3), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        wq3 = O.quantize_q4_0(w3)
+        b3, e3 = synth.shard_rows(N3, world, rank)
+        d_w3 = torch.from_numpy(np.ascontiguousarray(wq3[b3:e3])).to(dev)
+        ta = TaggedBands(1, N, dev)
+        tb = TaggedBands(1, N3, dev, share_with=ta)
+        seg_len, seg_stride = K3 // world, synth.shard_rows(N, world, 1)[0]
+        for step in range(4):
+            x = rng.standard_normal((1, K), dtype=np.float32)
+            d_x = torch.from_numpy(x).to(dev)
+            ta.linear(d_w, K, b, e - b, x=d_x)
+            y1 = ta.read().cpu().numpy()  # the first layer's gathered output, to build the expectation from
+            tb.linear(d_w3, K3, b3, e3 - b3, source=ta, seg_len=seg_len, seg_stride=seg_stride)
+            y3 = tb.read().cpu().numpy()
+            xq = O.quantize_q8_1(x, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+            ok = ok and O.err_max_rel(y1, O.mul_mat_ref(wq, xq, K, N, 1)) <= 1e-5
+            x3 = segments_of(torch.from_numpy(y1), K3, seg_len, seg_stride).numpy()
+            xq3 = O.quantize_q8_1(x3, O.ORDER_COL_KSUPER, O.S_D_SUM_Q)
+            ok = ok and O.err_max_rel(y3, O.mul_mat_ref(wq3, xq3, K3, N3, 1)) <= 1e-5
+            # the same pair back to back: nothing orders the second layer after the first but the words
+            ta.linear(d_w, K, b, e - b, x=d_x)
+            tb.linear(d_w3, K3, b3, e3 - b3, source=ta, seg_len=seg_len, seg_stride=seg_stride)
+            ok = ok and np.array_equal(tb.read().cpu().numpy(), y3)
+        tb.close()
+        ta.close()
         ok = ok and capi.device_fault() == 0
         q.put((rank, bool(ok)))
     except Exception as ex:
