@@ -206,22 +206,29 @@ def workload_config(K, N, M, world, shape="cfg2"):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
-def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None):
+def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None, preamble=None):
     """Times exactly `steps` calls of step_fn(i) with CUDA events; the calls are replayed from
     CUDA graphs of up to GRAPH_BLOCK steps each.  When one graph holds all the steps, the two events are recorded
-    inside it, directly around the steps: they then bracket the device time of the K steps and not the launch
-    latency of the graph itself (about 10 us on the device, which at K = 20 steps of 7 us is 7 % of the region)."""
+    inside it, directly around the steps (and `finalize`, e.g. the wait for the last step's bands from every rank):
+    they then bracket the device time of the K steps and not the launch latency of the graph itself (about 10 us on
+    the device, which at K = 20 steps of 7 us is 7 % of the region).  `preamble` is queued, untimed, ahead of the
+    timed steps (a chain of steps that feed one another needs a first step with an input of its own)."""
     stream = torch.cuda.Stream()
+    side = torch.cuda.Stream()
     with torch.cuda.stream(stream):
+        if preamble is not None:
+            preamble()
         for i in range(max(warmup, 3)):
             step_fn(i)
+        if finalize is not None:
+            finalize()
     stream.synchronize()
 
     graphs = []  # (graph, count)
     used_graph = True
     inner_events = None
+    single = steps <= GRAPH_BLOCK
     try:
-        single = steps <= GRAPH_BLOCK and finalize is None
         if single:
             try:
                 inner_events = (torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True))
@@ -237,15 +244,30 @@ def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None):
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=stream):
                     if inner_events is not None:
-                        inner_events[0].record(stream)
+                        if preamble is not None:
+                            preamble()
+                            # The first event is recorded on a branch of the capture: it completes when the last
+                            # untimed kernel does, without standing between that kernel and the first timed one
+                            # (an event node in the chain costs the first timed steps their dependent launch, and a
+                            # chain of ranks that feed one another needs a dozen steps to settle again).
+                            side.wait_stream(stream)
+                            inner_events[0].record(side)
+                        else:
+                            inner_events[0].record(stream)
                     for i in range(n):
                         step_fn(i)
                     if inner_events is not None:
+                        if finalize is not None:
+                            finalize()
+                        if preamble is not None:
+                            stream.wait_stream(side)
                         inner_events[1].record(stream)
                 graphs.append((g, n))
             done += n
         with torch.cuda.stream(stream):
             graphs[0][0].replay()  # one untimed replay: graph upload
+            if inner_events is None and finalize is not None:
+                finalize()
         stream.synchronize()
     except Exception as ex:  # capture refused (e.g. by a collective): time plain launches
         used_graph = False
@@ -258,6 +280,8 @@ def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
+        if inner_events is None and preamble is not None:
+            preamble()
         start.record(stream)
         if used_graph:
             for g, _ in graphs:
@@ -265,7 +289,7 @@ def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None):
         else:
             for i in range(steps):
                 step_fn(i)
-        if finalize is not None:
+        if inner_events is None and finalize is not None:
             finalize()  # e.g. wait for the last step's bands from every rank
         end.record(stream)
     stream.synchronize()
@@ -333,12 +357,26 @@ def run_ours(args) -> None:
         # prefill batches: the GEMM's peer-store epilogue was measured level with NCCL (8 GPUs, cfg4 M=2048: 960 us
         # against 950 us), so the plain all-gather stays the default there; --collective fused still selects it
         collective = args.collective if args.collective is not None else ("fused" if M <= 2 else "nccl")
-    if collective == "fused":
+    tagged = None
+    if collective == "fused" and M <= 2:
+        # decode: the band travels as tagged words, and every step takes its activations from the gathered output
+        # of the step before it (runs of 8 words spread evenly over the whole row), so a step cannot begin before
+        # every CTA of every rank has delivered its part of the previous one: a chain of dependent sharded layers
+        from jjjetson_ops_b200.sharded import TaggedBands, segments_of
+
+        tagged = TaggedBands(M, N * world, dev)
+        x_stride = (N * world // (K // 8)) // 2 * 2  # runs of 8 words spread evenly over the whole gathered row
+        collective = ("fused, tagged words; each step's activations are read from the previous step's gathered output "
+                      "(8 words out of every %d: every CTA of every rank feeds every CTA of the next step)" % x_stride)
+    elif collective in ("fused", "fused_flags"):
         from jjjetson_ops_b200.sharded import PeerBands
 
         bands = PeerBands(M, N * world, dev)
 
     def step(i):
+        if tagged is not None:
+            tagged.linear(weights[i % R], K, rank * N, N, source=tagged, seg_len=8, seg_stride=x_stride)
+            return
         if bands is not None:
             # multiply + all-gather in one kernel: the band goes straight into every rank's buffer
             bands.linear(weights[i % R], d_x, d_ws, rank * N, N)
@@ -347,10 +385,22 @@ def run_ours(args) -> None:
         if gather is not None:
             dist.all_gather_into_tensor(gather, d_y)
 
+    def preamble():
+        # Untimed steps ahead of the timed ones.  The processes replay their graphs some tens of microseconds apart:
+        # a step that needs every rank's previous output makes the early ranks wait here, not inside the timed region.
+        if tagged is not None:
+            tagged.linear(weights[R - 1], K, rank * N, N, x=d_x)  # the chain's first step has activations of its own
+            step(R - 1)
+        else:
+            step(R - 2)
+            step(R - 1)
+
     sampler = ClockSampler(local)
     sampler.start()
-    seconds, used_graph = time_graph_steps(torch, step, args.steps, args.warmup, barrier,
-                                           finalize=bands.wait if bands is not None else None)
+    seconds, used_graph = time_graph_steps(
+        torch, step, args.steps, args.warmup, barrier,
+        finalize=tagged.read if tagged is not None else (bands.wait if bands is not None else None),
+        preamble=preamble if world > 1 else None)
     sampler.stop()
     if dist is not None:
         t = torch.tensor([seconds], dtype=torch.float64, device=dev)
@@ -362,12 +412,22 @@ def run_ours(args) -> None:
     gather_verified = None
     sharded_extras = None
     if world > 1:
-        def expected_band(q):
+        def expected_band(q, x_in=None, copy=0):
             # cfg2: every rank holds the same weights; cfg4: rank q's shard is regenerated from its seed
-            wq_q = weights[0] if args.shape == "cfg2" else cfg4_shard(torch, capi, dev, K, N, 3 + q)
-            return capi.linear_q4_0(wq_q, d_x, N, capi.S_D_SUM_Q)
+            wq_q = weights[copy] if args.shape == "cfg2" else torch.roll(cfg4_shard(torch, capi, dev, K, N, 3 + q), shifts=32 * copy, dims=0)
+            return capi.linear_q4_0(wq_q.contiguous(), d_x if x_in is None else x_in, N, capi.S_D_SUM_Q)
 
-        if bands is not None:
+        x_check = d_x
+        if tagged is not None:
+            # a step on plain activations, then a step fed by its words: both gathered outputs are checked
+            tagged.linear(weights[0], K, rank * N, N, x=d_x)
+            first = tagged.read().clone()
+            step(1)
+            got = tagged.read()
+            torch.cuda.synchronize()
+            first_ok = all(bool(torch.equal(first[:, q * N:(q + 1) * N], expected_band(q))) for q in range(world))
+            x_check = segments_of(first, K, 8, x_stride)
+        elif bands is not None:
             bands.linear(weights[0], d_x, d_ws, rank * N, N)
             bands.wait()
             torch.cuda.synchronize()
@@ -380,6 +440,8 @@ def run_ours(args) -> None:
         if bands is not None and M > 2:
             # the fused epilogue belongs to the exact-integer GEMM, the single-GPU entry takes the fp16-operand GEMM
             ok = all(float((got[:, q * N:(q + 1) * N] - expected_band(q)).abs().max()) <= 1e-3 * float(got.abs().max()) for q in range(world))
+        elif tagged is not None:
+            ok = first_ok and all(bool(torch.equal(got[:, q * N:(q + 1) * N], expected_band(q, x_check, 1 % R))) for q in range(world))
         else:
             ok = all(bool(torch.equal(got[:, q * N:(q + 1) * N], expected_band(q))) for q in range(world))
         fault = max(fault, capi.device_fault())
@@ -392,12 +454,14 @@ def run_ours(args) -> None:
     e2e = None
     if world > 1:
         e2e = measure_e2e_sharded(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world, rank, bands, gather,
-                                  d_x, d_ws, d_y)
+                                  d_x, d_ws, d_y, tagged)
     elif rank == 0:
         e2e = measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world)
 
     if bands is not None:
         bands.close()
+    if tagged is not None:
+        tagged.close()
     if world > 1 and not args.no_extras and args.shape == "cfg2":
         del weights, wq0
         torch.cuda.empty_cache()
@@ -453,22 +517,24 @@ def run_ours(args) -> None:
 
 
 def cfg4_shard(torch, capi, dev, K, N, seed):
-    """N rows of random nibbles with the scale 2^-7 everywhere: a stand-in for a shard of quantized N(0, 0.015)
-    weights (timing does not depend on the values), reproducible on any rank from its seed."""
+    """N rows of random nibbles with the scale 2^-9 everywhere: a stand-in for a shard of quantized N(0, 0.015)
+    weights (timing does not depend on the values), reproducible on any rank from its seed.  With this scale a row of
+    K = 8192 has a gain of about 0.8, so a long chain of steps that feed one another stays inside the fp32 range."""
     rng = np.random.default_rng(seed)
     w = torch.from_numpy(rng.integers(0, 256, size=capi.q4_0_bytes(N, K), dtype=np.uint8)).to(dev).view(N, -1)
     blk = w.view(N, K // 32, 18)
     blk[:, :, 0] = 0
-    blk[:, :, 1] = 0x20
+    blk[:, :, 1] = 0x18
     return w
 
 
 def device_random_q4_0(torch, dev, N, K, gen):
-    """Random Q4_0 rows generated on the device (finite scales), for shapes whose values are never checked."""
+    """Random Q4_0 rows generated on the device with the scale 2^-8 everywhere (a gain of 1.2 per projection of
+    K = 4096, 1.9 at K = 11008: forty passes of a chain that feeds itself stay finite)."""
     w = torch.randint(0, 256, (N, K // 32 * 18), dtype=torch.uint8, device=dev, generator=gen)
     blk = w.view(N, K // 32, 18)
     blk[:, :, 0] = 0
-    blk[:, :, 1] = 0x20
+    blk[:, :, 1] = 0x1C
     return w
 
 
@@ -535,7 +601,8 @@ def measure_e2e(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, 
     }
 
 
-def measure_e2e_sharded(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world, rank, bands, gather, d_x, d_ws, d_y):
+def measure_e2e_sharded(torch, capi, weights, x_host, K, N, M, alg, args, dev, barrier, dist, world, rank, bands, gather, d_x, d_ws, d_y,
+                        tagged=None):
     """End to end on N > 1 ranks: every step copies the activations from pinned host memory to the device, runs this
     rank's quantize + multiply with the all-gather (fused or NCCL, as the headline), waits for all bands and copies the
     gathered [M, N_total] output back to pinned host memory; wall clock per rank, maximum over ranks."""
@@ -547,7 +614,10 @@ def measure_e2e_sharded(torch, capi, weights, x_host, K, N, M, alg, args, dev, b
 
     def one(i):
         d_x.copy_(x_pin, non_blocking=True)
-        if bands is not None:
+        if tagged is not None:
+            tagged.linear(weights[i % R], K, rank * N, N, x=d_x)
+            y_pin.copy_(tagged.read(), non_blocking=True)  # waits on the device for every rank's words
+        elif bands is not None:
             bands.linear(weights[i % R], d_x, d_ws, rank * N, N)
             bands.wait()
             stream.synchronize()                      # the device-side step counter picks the buffer
@@ -572,8 +642,9 @@ def measure_e2e_sharded(torch, capi, weights, x_host, K, N, M, alg, args, dev, b
     return {
         "value": alg * world * steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": int(x_pin.numel() * 4),
         "d2h_bytes_per_step": int(y_pin.numel() * 4), "steps": steps, "ms_per_step": dt / steps * 1e3,
-        "api": "per rank: pinned host x -> device, jq_linear_q4_0_allgather_device (sharded multiply, all-gather inside) or "
-               "jq_linear_q4_0_device + NCCL all-gather, wait for all bands, gathered [M, N_total] -> pinned host; synchronous",
+        "api": "per rank: pinned host x -> device, jq_linear_q4_0_allgather_tagged_device (M <= 2) or jq_linear_q4_0_allgather_device "
+               "(sharded multiply, all-gather inside) or jq_linear_q4_0_device + NCCL all-gather, wait for all bands, gathered "
+               "[M, N_total] -> pinned host; synchronous",
     }
 
 
@@ -581,7 +652,7 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
     """The sharded configurations on `world` GPUs (strong scaling): configuration 4 (K = 8192, N = 28672 split along N)
     at M = 1 and M = 2048, and the configuration-5 chain at M = 1 with every projection split along N.  Every gathered
     output is checked on every rank against the bands recomputed through the single-GPU entry."""
-    from jjjetson_ops_b200.sharded import PeerBands
+    from jjjetson_ops_b200.sharded import PeerBands, TaggedBands, segments_of
 
     out = {}
     gen = torch.Generator(device=dev)
@@ -632,10 +703,16 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
             capi.linear_q4_0(shards[i % R], x, N, capi.S_D_SUM_Q, ws=ws, out=y)
             dist.all_gather_into_tensor(gather, y)
 
-        sec, _ = time_graph_steps(torch, step_nccl, steps, 3, barrier)
+        sec, _ = time_graph_steps(torch, step_nccl, steps, 3, barrier, preamble=lambda: step_nccl(R - 1))
         finish("nccl_gather", sec, steps)
         bands = PeerBands(M, n_total, dev)
-        sec, _ = time_graph_steps(torch, lambda i: bands.linear(shards[i % R], x, ws, rank * N, N), steps, 3, barrier, finalize=bands.wait)
+
+        def step_fused(i):
+            bands.linear(shards[i % R], x, ws, rank * N, N)
+
+        # (untimed steps ahead of the timed ones absorb the skew between the processes' graph launches)
+        sec, _ = time_graph_steps(torch, step_fused, steps, 3, barrier, finalize=bands.wait,
+                                  preamble=lambda: (step_fused(R - 2), step_fused(R - 1)))
         finish("fused_gather", sec, steps)
         # values: one more fused step and one more NCCL step, every band against the single-GPU entry
         bands.linear(shards[0], x, ws, rank * N, N)
@@ -655,6 +732,31 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
                 err = float((fused_out[:, q * N:(q + 1) * N] - want).abs().max() / want.abs().max())
                 ok = ok and err <= 1e-3
             del wq_q, want
+        if M <= 2:
+            # the decode form: tagged words, every step fed by the gathered output of the step before it
+            tb = TaggedBands(M, n_total, dev)
+            seg, seg_stride = 8, (n_total // (K // 8)) // 2 * 2
+            def step_tagged(i):
+                tb.linear(shards[i % R], K, rank * N, N, source=tb, seg_len=seg, seg_stride=seg_stride)
+
+            sec, _ = time_graph_steps(torch, step_tagged, steps, 3, barrier, finalize=tb.read,
+                                      preamble=lambda: (tb.linear(shards[R - 1], K, rank * N, N, x=x), step_tagged(R - 1)))
+            finish("tagged_gather", sec, steps)
+            tb.linear(shards[0], K, rank * N, N, x=x)
+            first = tb.read().clone()
+            tb.linear(shards[1], K, rank * N, N, source=tb, seg_len=seg, seg_stride=seg_stride)
+            second = tb.read()
+            torch.cuda.synchronize()
+            x2 = segments_of(first, K, seg, seg_stride)
+            for q in range(world):
+                wq_q = w0 if q == rank else cfg4_shard(torch, capi, dev, K, N, 3 + q)
+                ok = ok and bool(torch.equal(first[:, q * N:(q + 1) * N], capi.linear_q4_0(wq_q, x, N, capi.S_D_SUM_Q)))
+                rolled = torch.roll(wq_q, shifts=32, dims=0).contiguous()
+                ok = ok and bool(torch.equal(second[:, q * N:(q + 1) * N], capi.linear_q4_0(rolled, x2, N, capi.S_D_SUM_Q)))
+                del wq_q, rolled
+            tb.close()
+            rec["tagged_gather_note"] = ("each step reads its activations (8 words out of every 28 of the whole row) from the previous "
+                                         "step's gathered output; fused_gather is the count-and-release form on fixed activations")
         rec["gather_verified"] = all_ok(ok)
         rec["kernels"] = ("fused quantize + dp4a GEMV, peer-store all-gather in its epilogue" if M == 1 else
                           "compute_only / nccl_gather: quantize + fp16-operand tcgen05 GEMM (the automatic choice); fused_gather: "
@@ -699,7 +801,7 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
         chain_pass(2 * i + 1)
 
     steps = 20
-    sec, _ = time_graph_steps(torch, chain_two, steps, 3, barrier, finalize=chain[4].wait)
+    sec, _ = time_graph_steps(torch, chain_two, steps, 3, barrier, finalize=chain[4].wait, preamble=lambda: chain_two(R // 2 - 1))
     t = reduce_max(sec) / (2 * steps)
     alg = sum(synth.algorithmic_bytes(k, n // world, M) for _, k, n in shapes)
     # values: the last pass's down projection and the o projection's input chain are checked band by band
@@ -725,6 +827,68 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
                         "sums of all five gathered buffers equal on every rank",
     }
     for c in reversed(chain):
+        c.close()
+
+    # ---- the same chain in the decode form: tagged words, each projection fed by the words of the one before it ----
+    # qkv <- down of the previous pass (4096 words), o <- qkv (8 words out of every 24 of the row), gate and up <- o,
+    # down <- gate (11008 words, standing in for the synthetic tensor: values do not change the timing).
+    tch = []
+    for _, k, n in shapes:
+        tch.append(TaggedBands(M, n, dev, share_with=tch[0] if tch else None))
+    feeds = [4, 0, 1, 1, 2]  # index of the projection whose gathered output feeds projection j
+    backs = [0, 0, 0, 1, 1]  # ... which was queued this many all-gathers before the one just ahead of projection j
+
+    def tagged_layer(j, w, source_words=True, x=None):
+        _, k, n = shapes[j]
+        src = tch[feeds[j]]
+        if source_words:
+            tch[j].linear(w, k, rank * (n // world), n // world, source=src, seg_len=8, seg_stride=(src.N_total // (k // 8)) // 2 * 2,
+                          back=backs[j])
+        else:
+            tch[j].linear(w, k, rank * (n // world), n // world, x=x)
+
+    def tagged_pass(i):
+        w = layers[i % R]
+        for j in range(5):
+            tagged_layer(j, w[j])
+
+    def tagged_two(i):
+        tagged_pass(2 * i)
+        tagged_pass(2 * i + 1)
+
+    sec, _ = time_graph_steps(torch, tagged_two, steps, 3, barrier, finalize=tch[4].read,
+                              preamble=lambda: (tagged_layer(4, layers[0][4], source_words=False, x=xdown), tagged_two(R // 2 - 1)))
+    t = reduce_max(sec) / (2 * steps)
+    # values: one more pass with a read after every projection; this rank's band of each against the single-GPU entry
+    # on the activations the projection was given, and a checksum of every gathered output across the ranks
+    ok = True
+    wl = layers[0]
+    outs = [None] * 5
+    outs[4] = tch[4].read().clone()
+    sums = []
+    for j in range(5):
+        _, k, n = shapes[j]
+        src = outs[feeds[j]]
+        x_in = segments_of(src, k, 8, (src.shape[1] // (k // 8)) // 2 * 2)
+        tagged_layer(j, wl[j])
+        outs[j] = tch[j].read().clone()
+        want = capi.linear_q4_0(wl[j], x_in, n // world, capi.S_D_SUM_Q)
+        ok = ok and bool(torch.equal(outs[j][:, rank * (n // world):(rank + 1) * (n // world)], want))
+        sums.append(outs[j].double().sum())
+    sums = torch.stack(sums)
+    lo, hi = sums.clone(), sums.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    ok = ok and bool(torch.equal(lo, hi)) and bool(torch.isfinite(sums).all())
+    out["cfg5_chain_M1_sharded_tagged"] = {
+        "us": t * 1e6, "GB/s_per_gpu": alg / t / 1e9, "frac_hbm_per_gpu": alg / t / 1e9 / peaks["hbm_gbs"],
+        "launches_per_pass": "5 fused multiply + all-gather kernels in the tagged-word form; each polls the words of the projection "
+                             "that feeds it (qkv <- down of the pass before, o <- qkv, gate and up <- o, down <- gate)",
+        "gather_verified": all_ok(ok),
+        "verified_how": "one more pass with a read after every projection: this rank's band of each recomputed through the single-GPU "
+                        "entry on the same activations (bit-equal); sums of all five gathered outputs equal on every rank",
+    }
+    for c in reversed(tch):
         c.close()
     fault = capi.device_fault()
     out["device_fault_max"] = int(reduce_max(float(fault)))
@@ -1231,7 +1395,7 @@ def main() -> None:
     ap.add_argument("--shape", choices=["cfg2", "cfg4"], default="cfg2",
                     help="cfg2 (default): the headline shape per GPU, weak scaling; cfg4: K=8192, N=28672 split along N over "
                          "the GPUs, strong scaling (a secondary measurement, implies --no-extras)")
-    ap.add_argument("--collective", choices=["fused", "nccl"], default=None,
+    ap.add_argument("--collective", choices=["fused", "fused_flags", "nccl"], default=None,
                     help="N > 1: all-gather fused into the multiply kernel (peer stores) or a separate NCCL all-gather")
     ap.add_argument("--no-overlap", action="store_true",
                     help="do not let a step's weight stream start before the previous step has finished")

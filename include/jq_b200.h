@@ -244,9 +244,10 @@ int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const
  *                    launch that finds t is all-gather number e = (t >> 16) + 1, tags its words with e and
  *                    stores into buffer (e & 1).  Layers of a chain share one count.
  *   d_x            : plain fp32 activations [M][K]; or NULL and
- *   d_x_words      : this rank's own pair of word buffers whose all-gather number t >> 16 (the one launched
- *                    just before this call on every rank) is this call's input: row m, activation k is word
- *                    m * x_row_words + (k / x_seg_len) * x_seg_stride + k % x_seg_len of buffer ((t >> 16) & 1).
+ *   d_x_words      : this rank's own pair of word buffers whose all-gather number g = (t >> 16) - x_back is
+ *                    this call's input (x_back = 0: the one launched just before this call, 1: the one before
+ *                    that, e.g. the second of two projections fed by the same output): row m, activation k is
+ *                    word m * x_row_words + (k / x_seg_len) * x_seg_stride + k % x_seg_len of buffer (g & 1).
  *                    x_seg_len = K takes the first K words of a row; K / world words from the start of every
  *                    rank's band make the call depend on all ranks.
  * A call that consumes words needs no other ordering.  A call with plain d_x that follows other tagged calls
@@ -255,7 +256,7 @@ int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const
  * (JQ_OPT_WAIT_POLL_LIMIT); a wait that runs out sets jq_device_fault() to 2 and the kernel goes on. */
 int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const float *d_x, const void *d_x_words,
                                            size_t x_stride_bytes, int64_t x_row_words, int64_t x_seg_len,
-                                           int64_t x_seg_stride, int64_t K, int64_t N_local, int64_t M, int s_mode,
+                                           int64_t x_seg_stride, int x_back, int64_t K, int64_t N_local, int64_t M, int s_mode,
                                            void *const *word_peers, int world, int rank, int64_t n_offset,
                                            int64_t N_total, size_t y_stride_bytes, unsigned long long *d_ticket);
 /* Waits (bounded) for every word of the all-gather numbered *d_ticket >> 16 in this rank's pair of word

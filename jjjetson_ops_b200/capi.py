@@ -77,7 +77,7 @@ _SIGS = {
     "jq_linear_q4_0_allgather_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci, ctypes.POINTER(_vp),
                                               ctypes.POINTER(_vp), _ci, _ci, _i64, _i64, _sz, _ci, _vp, _vp]),
     "jq_allgather_wait_device": (_ci, [_vp, _vp, _ci, _vp]),
-    "jq_linear_q4_0_allgather_tagged_device": (_ci, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _i64, _i64, _i64, _ci,
+    "jq_linear_q4_0_allgather_tagged_device": (_ci, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _ci, _i64, _i64, _i64, _ci,
                                                      ctypes.POINTER(_vp), _ci, _ci, _i64, _i64, _sz, _vp]),
     "jq_allgather_tagged_read_device": (_ci, [_vp, _vp, _sz, _i64, _i64, _vp, _vp]),
     "jq_linear_q4_0_device_noalloc": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
@@ -317,7 +317,7 @@ def allgather_wait(device: torch.device, flags_ptr: int, world: int, epoch: torc
 
 
 def linear_q4_0_allgather_tagged(w: torch.Tensor, x: Optional[torch.Tensor], x_words_ptr: int, x_stride_bytes: int,
-                                 x_row_words: int, x_seg_len: int, x_seg_stride: int, K: int, N_local: int, M: int,
+                                 x_row_words: int, x_seg_len: int, x_seg_stride: int, x_back: int, K: int, N_local: int, M: int,
                                  s_mode: int, word_peers, world: int, rank: int, n_offset: int, N_total: int,
                                  y_stride_bytes: int, ticket: torch.Tensor) -> None:
     """Decode form of the fused all-gather: this rank's band goes to every rank as tagged 8-byte words.  The
@@ -326,7 +326,7 @@ def linear_q4_0_allgather_tagged(w: torch.Tensor, x: Optional[torch.Tensor], x_w
     with torch.cuda.device(w.device):
         check(_lib.jq_linear_q4_0_allgather_tagged_device(
             _stream(w), _dev(w, torch.uint8, "w"), None if x is None else _dev(x, torch.float32, "x"),
-            x_words_ptr if x is None else None, x_stride_bytes, x_row_words, x_seg_len, x_seg_stride, K, N_local, M, s_mode, wp,
+            x_words_ptr if x is None else None, x_stride_bytes, x_row_words, x_seg_len, x_seg_stride, x_back, K, N_local, M, s_mode, wp,
             world, rank, n_offset, N_total, y_stride_bytes, _dev(ticket, torch.int64, "ticket")))
 
 

@@ -549,7 +549,7 @@ int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const
 
 int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const float *d_x, const void *d_x_words,
                                            size_t x_stride_bytes, int64_t x_row_words, int64_t x_seg_len, int64_t x_seg_stride,
-                                           int64_t K, int64_t N_local, int64_t M, int s_mode, void *const *word_peers, int world,
+                                           int x_back, int64_t K, int64_t N_local, int64_t M, int s_mode, void *const *word_peers, int world,
                                            int rank, int64_t n_offset, int64_t N_total, size_t y_stride_bytes,
                                            unsigned long long *d_ticket) {
     if (int rc = check_mul_mat_shape(K, N_local, M)) return rc;
@@ -574,6 +574,7 @@ int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const 
             return set_error(JQ_ERR_INVALID_ARG, "null or misaligned peer pointer %d", q);
     }
     if (d_x_words) {
+        if (x_back < 0 || x_back > 64) return set_error(JQ_ERR_INVALID_ARG, "x_back = %d", x_back);
         if (x_seg_len < 8 || x_seg_len % 8 != 0 || K % x_seg_len != 0 || x_seg_stride < 0 || (x_seg_stride & 1) != 0 ||
             (x_row_words & 1) != 0 || ((uintptr_t)d_x_words & 15u) != 0 || (x_stride_bytes & 15u) != 0 ||
             (K / x_seg_len - 1) * x_seg_stride + x_seg_len > x_row_words)
@@ -584,6 +585,7 @@ int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const 
         ga.x_row_words = x_row_words;
         ga.x_seg_len = (int)x_seg_len;
         ga.x_seg_stride = x_seg_stride;
+        ga.x_back = x_back;
     }
     ga.world = world;
     ga.rank = rank;

@@ -96,8 +96,9 @@ struct GatherArgs {
     unsigned long long *ticket = nullptr;         // local 64-bit count, zero before the first call; non-null selects this
                                                   // form.  Every launch adds 65536 (in shares, one per CTA): the launch
                                                   // that finds t is all-gather number (t >> 16) + 1.
-    const unsigned long long *x_words = nullptr;  // this rank's pair of word buffers whose latest all-gather (number
-                                                  // t >> 16) is this launch's input, or nullptr: plain fp32 input
+    const unsigned long long *x_words = nullptr;  // this rank's pair of word buffers whose all-gather number
+                                                  // (t >> 16) - x_back is this launch's input, or nullptr: plain fp32
+    int x_back = 0;                               // 0: the all-gather launched just before this one, 1: the one before that
     uint64_t x_stride_bytes = 0;                  // distance between the two buffers of that pair
     int64_t x_row_words = 0;                      // words per row there (that all-gather's N_total)
     int x_seg_len = 0;                            // activation k of a row is word (k / x_seg_len) * x_seg_stride +

@@ -211,10 +211,10 @@ class TaggedBands:
 
     def linear(self, w_shard: torch.Tensor, K: int, n_offset: int, N_local: int, x: Optional[torch.Tensor] = None,
                source: "Optional[TaggedBands]" = None, seg_len: Optional[int] = None, seg_stride: int = 0,
-               s_mode: Optional[int] = None) -> None:
-        """Queue one fused step.  The activations are the plain tensor ``x``, or the latest all-gather of
-        ``source`` (the one queued just before this call): activation ``k`` is word
-        ``(k // seg_len) * seg_stride + k % seg_len`` of its row (``seg_len`` defaults to ``K``: the first
+               back: int = 0, s_mode: Optional[int] = None) -> None:
+        """Queue one fused step.  The activations are the plain tensor ``x``, or an all-gather of ``source``:
+        the one queued just before this call (``back`` = 0) or ``back`` calls earlier.  Activation ``k`` is
+        word ``(k // seg_len) * seg_stride + k % seg_len`` of its row (``seg_len`` defaults to ``K``: the first
         ``K`` words)."""
         capi = self._capi
         if (x is None) == (source is None):
@@ -225,7 +225,7 @@ class TaggedBands:
             raise ValueError("the source all-gather has a different M")
         capi.linear_q4_0_allgather_tagged(
             w_shard, x, 0 if source is None else source.local_ptr, 0 if source is None else source.y_bytes,
-            0 if source is None else source.N_total, K if seg_len is None else seg_len, seg_stride, K, N_local, self.M,
+            0 if source is None else source.N_total, K if seg_len is None else seg_len, seg_stride, back, K, N_local, self.M,
             capi.S_D_SUM_Q if s_mode is None else s_mode, list(self.ptrs), self.world, self.rank, n_offset, self.N_total,
             self.y_bytes, self.ticket)
 

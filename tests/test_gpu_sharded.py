@@ -135,11 +135,14 @@ def test_tagged_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M, 
             # the same bits as the single-GPU entry on the same activations
             y2_single = c.linear_q4_0(d_w2, torch.from_numpy(x2).to(cuda_device), N2).cpu().numpy()
             assert np.array_equal(y2, y2_single)
+            # a second projection fed by the same output: its input is the all-gather before the one just ahead of it
+            b.linear(d_w2, K2, 0, N2, source=a, seg_len=seg_len, seg_stride=seg_stride, back=1)
+            assert np.array_equal(b.read().cpu().numpy(), y2)
             # the same pair back to back: nothing orders the second layer after the first but the words
             a.linear(d_w1, K, 0, N, x=torch.from_numpy(x).to(cuda_device))
             b.linear(d_w2, K2, 0, N2, source=a, seg_len=seg_len, seg_stride=seg_stride)
             assert np.array_equal(b.read().cpu().numpy(), y2)
-            assert int(a.ticket.item()) == 4 * (step + 1) << 16
+            assert int(a.ticket.item()) == 5 * (step + 1) << 16
         assert c.device_fault() == 0
     finally:
         b.close()
