@@ -293,10 +293,22 @@ int jq_block_sums_q4_0_q8_1_device(void *stream, const void *d_w, const void *d_
 int jq_quantize_q4_0_device(void *stream, const float *d_w, void *d_wq, int64_t N, int64_t K);
 
 /* *fault_out is non-zero after a kernel of this library gave up on a bounded wait on the current device
- * (1: a bulk copy or pipeline stage never completed; 2: the bands of an all-gather never arrived); the call
- * then returns JQ_ERR_TIMEOUT, else JQ_OK.  The kernel that gave up has returned, its output is not valid,
- * and the device stays usable.  Synchronises the device.  `clear` != 0 resets the word. */
+ * (1: a bulk copy or pipeline stage never completed; 2: the bands of an all-gather never arrived), or, in the
+ * range-checked debug build, skipped an access that fell outside its buffer (3); the word keeps the highest
+ * code.  The call then returns JQ_ERR_TIMEOUT, else JQ_OK.  The kernel has returned, its output is not
+ * valid, and the device stays usable.  Synchronises the device.  `clear` != 0 resets the word. */
 int jq_device_fault(int clear, int *fault_out);
+
+/* The range-checked debug build (compiled with -DJQ_BOUNDS_CHECK, linked as libjq_b200_check.so) stands in
+ * for a memory checker: its kernels check every global access against the extent that the entry point's
+ * shape arguments give the buffer, and every dynamic shared-memory offset against the launch's size; an
+ * access outside is skipped and jq_device_fault() reads 3.  (The reference's own hook is the sanitizer
+ * option of its Debug configuration, src/cuda/CMakeLists.txt:127-129.)
+ * jq_bounds_checked(): 1 in that build, 0 otherwise.  jq_debug_set_extent_shrink(n): every extent the
+ * kernels are given from now on is n bytes shorter than the shapes say, so that a test can watch the checks
+ * fire, and the accesses being skipped, on addresses that are in fact in range; 0 restores. */
+int jq_bounds_checked(void);
+int jq_debug_set_extent_shrink(unsigned long long bytes);
 
 /* ---- host entry points (reference-facing) ------------------------------------------------ */
 

@@ -19,6 +19,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libjq_b200.so")
+# the range-checked debug build of the same sources (-DJQ_BOUNDS_CHECK): a library of its own, used by one GPU test
+CHECK_OBJ_DIR = os.path.join(PKG_DIR, "build_check")
+CHECK_LIB_PATH = os.path.join(PKG_DIR, "libjq_b200_check.so")
 PY_DIR = os.path.join(PKG_DIR, "python")
 INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 
@@ -75,27 +78,38 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), proc.stdout, proc.stderr))
 
 
-def build_all(force: bool = False, verbose: bool = False) -> str:
-    """Compile what is out of date; returns the path of ``libjq_b200.so``."""
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    os.makedirs(PY_DIR, exist_ok=True)
+def _build_library(lib_path: str, obj_dir: str, extra_flags: list[str], force: bool, verbose: bool) -> None:
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     hdr_time = _newest_header()
     jobs = []
     objs = []
     for src in CUDA_SOURCES:
         src_path = os.path.join(CSRC, src)
-        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
         objs.append(obj)
         if force or _mtime(obj) < max(_mtime(src_path), hdr_time):
-            jobs.append([nvcc, *NVCC_FLAGS, "-I", INCLUDE_DIR, "-c", src_path, "-o", obj])
+            jobs.append([nvcc, *NVCC_FLAGS, *extra_flags, "-I", INCLUDE_DIR, "-c", src_path, "-o", obj])
     if jobs:
         if verbose:
-            print("[jq build] compiling %d source(s) for sm_100a" % len(jobs), file=sys.stderr)
+            print("[jq build] compiling %d source(s) for sm_100a -> %s" % (len(jobs), os.path.basename(lib_path)), file=sys.stderr)
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
             list(pool.map(_run, jobs))
-    if force or jobs or not os.path.exists(LIB_PATH):
-        _run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+    if force or jobs or not os.path.exists(lib_path):
+        _run([nvcc, "-shared", "-o", lib_path, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+
+
+def build_check(force: bool = False, verbose: bool = False) -> str:
+    """The range-checked debug build; returns the path of ``libjq_b200_check.so``."""
+    _build_library(CHECK_LIB_PATH, CHECK_OBJ_DIR, ["-DJQ_BOUNDS_CHECK"], force, verbose)
+    return CHECK_LIB_PATH
+
+
+def build_all(force: bool = False, verbose: bool = False) -> str:
+    """Compile what is out of date; returns the path of ``libjq_b200.so``."""
+    os.makedirs(PY_DIR, exist_ok=True)
+    hdr_time = _newest_header()
+    _build_library(LIB_PATH, OBJ_DIR, [], force, verbose)
 
     import pybind11  # build-time only
 
@@ -118,3 +132,5 @@ def build_all(force: bool = False, verbose: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build_all(force="--force" in sys.argv, verbose=True))
+    if "--check" in sys.argv:
+        print(build_check(force="--force" in sys.argv, verbose=True))

@@ -13,7 +13,9 @@ from typing import Optional
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libjq_b200.so")
+# JQ_B200_LIBRARY names another build of the same library beside this file (the range-checked debug build,
+# libjq_b200_check.so, for the test that runs the kernels with their range checks on)
+LIB_PATH = os.path.join(_PKG, os.path.basename(os.environ.get("JQ_B200_LIBRARY", "") or "libjq_b200.so"))
 
 OK = 0
 ERR_INVALID_ARG, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_TOO_LARGE = range(1, 8)
@@ -84,6 +86,8 @@ _SIGS = {
     "jq_block_sums_q4_0_q8_1_device": (_ci, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _ci]),
     "jq_quantize_q4_0_device": (_ci, [_vp, _vp, _vp, _i64, _i64]),
     "jq_device_fault": (_ci, [_ci, ctypes.POINTER(_ci)]),
+    "jq_bounds_checked": (_ci, []),
+    "jq_debug_set_extent_shrink": (_ci, [ctypes.c_ulonglong]),
     "jq_q8_1_host": (_ci, [_vp, _vp, ctypes.POINTER(_ci), _ci]),
     "jq_parse_q8_1_output": (_ci, [_vp, _vp, _vp, _vp, _i64]),
     "jq_mat_mul_q4_0_q8_1_host": (_ci, [_vp, _vp, _vp, _vp, ctypes.POINTER(_ci), _ci, _ci, _ci]),

@@ -121,6 +121,26 @@ int ensure_dynamic_smem(const void *kernel, int bytes, bool max_carveout) {
     return JQ_OK;
 }
 
+namespace {
+std::atomic<unsigned long long> g_extent_shrink{0};
+}
+Extent make_extent(const void *base, unsigned long long bytes) {
+    Extent e;
+    e.base = base;
+    const unsigned long long shrink = g_extent_shrink.load(std::memory_order_relaxed);
+    e.bytes = bytes > shrink ? bytes - shrink : 0;
+    return e;
+}
+
+MulMatBounds mul_mat_bounds(const void *d_w, const void *d_xq, const void *d_y, int64_t K, int64_t N, int64_t M, size_t y_elem_bytes) {
+    MulMatBounds b;
+    b.w = make_extent(d_w, (unsigned long long)N * (unsigned long long)(K / QK) * Q4_BYTES);
+    b.xq = make_extent(d_xq, (unsigned long long)M * (unsigned long long)(K / SUPER) * Q8_BYTES);
+    b.y = make_extent(d_y, (unsigned long long)M * (unsigned long long)N * y_elem_bytes);
+    b.fault = BOUNDS_CHECK ? device_fault_ptr() : nullptr;
+    return b;
+}
+
 int *device_fault_ptr() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
@@ -685,9 +705,18 @@ int jq_device_fault(int clear, int *fault_out) {
         JQ_CUDA_TRY(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
     }
     if (fault_out) *fault_out = v;
+    if (v == 3)
+        return set_error(JQ_ERR_TIMEOUT, "a range check of the debug build failed: an access outside its buffer was skipped");
     if (v != 0)
         return set_error(JQ_ERR_TIMEOUT, "a kernel gave up on a bounded wait (%s): its results are not valid",
                          v == 2 ? "bands of an all-gather did not arrive" : "a bulk copy or pipeline stage did not complete");
+    return JQ_OK;
+}
+
+int jq_bounds_checked(void) { return BOUNDS_CHECK ? 1 : 0; }
+
+int jq_debug_set_extent_shrink(unsigned long long bytes) {
+    g_extent_shrink.store(bytes, std::memory_order_relaxed);
     return JQ_OK;
 }
 

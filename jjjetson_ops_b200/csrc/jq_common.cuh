@@ -59,8 +59,34 @@ uint32_t wait_poll_limit();
 void *next_trace_slot();
 
 // Device address (on the current device) of the word a kernel sets when one of its bounded waits
-// gives up; nullptr if it cannot be obtained.  Kernels receive it as a parameter.
+// gives up; nullptr if it cannot be obtained.  Kernels receive it as a parameter.  The word keeps the highest
+// code reported: 1 a wait for a copy, 2 a wait for another rank's data, 3 a range check of the debug build.
 int *device_fault_ptr();
+
+// ---- range-checked debug build (-DJQ_BOUNDS_CHECK) ----------------------------------------------
+// Stands in for a memory checker: every global access of the kernels is checked against the extent of the
+// buffer it belongs to (what the entry point was told through its shape arguments, not what was allocated),
+// every shared-memory offset against the kernel's dynamic shared memory; an access that falls outside is
+// skipped and the fault word is set to 3.  Without the flag the checks compile to nothing and the extents
+// are dead kernel parameters.
+struct Extent {
+    const void *base = nullptr;
+    unsigned long long bytes = 0;
+};
+// Extent of `bytes` at `base`, less the debug shrink (jq_debug_set_extent_shrink: lets a test see the checks
+// fire on accesses that are in fact in range).
+Extent make_extent(const void *base, unsigned long long bytes);
+// The buffers of one multiply, for the kernels that take plain pointers.
+struct MulMatBounds {
+    Extent w, xq, y;
+    int *fault = nullptr;
+};
+MulMatBounds mul_mat_bounds(const void *d_w, const void *d_xq, const void *d_y, int64_t K, int64_t N, int64_t M, size_t y_elem_bytes);
+#ifdef JQ_BOUNDS_CHECK
+constexpr bool BOUNDS_CHECK = true;
+#else
+constexpr bool BOUNDS_CHECK = false;
+#endif
 
 // ---- launchers implemented in the .cu files ----------------------------------------------
 int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t K, int64_t M,
@@ -201,6 +227,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The fault word keeps the highest code reported (see device_fault_ptr()).
+__device__ __forceinline__ void report_fault(int *fault, int code) {
+    if (fault != nullptr) atomicMax(fault, code);
+}
+
+// Range checks of the debug build: true when [p, p + n) lies inside the extent (always, in a normal build).
+__device__ __forceinline__ bool in_extent(const Extent &e, const void *p, unsigned long long n, int *fault) {
+    if (!BOUNDS_CHECK) return true;
+    const unsigned long long a = (unsigned long long)p, b = (unsigned long long)e.base;
+    const bool ok = a >= b && n <= e.bytes && a - b <= e.bytes - n;
+    if (!ok) report_fault(fault, 3);
+    return ok;
+}
+// ... and when [offset, offset + n) lies inside `total` bytes of shared memory.
+__device__ __forceinline__ bool in_shared(unsigned long long offset, unsigned long long n, unsigned long long total, int *fault) {
+    if (!BOUNDS_CHECK) return true;
+    const bool ok = n <= total && offset <= total - n;
+    if (!ok) report_fault(fault, 3);
+    return ok;
+}
+
 // Bounded wait: gives up after `limit` polls, records the fault and reports false so that the
 // caller can leave the kernel instead of hanging the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *fault,
@@ -208,7 +255,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
-    if (fault != nullptr) atomicExch(fault, 1);
+    report_fault(fault, 1);
     return false;
 }
 

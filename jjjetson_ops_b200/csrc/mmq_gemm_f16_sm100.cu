@@ -99,6 +99,7 @@ struct HfParams {
     const uint8_t *xq;
     float *y;
     int *fault;
+    Extent ext_y;  // range-checked debug build (the operand loads are tensor copies: their maps bound them)
     int64_t N, M;
     int K, order, n_super;
     uint32_t row_bytes;
@@ -358,7 +359,8 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll 8
             for (int rr = 0; rr < 32; ++rr) {
                 const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
-                if (m_first + rr < p.M && n < p.N) p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
+                if (m_first + rr < p.M && n < p.N && in_extent(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
+                    p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
             }
         }
     } else if (warp == HF_COPY_WARP) {
@@ -447,6 +449,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.xq = static_cast<const uint8_t *>(d_xq);
     p.y = d_y;
     p.fault = device_fault_ptr();
+    p.ext_y = make_extent(d_y, (unsigned long long)M * (unsigned long long)N * sizeof(float));
     p.N = N;
     p.M = M;
     p.K = (int)K;

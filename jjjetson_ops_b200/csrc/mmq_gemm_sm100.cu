@@ -90,13 +90,15 @@ struct GemmParams {
     uint32_t row_bytes;  // K / 32 * 18
     int *fault;
     GatherArgs gather;   // world > 0: the tile goes to every rank's [M][N_total] buffer instead of y (all-gather epilogue)
+    MulMatBounds bounds; // range-checked debug build: extents of w, xq, y
+    uint32_t smem_total; // ... and the launch's dynamic shared memory
 };
 
 constexpr uint32_t GM_GATHER_UNITS = 1u << 16;  // what one all-gather adds to each arrival count (shares of the CTAs sum to it)
 
 template <int RT, int CT>
-__device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_addr, int chunk, int64_t n0, int64_t m0,
-                                           int tid) {
+__device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t smem_base, uint32_t stage_addr, int chunk, int64_t n0,
+                                           int64_t m0, int tid) {
     constexpr int GM_BN = GemmTile<RT, CT>::BN, GM_BM = GemmTile<RT, CT>::BM, GM_W_BYTES = GemmTile<RT, CT>::W_BYTES;
     // weights: BN rows x 9 sixteen-byte units
 #pragma unroll
@@ -106,8 +108,9 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
             const int row = idx / 9, part = idx - row * 9;
             // rows past the end are not loaded: whatever the stage holds there only reaches outputs that are never stored
             if (n0 + row < p.N) {
-                cp_async_16(stage_addr + row * GM_W_PITCH + part * 16,
-                            p.w + (n0 + row) * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16);
+                const uint32_t dst = stage_addr + row * GM_W_PITCH + part * 16;
+                const uint8_t *src = p.w + (n0 + row) * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16;
+                if (in_extent(p.bounds.w, src, 16, p.fault) && in_shared(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
             }
         }
     }
@@ -121,7 +124,9 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t stage_a
         const int ks = part / 9, unit = part - ks * 9;
         if (m0 + col < p.M) {  // columns past the end: as for the rows
             const int64_t blk = q8_block_index(2 * chunk + ks, m0 + col, p.n_super, p.M, p.order);
-            cp_async_16(xs + col * GM_X_PITCH + ks * Q8_BYTES + unit * 16, p.xq + blk * Q8_BYTES + unit * 16);
+            const uint32_t dst = xs + col * GM_X_PITCH + ks * Q8_BYTES + unit * 16;
+            const uint8_t *src = p.xq + blk * Q8_BYTES + unit * 16;
+            if (in_extent(p.bounds.xq, src, 16, p.fault) && in_shared(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
         }
     }
 }
@@ -148,7 +153,7 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
 
 #pragma unroll
     for (int s = 0; s < GM_STAGES - 1; ++s) {
-        if (s < n_chunks) load_stage<RT, CT>(p, smem_base + s * GM_STAGE_BYTES, s, n0, m0, tid);
+        if (s < n_chunks) load_stage<RT, CT>(p, smem_base, smem_base + s * GM_STAGE_BYTES, s, n0, m0, tid);
         cp_async_commit();
     }
 
@@ -159,7 +164,7 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
         __syncthreads();  // chunk c has landed for everyone; stage (c-1)%S is free again
         {
             const int nc = c + GM_STAGES - 1;
-            if (nc < n_chunks) load_stage<RT, CT>(p, smem_base + (nc % GM_STAGES) * GM_STAGE_BYTES, nc, n0, m0, tid);
+            if (nc < n_chunks) load_stage<RT, CT>(p, smem_base, smem_base + (nc % GM_STAGES) * GM_STAGE_BYTES, nc, n0, m0, tid);
             cp_async_commit();
         }
         const uint32_t ws = smem_base + (c % GM_STAGES) * GM_STAGE_BYTES;
@@ -321,7 +326,7 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int64_t nn = n + (e >> 1) * 8, mm = m + (e & 1);
-                if (nn < p.N && mm < p.M) p.y[mm * p.N + nn] = acc[i][j][e];
+                if (nn < p.N && mm < p.M && in_extent(p.bounds.y, p.y + mm * p.N + nn, sizeof(float), p.fault)) p.y[mm * p.N + nn] = acc[i][j][e];
             }
         }
     }
@@ -332,8 +337,9 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
 namespace {
 
 template <int RT, int CT>
-int run_gemm_mma(cudaStream_t st, const GemmParams &p) {
+int run_gemm_mma(cudaStream_t st, GemmParams &p) {
     using Tile = GemmTile<RT, CT>;
+    p.smem_total = (uint32_t)Tile::SMEM;
     const int64_t gx = (p.N + Tile::BN - 1) / Tile::BN, gy = (p.M + Tile::BM - 1) / Tile::BM;
     if (gy > 65535) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_mma_kernel<RT, CT>), Tile::SMEM, true)) return rc;
@@ -363,6 +369,7 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.fault = device_fault_ptr();
+    p.bounds = mul_mat_bounds(d_w, d_xq, d_y, K, N, M, sizeof(float));
     if (gather != nullptr) p.gather = *gather;
     DeviceCaps caps;
     if (int rc = device_caps(&caps)) return rc;

@@ -32,7 +32,7 @@ __device__ __forceinline__ int block_sumi(const uint8_t *wblk, const int *xq_int
 
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
-                   int64_t K, int64_t N, int64_t M, int order) {
+                   int64_t K, int64_t N, int64_t M, int order, const MulMatBounds bounds) {
     const int lane = threadIdx.x & 31;
     const int64_t n = (int64_t)blockIdx.x * GEN_WARPS + (threadIdx.x >> 5);
     const int64_t m0 = (int64_t)blockIdx.y * GEN_COLS;
@@ -44,6 +44,7 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
 
     for (int64_t kb = lane; kb < nb; kb += 32) {
         const uint8_t *wblk = w + (n * nb + kb) * Q4_BYTES;
+        if (!in_extent(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
         const float d4 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(wblk));
         uint32_t wq[4];
 #pragma unroll
@@ -53,6 +54,7 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
             const int64_t m = m0 + c;
             if (m < M) {
                 const uint8_t *xb = xq + q8_block_index(kb >> 2, m, n_super, M, order) * Q8_BYTES;
+                if (!in_extent(bounds.xq, xb, Q8_BYTES, bounds.fault)) continue;
                 const int sub = (int)(kb & 3);
                 const int4 *xi = reinterpret_cast<const int4 *>(xb + Q8_QS_OFFSET + sub * QK);
                 const int4 lo = __ldg(xi), hi = __ldg(xi + 1);
@@ -77,21 +79,25 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
         float v = acc[c];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
-        if (lane == 0 && m0 + c < M) y[(m0 + c) * N + n] = v;
+        if (lane == 0 && m0 + c < M && in_extent(bounds.y, y + (m0 + c) * N + n, sizeof(float), bounds.fault)) y[(m0 + c) * N + n] = v;
     }
 }
 
 __global__ void __launch_bounds__(256)
 block_sums_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, int32_t *__restrict__ sums,
-                  int64_t K, int64_t N, int64_t M, int order) {
+                  int64_t K, int64_t N, int64_t M, int order, const MulMatBounds bounds) {
     const int64_t nb = K / QK, n_super = K / SUPER;
     const int64_t total = N * nb;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = i / nb, kb = i - n * nb;
         const uint8_t *wblk = w + i * Q4_BYTES;
+        if (!in_extent(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
         for (int64_t m = 0; m < M; ++m) {
             const uint8_t *xb = xq + q8_block_index(kb >> 2, m, n_super, M, order) * Q8_BYTES;
+            if (!in_extent(bounds.xq, xb, Q8_BYTES, bounds.fault) ||
+                !in_extent(bounds.y, sums + (m * N + n) * nb + kb, sizeof(int32_t), bounds.fault))
+                continue;
             const int *xi = reinterpret_cast<const int *>(xb + Q8_QS_OFFSET + (kb & 3) * QK);
             int x8[8];
 #pragma unroll
@@ -111,7 +117,8 @@ int launch_mmq_generic(cudaStream_t st, const void *d_w, const void *d_xq, float
                                      65535 * GEN_COLS);
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     mmq_generic_kernel<<<dim3((unsigned)gx, (unsigned)gy), GEN_WARPS * 32, 0, st>>>(
-        static_cast<const uint8_t *>(d_w), static_cast<const uint8_t *>(d_xq), d_y, K, N, M, order);
+        static_cast<const uint8_t *>(d_w), static_cast<const uint8_t *>(d_xq), d_y, K, N, M, order,
+        mul_mat_bounds(d_w, d_xq, d_y, K, N, M, sizeof(float)));
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }
@@ -124,7 +131,8 @@ int launch_block_sums(cudaStream_t st, const void *d_w, const void *d_xq, int32_
     if (ctas > 148 * 16) ctas = 148 * 16;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
     block_sums_kernel<<<(unsigned)ctas, 256, 0, st>>>(static_cast<const uint8_t *>(d_w),
-                                                      static_cast<const uint8_t *>(d_xq), d_sums, K, N, M, order);
+                                                      static_cast<const uint8_t *>(d_xq), d_sums, K, N, M, order,
+                                                      mul_mat_bounds(d_w, d_xq, d_sums, K, N, M, sizeof(int32_t) * (size_t)(K / QK)));
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }

@@ -12,6 +12,11 @@ namespace {
 
 constexpr int QUANT_THREADS = 256;
 constexpr int QUANT_UNROLL = 4;
+struct QuantBounds {  // the buffers of one quantizer launch (range-checked debug build)
+    Extent x, xq;
+    int *fault = nullptr;
+};
+
 constexpr int QUANT_PAIR_UNROLL = 2;  // pairs in flight per warp (4 cost occupancy: 78 registers, 34 % warps active, 3 % slower)
 
 // IDX is the type of the block counter: 32-bit whenever M * K / 128 fits (64-bit division costs more
@@ -19,7 +24,7 @@ constexpr int QUANT_PAIR_UNROLL = 2;  // pairs in flight per warp (4 cost occupa
 template <typename IDX>
 __global__ void __launch_bounds__(QUANT_THREADS)
 quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq, int64_t K, int64_t M,
-                           int64_t n_super_, int order, int s_mode) {
+                           int64_t n_super_, int order, int s_mode, const QuantBounds bounds) {
     // let the multiply that follows on the stream start its weight stream right away; wait for
     // whatever produced x before reading it
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -42,7 +47,8 @@ quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq
                 row[u] = b / n_super;
                 ks[u] = b - row[u] * n_super;
                 const int64_t k = (int64_t)ks[u] * SUPER + lane * 4;
-                if (k < K) xi[u] = __ldg(reinterpret_cast<const float4 *>(x + (int64_t)row[u] * K + k));
+                const float *src = x + (int64_t)row[u] * K + k;
+                if (k < K && in_extent(bounds.x, src, sizeof(float4), bounds.fault)) xi[u] = __ldg(reinterpret_cast<const float4 *>(src));
             }
         }
 #pragma unroll
@@ -52,6 +58,7 @@ quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq
             uint32_t ds;
             const uint32_t q = quantize_group_q8_1(xi[u], s_mode, &ds);
             uint8_t *blk = xq + q8_block_index(ks[u], row[u], n_super_, M, order) * Q8_BYTES;
+            if (!in_extent(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
             reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
             if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
         }
@@ -65,7 +72,7 @@ quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq
 template <typename IDX>
 __global__ void __launch_bounds__(QUANT_THREADS, 5)
 quantize_q8_1_pairs_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq, int64_t K, int64_t M, int64_t n_super_,
-                                 int order, int s_mode) {
+                                 int order, int s_mode, const QuantBounds bounds) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
@@ -86,8 +93,10 @@ quantize_q8_1_pairs_kernel_sm100(const float *__restrict__ x, uint8_t *__restric
                 row[u] = p / n_pairs_row;
                 pr[u] = p - row[u] * n_pairs_row;
                 const float4 *src = reinterpret_cast<const float4 *>(x + (int64_t)row[u] * K + (int64_t)pr[u] * (2 * SUPER)) + 2 * lane;
-                xa[u] = __ldg(src);
-                xb[u] = __ldg(src + 1);
+                if (in_extent(bounds.x, src, 2 * sizeof(float4), bounds.fault)) {
+                    xa[u] = __ldg(src);
+                    xb[u] = __ldg(src + 1);
+                }
             }
         }
 #pragma unroll
@@ -100,6 +109,7 @@ quantize_q8_1_pairs_kernel_sm100(const float *__restrict__ x, uint8_t *__restric
             quantize_8_per_lane_q8_1(v, s_mode, &q, &ds);
             const int64_t ks = 2 * (int64_t)pr[u] + (lane >> 4);  // this lane's block of the pair
             uint8_t *blk = xq + q8_block_index(ks, row[u], n_super_, M, order) * Q8_BYTES;
+            if (!in_extent(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
             reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = q;
             if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
         }
@@ -192,20 +202,24 @@ int launch_quantize_q8_1(cudaStream_t st, const float *d_x, void *d_xq, int64_t 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const bool idx32 = total + (int64_t)ctas * QUANT_THREADS < (int64_t)0x7FFFFFFF;
+    QuantBounds bounds;
+    bounds.x = make_extent(d_x, (unsigned long long)M * (unsigned long long)K * sizeof(float));
+    bounds.xq = make_extent(d_xq, (unsigned long long)total * Q8_BYTES);
+    bounds.fault = BOUNDS_CHECK ? device_fault_ptr() : nullptr;
     if (pairs) {
         if (idx32) {
             JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_pairs_kernel_sm100<uint32_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
-                                           n_super, order, s_mode));
+                                           n_super, order, s_mode, bounds));
         } else {
             JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_pairs_kernel_sm100<int64_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
-                                           n_super, order, s_mode));
+                                           n_super, order, s_mode, bounds));
         }
     } else if (idx32) {
         JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100<uint32_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
-                                       n_super, order, s_mode));
+                                       n_super, order, s_mode, bounds));
     } else {
         JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_kernel_sm100<int64_t>, d_x, static_cast<uint8_t *>(d_xq), K, M,
-                                       n_super, order, s_mode));
+                                       n_super, order, s_mode, bounds));
     }
     return JQ_OK;
 }
