@@ -67,8 +67,8 @@ int *device_fault_ptr();
 // Stands in for a memory checker: every global access of the kernels is checked against the extent of the
 // buffer it belongs to (what the entry point was told through its shape arguments, not what was allocated),
 // every shared-memory offset against the kernel's dynamic shared memory; an access that falls outside is
-// skipped and the fault word is set to 3.  Without the flag the checks compile to nothing and the extents
-// are dead kernel parameters.
+// skipped and the fault word is set to 3.  Without the flag the checks are not there (JQ_IN_EXTENT / JQ_IN_SHARED
+// expand to `true`) and the larger kernel-parameter structures do not carry the extents.
 struct Extent {
     const void *base = nullptr;
     unsigned long long bytes = 0;
@@ -229,7 +229,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // The fault word keeps the highest code reported (see device_fault_ptr()).
 __device__ __forceinline__ void report_fault(int *fault, int code) {
+#ifdef JQ_BOUNDS_CHECK
     if (fault != nullptr) atomicMax(fault, code);
+#else
+    if (fault != nullptr) atomicExch(fault, code);
+#endif
 }
 
 // Range checks of the debug build: true when [p, p + n) lies inside the extent (always, in a normal build).
@@ -247,6 +251,16 @@ __device__ __forceinline__ bool in_shared(unsigned long long offset, unsigned lo
     if (!ok) report_fault(fault, 3);
     return ok;
 }
+
+// What the kernels write: in a normal build the conditions are the literal `true` and their arguments are not even
+// evaluated, so the code is what it would be without the checks.
+#ifdef JQ_BOUNDS_CHECK
+#define JQ_IN_EXTENT(e, p, n, fault) ::jq::in_extent(e, p, n, fault)
+#define JQ_IN_SHARED(offset, n, total, fault) ::jq::in_shared(offset, n, total, fault)
+#else
+#define JQ_IN_EXTENT(e, p, n, fault) true
+#define JQ_IN_SHARED(offset, n, total, fault) true
+#endif
 
 // Bounded wait: gives up after `limit` polls, records the fault and reports false so that the
 // caller can leave the kernel instead of hanging the GPU.

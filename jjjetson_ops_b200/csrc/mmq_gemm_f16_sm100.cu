@@ -99,7 +99,9 @@ struct HfParams {
     const uint8_t *xq;
     float *y;
     int *fault;
+#ifdef JQ_BOUNDS_CHECK
     Extent ext_y;  // range-checked debug build (the operand loads are tensor copies: their maps bound them)
+#endif
     int64_t N, M;
     int K, order, n_super;
     uint32_t row_bytes;
@@ -359,7 +361,7 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll 8
             for (int rr = 0; rr < 32; ++rr) {
                 const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
-                if (m_first + rr < p.M && n < p.N && in_extent(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
+                if (m_first + rr < p.M && n < p.N && JQ_IN_EXTENT(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
                     p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
             }
         }
@@ -449,7 +451,9 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.xq = static_cast<const uint8_t *>(d_xq);
     p.y = d_y;
     p.fault = device_fault_ptr();
+#ifdef JQ_BOUNDS_CHECK
     p.ext_y = make_extent(d_y, (unsigned long long)M * (unsigned long long)N * sizeof(float));
+#endif
     p.N = N;
     p.M = M;
     p.K = (int)K;

@@ -90,8 +90,10 @@ struct GemmParams {
     uint32_t row_bytes;  // K / 32 * 18
     int *fault;
     GatherArgs gather;   // world > 0: the tile goes to every rank's [M][N_total] buffer instead of y (all-gather epilogue)
+#ifdef JQ_BOUNDS_CHECK
     MulMatBounds bounds; // range-checked debug build: extents of w, xq, y
     uint32_t smem_total; // ... and the launch's dynamic shared memory
+#endif
 };
 
 constexpr uint32_t GM_GATHER_UNITS = 1u << 16;  // what one all-gather adds to each arrival count (shares of the CTAs sum to it)
@@ -110,7 +112,7 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t smem_ba
             if (n0 + row < p.N) {
                 const uint32_t dst = stage_addr + row * GM_W_PITCH + part * 16;
                 const uint8_t *src = p.w + (n0 + row) * p.row_bytes + (size_t)chunk * GM_W_PITCH + part * 16;
-                if (in_extent(p.bounds.w, src, 16, p.fault) && in_shared(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
+                if (JQ_IN_EXTENT(p.bounds.w, src, 16, p.fault) && JQ_IN_SHARED(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
             }
         }
     }
@@ -126,7 +128,7 @@ __device__ __forceinline__ void load_stage(const GemmParams &p, uint32_t smem_ba
             const int64_t blk = q8_block_index(2 * chunk + ks, m0 + col, p.n_super, p.M, p.order);
             const uint32_t dst = xs + col * GM_X_PITCH + ks * Q8_BYTES + unit * 16;
             const uint8_t *src = p.xq + blk * Q8_BYTES + unit * 16;
-            if (in_extent(p.bounds.xq, src, 16, p.fault) && in_shared(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
+            if (JQ_IN_EXTENT(p.bounds.xq, src, 16, p.fault) && JQ_IN_SHARED(dst - smem_base, 16, p.smem_total, p.fault)) cp_async_16(dst, src);
         }
     }
 }
@@ -326,7 +328,7 @@ __global__ void __launch_bounds__(GM_THREADS, GemmTile<RT, CT>::MIN_CTAS) gemm_q
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int64_t nn = n + (e >> 1) * 8, mm = m + (e & 1);
-                if (nn < p.N && mm < p.M && in_extent(p.bounds.y, p.y + mm * p.N + nn, sizeof(float), p.fault)) p.y[mm * p.N + nn] = acc[i][j][e];
+                if (nn < p.N && mm < p.M && JQ_IN_EXTENT(p.bounds.y, p.y + mm * p.N + nn, sizeof(float), p.fault)) p.y[mm * p.N + nn] = acc[i][j][e];
             }
         }
     }
@@ -339,7 +341,9 @@ namespace {
 template <int RT, int CT>
 int run_gemm_mma(cudaStream_t st, GemmParams &p) {
     using Tile = GemmTile<RT, CT>;
+#ifdef JQ_BOUNDS_CHECK
     p.smem_total = (uint32_t)Tile::SMEM;
+#endif
     const int64_t gx = (p.N + Tile::BN - 1) / Tile::BN, gy = (p.M + Tile::BM - 1) / Tile::BM;
     if (gy > 65535) return set_error(JQ_ERR_UNSUPPORTED, "shape too large for the tensor-core GEMM");
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_mma_kernel<RT, CT>), Tile::SMEM, true)) return rc;
@@ -369,7 +373,9 @@ int launch_gemm_mma(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.fault = device_fault_ptr();
+#ifdef JQ_BOUNDS_CHECK
     p.bounds = mul_mat_bounds(d_w, d_xq, d_y, K, N, M, sizeof(float));
+#endif
     if (gather != nullptr) p.gather = *gather;
     DeviceCaps caps;
     if (int rc = device_caps(&caps)) return rc;

@@ -110,7 +110,9 @@ struct TcParams {
     const uint8_t *xq;
     float *y;
     int *fault;
+#ifdef JQ_BOUNDS_CHECK
     Extent ext_y;  // range-checked debug build (the operand loads are tensor copies: their maps bound them)
+#endif
     int64_t N, M;
     int K, order, n_super;
     uint32_t row_bytes;
@@ -352,8 +354,13 @@ gemm_q4_0_q8_1_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap w
                 }
             }
             const int64_t m = m0 + row;
+#ifdef JQ_BOUNDS_CHECK
             const int64_t n_row = p.N - (n0 + half * 64) < 64 ? p.N - (n0 + half * 64) : 64;  // outputs of this lane's row
-            if (m < p.M && (n_row <= 0 || in_extent(p.ext_y, p.y + m * p.N + n0 + half * 64, (unsigned long long)n_row * sizeof(float), p.fault))) {
+            const bool y_ok = m >= p.M || n_row <= 0 || in_extent(p.ext_y, p.y + m * p.N + n0 + half * 64, (unsigned long long)n_row * sizeof(float), p.fault);
+#else
+            const bool y_ok = true;
+#endif
+            if (m < p.M && y_ok) {
                 float *dst = p.y + m * p.N + n0 + half * 64;
                 const int64_t n_left = p.N - (n0 + half * 64);
                 if (n_left >= 64 && ((uintptr_t)dst & 15u) == 0) {
@@ -502,7 +509,9 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
     p.xq = static_cast<const uint8_t *>(d_xq);
     p.y = d_y;
     p.fault = device_fault_ptr();
+#ifdef JQ_BOUNDS_CHECK
     p.ext_y = make_extent(d_y, (unsigned long long)M * (unsigned long long)N * sizeof(float));
+#endif
     p.N = N;
     p.M = M;
     p.K = (int)K;

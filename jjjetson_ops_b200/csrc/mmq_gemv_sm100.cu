@@ -67,20 +67,28 @@ struct GemvParams {
     unsigned long long *trace;  // 8 timestamps per CTA of this launch (tracing aid), or nullptr
     uint32_t poll_limit;        // polls after which a bounded wait gives up
     uint32_t rows_q, rows_r;    // N = rows_q * grid + rows_r (see cta_row_range)
+#ifdef JQ_BOUNDS_CHECK
     // range-checked debug build: extents of the buffers (per weight matrix / output), of the activations in whichever
     // form they come, of the workspace, of every rank's all-gather buffers, and the launch's dynamic shared memory
     Extent ext_w[GV_MAX_MATS], ext_y[GV_MAX_MATS], ext_x, ext_xq_out, ext_peer[MAX_PEERS], ext_x_words;
     uint32_t smem_total;
+#endif
 };
 
 // offset of a shared-memory address inside the launch's dynamic shared memory
 extern __shared__ __align__(128) uint8_t gv_dynamic_smem[];
 __device__ __forceinline__ uint32_t dyn_offset(const void *p) { return smem_u32(p) - smem_u32(gv_dynamic_smem); }
-// a bulk copy whose source lies inside `e` and whose destination lies inside the dynamic shared memory
-__device__ __forceinline__ void bulk_g2s_checked(const GemvParams &p, const Extent &e, void *dst, const void *src, uint32_t bytes,
-                                                 uint64_t *bar) {
-    if (in_extent(e, src, bytes, p.fault) && in_shared(dyn_offset(dst), bytes, p.smem_total, p.fault)) bulk_g2s(dst, src, bytes, bar);
-}
+// a bulk copy whose source lies inside extent `e` of the parameters and whose destination lies inside the dynamic
+// shared memory (debug build); the plain copy otherwise
+#ifdef JQ_BOUNDS_CHECK
+#define JQ_BULK_G2S(p, e, dst, src, bytes, bar)                                                                          \
+    do {                                                                                                                 \
+        if (in_extent((p).e, src, bytes, (p).fault) && in_shared(dyn_offset(dst), bytes, (p).smem_total, (p).fault))     \
+            bulk_g2s(dst, src, bytes, bar);                                                                              \
+    } while (0)
+#else
+#define JQ_BULK_G2S(p, e, dst, src, bytes, bar) bulk_g2s(dst, src, bytes, bar)
+#endif
 
 // matrix that owns row r of the concatenation (n_mats is tiny: a linear scan)
 __device__ __forceinline__ int mat_of_row(const GemvParams &p, int64_t r) {
@@ -97,9 +105,13 @@ __device__ __forceinline__ float *y_slot(const GemvParams &p, int m, int64_t r, 
 }
 // store of output (column m, row r), range-checked in the debug build
 __device__ __forceinline__ void store_y(const GemvParams &p, int m, int64_t r, float v) {
+#ifdef JQ_BOUNDS_CHECK
     int mat = 0;
     float *dst = y_slot(p, m, r, &mat);
     if (in_extent(p.ext_y[mat], dst, sizeof(float), p.fault)) *dst = v;
+#else
+    *y_slot(p, m, r) = v;
+#endif
 }
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -262,7 +274,7 @@ __device__ __forceinline__ bool producer_activations(const GemvParams &p, uint64
     }
     mbar_arrive_expect_tx(x_full, p.x_copy_bytes);
     const uint32_t per_row = (uint32_t)p.n_super * Q8_BYTES;
-    for (int m = 0; m < p.M; ++m) bulk_g2s_checked(p, p.ext_x, xs + (size_t)m * p.x_pitch, p.xq + (size_t)m * per_row, per_row, x_full);
+    for (int m = 0; m < p.M; ++m) JQ_BULK_G2S(p, ext_x, xs + (size_t)m * p.x_pitch, p.xq + (size_t)m * per_row, per_row, x_full);
     return true;
 }
 
@@ -301,15 +313,15 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
             const uint8_t *src = p.w + r0 * p.row_bytes;
             if (PER_ROW) {
                 for (int r = lane; r < rows; r += 32) {
-                    bulk_g2s_checked(p, p.ext_w[0], dst + (size_t)r * p.row_stride, src + (size_t)r * p.row_bytes, p.row_bytes, &full[s]);
+                    JQ_BULK_G2S(p, ext_w[0], dst + (size_t)r * p.row_stride, src + (size_t)r * p.row_bytes, p.row_bytes, &full[s]);
                 }
             } else {
-                bulk_g2s_checked(p, p.ext_w[0], dst, src, (uint32_t)rows * p.row_bytes, &full[s]);
+                JQ_BULK_G2S(p, ext_w[0], dst, src, (uint32_t)rows * p.row_bytes, &full[s]);
             }
         } else if (PER_ROW) {
             for (int r = lane; r < rows; r += 32) {
                 const int i = mat_of_row(p, r0 + r);
-                bulk_g2s_checked(p, p.ext_w[i], dst + (size_t)r * p.row_stride, p.w_mat[i] + (r0 + r - p.mat_begin[i]) * p.row_bytes,
+                JQ_BULK_G2S(p, ext_w[i], dst + (size_t)r * p.row_stride, p.w_mat[i] + (r0 + r - p.mat_begin[i]) * p.row_bytes,
                                  p.row_bytes, &full[s]);
             }
         } else {
@@ -319,7 +331,7 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
             while (left > 0) {
                 const int i = mat_of_row(p, r);
                 const int take = (int)min((int64_t)left, p.mat_begin[i + 1] - r);
-                bulk_g2s_checked(p, p.ext_w[i], dst, p.w_mat[i] + (r - p.mat_begin[i]) * p.row_bytes, (uint32_t)take * p.row_bytes, &full[s]);
+                JQ_BULK_G2S(p, ext_w[i], dst, p.w_mat[i] + (r - p.mat_begin[i]) * p.row_bytes, (uint32_t)take * p.row_bytes, &full[s]);
                 dst += (size_t)take * p.row_bytes;
                 r += take;
                 left -= take;
@@ -350,7 +362,7 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
         if (idx < total) {
             const int m = idx / p.n_super, ks = idx - m * p.n_super;
             const float4 *src = reinterpret_cast<const float4 *>(p.x_f32 + (size_t)m * p.K + ks * SUPER) + lane;
-            if (in_extent(p.ext_x, src, sizeof(float4), p.fault)) xi[u] = __ldg(src);
+            if (JQ_IN_EXTENT(p.ext_x, src, sizeof(float4), p.fault)) xi[u] = __ldg(src);
         }
     }
     if (first) {
@@ -374,12 +386,12 @@ __device__ __forceinline__ void quantize_batch(const GemvParams &p, uint8_t *xs,
         if (idx < total) {
             const int m = idx / p.n_super, ks = idx - m * p.n_super;
             uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-            if (!in_shared(dyn_offset(blk), Q8_BYTES, p.smem_total, p.fault)) continue;
+            if (!JQ_IN_SHARED(dyn_offset(blk), Q8_BYTES, p.smem_total, p.fault)) continue;
             reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = qv[u];
             if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = dsv[u];
             if (p.xq_out != nullptr && blockIdx.x == 0) {
                 uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-                if (!in_extent(p.ext_xq_out, g, Q8_BYTES, p.fault)) continue;
+                if (!JQ_IN_EXTENT(p.ext_xq_out, g, Q8_BYTES, p.fault)) continue;
                 reinterpret_cast<uint32_t *>(g + Q8_QS_OFFSET)[lane] = qv[u];
                 if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(g)[lane >> 3] = dsv[u];
             }
@@ -392,12 +404,12 @@ __device__ __forceinline__ void store_pair_blocks(const GemvParams &p, uint8_t *
     const int idx = 2 * pr + (lane >> 4);  // this lane's block, (m, ks) in row-major order
     const int m = idx / p.n_super, ks = idx - m * p.n_super;
     uint8_t *blk = xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES;
-    if (!in_shared(dyn_offset(blk), Q8_BYTES, p.smem_total, p.fault)) return;
+    if (!JQ_IN_SHARED(dyn_offset(blk), Q8_BYTES, p.smem_total, p.fault)) return;
     reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = qv;
     if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
     if (p.xq_out != nullptr && blockIdx.x == 0) {
         uint8_t *g = p.xq_out + (size_t)idx * Q8_BYTES;  // JQ_ORDER_COL_KSUPER
-        if (!in_extent(p.ext_xq_out, g, Q8_BYTES, p.fault)) return;
+        if (!JQ_IN_EXTENT(p.ext_xq_out, g, Q8_BYTES, p.fault)) return;
         reinterpret_cast<uint2 *>(g + Q8_QS_OFFSET)[lane & 15] = qv;
         if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(g)[(lane & 15) >> 2] = ds;
     }
@@ -424,9 +436,12 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
             // (Measured and dropped: one lane per warp watching a single pair of words before all lanes look, 9.55
             // against 9.15 us per step on two GPUs: the words of different senders arrive microseconds apart, and the
             // lanes are better off each watching their own.)
-            uint4 w[4] = {};
+            uint4 w[4];
+#ifdef JQ_BOUNDS_CHECK
+            for (int u = 0; u < 4; ++u) w[u] = make_uint4(0u, 0u, 0u, 0u);
+#endif
             bool ok = false;
-            const bool readable = in_extent(p.ext_x_words, src, 8 * sizeof(unsigned long long), p.fault);
+            const bool readable = JQ_IN_EXTENT(p.ext_x_words, src, 8 * sizeof(unsigned long long), p.fault);
             for (uint32_t spin = 0; readable && spin < p.poll_limit && !ok; ++spin) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) w[u] = ld_words2(src + 2 * u);
@@ -462,7 +477,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
                 xa[u] = xb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (pr < pairs) {
                     const float4 *src = reinterpret_cast<const float4 *>(p.x_f32 + (size_t)pr * (2 * SUPER)) + 2 * lane;
-                    if (in_extent(p.ext_x, src, 2 * sizeof(float4), p.fault)) {
+                    if (JQ_IN_EXTENT(p.ext_x, src, 2 * sizeof(float4), p.fault)) {
                         xa[u] = __ldg(src);
                         xb[u] = __ldg(src + 1);
                     }
@@ -509,9 +524,14 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
             const int idx = i / 9, part = i - idx * 9;
             const int m = idx / p.n_super, ks = idx - m * p.n_super;
             const uint8_t *g = p.xq + (size_t)q8_block_index(ks, m, p.n_super, p.M, p.order) * Q8_BYTES;
+#ifdef JQ_BOUNDS_CHECK
             uint4 *dst = reinterpret_cast<uint4 *>(xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES) + part;
             if (in_extent(p.ext_x, g + 16 * part, 16, p.fault) && in_shared(dyn_offset(dst), 16, p.smem_total, p.fault))
                 *dst = __ldg(reinterpret_cast<const uint4 *>(g) + part);
+#else
+            reinterpret_cast<uint4 *>(xs + (size_t)m * p.x_pitch + (size_t)ks * Q8_BYTES)[part] =
+                __ldg(reinterpret_cast<const uint4 *>(g) + part);
+#endif
         }
     }
     if (!arrived) {
@@ -738,10 +758,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
 #pragma unroll
             for (int i = 0; i < NSB; ++i) {
                 if (lane + 32 * i < p.n_super) {  // lanes past the end of K hold no activations: their bytes are another row's
-                    if (BOUNDS_CHECK) {
+#ifdef JQ_BOUNDS_CHECK
+                    {
                         const uint32_t base = smem_u32(gv_dynamic_smem) - (uint32_t)i * (32u * 72u);
                         if (!in_shared(rowA - base, 72, p.smem_total, p.fault) || !in_shared(rowB - base, 72, p.smem_total, p.fault)) continue;
                     }
+#endif
                     uint32_t wA[18], wB[18];
 #pragma unroll
                     for (int j = 0; j < 9; ++j) {
@@ -768,12 +790,15 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
 #pragma unroll
                 for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
                 if ((lane & 15) == 0 && m < p.M && (upper ? hasB : hasA)) {
-                    if (p.gather.world > 0) {  // the band's staging buffer in shared memory
+                    if (y_cta != nullptr) {  // the band's staging buffer in shared memory, or a single matrix's output
+#ifdef JQ_BOUNDS_CHECK
                         float *dst = y_cta + (size_t)m * y_pitch + (size_t)rel;
-                        if (in_shared(dyn_offset(dst), sizeof(float), p.smem_total, p.fault)) *dst = v;
-                    } else if (y_cta != nullptr) {
-                        float *dst = y_cta + (size_t)m * y_pitch + (size_t)rel;
-                        if (in_extent(p.ext_y[0], dst, sizeof(float), p.fault)) *dst = v;
+                        if (p.gather.world > 0 ? in_shared(dyn_offset(dst), sizeof(float), p.smem_total, p.fault)
+                                               : in_extent(p.ext_y[0], dst, sizeof(float), p.fault))
+                            *dst = v;
+#else
+                        y_cta[(size_t)m * y_pitch + (size_t)rel] = v;
+#endif
                     } else {
                         store_y(p, m, r_begin + rel, v);
                     }
@@ -806,7 +831,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                                       (size_t)m * ga.N_total + ga.n_offset + r_begin;
             const float *src = ybuf + (size_t)m * p.y_rows;
             for (int i = lane; i < rows_cta; i += 32) {
-                if (in_extent(p.ext_peer[q], dst + i, sizeof(unsigned long long), p.fault)) st_word(dst + i, src[i], gather_epoch);
+                if (JQ_IN_EXTENT(p.ext_peer[q], dst + i, sizeof(unsigned long long), p.fault)) st_word(dst + i, src[i], gather_epoch);
             }
         }
         if (threadIdx.x == 0) trace_fine(p, 6);  // warp 0: its stores are issued
@@ -823,7 +848,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                          (size_t)m * ga.N_total + ga.n_offset + r_begin;
             const float *src = ybuf + (size_t)m * p.y_rows;
             for (int i = lane; i < rows_cta; i += 32) {  // 128 contiguous bytes per warp store
-                if (in_extent(p.ext_peer[q], dst + i, sizeof(float), p.fault)) dst[i] = src[i];
+                if (JQ_IN_EXTENT(p.ext_peer[q], dst + i, sizeof(float), p.fault)) dst[i] = src[i];
             }
         }
         named_bar_sync(1, NW * 32);  // all of this CTA's peer stores have been issued
@@ -1088,7 +1113,9 @@ int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     }
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "row of %u bytes does not fit the shared-memory ring", p.row_bytes);
     const int smem = GV_BAR_BYTES + (int)p.y_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+#ifdef JQ_BOUNDS_CHECK
     p.smem_total = (uint32_t)smem;
+#endif
     auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
@@ -1110,7 +1137,9 @@ int run_mma(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
     p.stages = (int)min((int64_t)GV_MAX_STAGES, avail / p.stage_bytes);
     if (p.stages < 2) return set_error(JQ_ERR_UNSUPPORTED, "16 rows of %u bytes do not fit the shared-memory ring", p.row_bytes);
     const int smem = GV_BAR_BYTES + red_bytes + (int)p.x_bytes + p.stages * (int)p.stage_bytes;
+#ifdef JQ_BOUNDS_CHECK
     p.smem_total = (uint32_t)smem;
+#endif
     auto kernel = gemv_mma_kernel<KBW, NW>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + 15) / 16;
@@ -1145,11 +1174,13 @@ int fill_params(GemvParams &p, const void *d_w, const void *d_xq, const float *d
     // activation loads that follow the wait).
     p.early_stages = p.prefetch_early ? 2 : (1 << 30);
     p.poll_limit = wait_poll_limit();
+#ifdef JQ_BOUNDS_CHECK
     const unsigned long long blocks_bytes = (unsigned long long)M * (unsigned long long)p.n_super * Q8_BYTES;
     p.ext_w[0] = make_extent(d_w, (unsigned long long)N * p.row_bytes);
     p.ext_y[0] = make_extent(d_y, (unsigned long long)M * (unsigned long long)N * sizeof(float));
     p.ext_x = d_x_f32 ? make_extent(d_x_f32, (unsigned long long)M * (unsigned long long)K * sizeof(float)) : make_extent(d_xq, blocks_bytes);
     p.ext_xq_out = make_extent(p.xq_out, blocks_bytes);
+#endif
 
     return JQ_OK;
 }
@@ -1168,8 +1199,10 @@ int apply_multi(GemvParams &p, const MultiMat *multi, const GatherArgs *gather) 
         p.w_mat[i] = static_cast<const uint8_t *>(multi->w[i]);
         p.y_mat[i] = multi->y[i];
         p.mat_begin[i + 1] = p.mat_begin[i] + multi->rows[i];
+#ifdef JQ_BOUNDS_CHECK
         p.ext_w[i] = make_extent(multi->w[i], (unsigned long long)multi->rows[i] * p.row_bytes);
         p.ext_y[i] = make_extent(multi->y[i], (unsigned long long)p.M * (unsigned long long)multi->rows[i] * sizeof(float));
+#endif
     }
     if (p.mat_begin[multi->n] != p.N) return set_error(JQ_ERR_INVALID_ARG, "row counts of the matrices do not add up to N");
     p.w = p.w_mat[0];
@@ -1217,11 +1250,13 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
     fill_params(p, d_w, d_xq, d_x_f32, d_xq_out, d_y, K, N, M, order, s_mode);
     if (gather != nullptr) {
         p.gather = *gather;
+#ifdef JQ_BOUNDS_CHECK
         const unsigned long long elem = gather->ticket != nullptr ? sizeof(unsigned long long) : sizeof(float);
         for (int q = 0; q < gather->world; ++q)
             p.ext_peer[q] = make_extent(gather->y_peer[q], gather->y_stride_bytes + (unsigned long long)M * (unsigned long long)gather->N_total * elem);
         if (gather->x_words != nullptr)
             p.ext_x_words = make_extent(gather->x_words, gather->x_stride_bytes + (unsigned long long)M * (unsigned long long)gather->x_row_words * 8ull);
+#endif
     }
     if (int rc = apply_multi(p, multi, gather)) return rc;
     // Ready Q8_1 blocks whose columns are contiguous come in by bulk copy, queued by the producer thread ahead of

@@ -44,7 +44,7 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
 
     for (int64_t kb = lane; kb < nb; kb += 32) {
         const uint8_t *wblk = w + (n * nb + kb) * Q4_BYTES;
-        if (!in_extent(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
+        if (!JQ_IN_EXTENT(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
         const float d4 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(wblk));
         uint32_t wq[4];
 #pragma unroll
@@ -54,7 +54,7 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
             const int64_t m = m0 + c;
             if (m < M) {
                 const uint8_t *xb = xq + q8_block_index(kb >> 2, m, n_super, M, order) * Q8_BYTES;
-                if (!in_extent(bounds.xq, xb, Q8_BYTES, bounds.fault)) continue;
+                if (!JQ_IN_EXTENT(bounds.xq, xb, Q8_BYTES, bounds.fault)) continue;
                 const int sub = (int)(kb & 3);
                 const int4 *xi = reinterpret_cast<const int4 *>(xb + Q8_QS_OFFSET + sub * QK);
                 const int4 lo = __ldg(xi), hi = __ldg(xi + 1);
@@ -79,7 +79,7 @@ mmq_generic_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
         float v = acc[c];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
-        if (lane == 0 && m0 + c < M && in_extent(bounds.y, y + (m0 + c) * N + n, sizeof(float), bounds.fault)) y[(m0 + c) * N + n] = v;
+        if (lane == 0 && m0 + c < M && JQ_IN_EXTENT(bounds.y, y + (m0 + c) * N + n, sizeof(float), bounds.fault)) y[(m0 + c) * N + n] = v;
     }
 }
 
@@ -92,11 +92,11 @@ block_sums_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq,
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = i / nb, kb = i - n * nb;
         const uint8_t *wblk = w + i * Q4_BYTES;
-        if (!in_extent(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
+        if (!JQ_IN_EXTENT(bounds.w, wblk, Q4_BYTES, bounds.fault)) continue;
         for (int64_t m = 0; m < M; ++m) {
             const uint8_t *xb = xq + q8_block_index(kb >> 2, m, n_super, M, order) * Q8_BYTES;
-            if (!in_extent(bounds.xq, xb, Q8_BYTES, bounds.fault) ||
-                !in_extent(bounds.y, sums + (m * N + n) * nb + kb, sizeof(int32_t), bounds.fault))
+            if (!JQ_IN_EXTENT(bounds.xq, xb, Q8_BYTES, bounds.fault) ||
+                !JQ_IN_EXTENT(bounds.y, sums + (m * N + n) * nb + kb, sizeof(int32_t), bounds.fault))
                 continue;
             const int *xi = reinterpret_cast<const int *>(xb + Q8_QS_OFFSET + (kb & 3) * QK);
             int x8[8];

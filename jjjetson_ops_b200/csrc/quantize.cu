@@ -48,7 +48,7 @@ quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq
                 ks[u] = b - row[u] * n_super;
                 const int64_t k = (int64_t)ks[u] * SUPER + lane * 4;
                 const float *src = x + (int64_t)row[u] * K + k;
-                if (k < K && in_extent(bounds.x, src, sizeof(float4), bounds.fault)) xi[u] = __ldg(reinterpret_cast<const float4 *>(src));
+                if (k < K && JQ_IN_EXTENT(bounds.x, src, sizeof(float4), bounds.fault)) xi[u] = __ldg(reinterpret_cast<const float4 *>(src));
             }
         }
 #pragma unroll
@@ -58,7 +58,7 @@ quantize_q8_1_kernel_sm100(const float *__restrict__ x, uint8_t *__restrict__ xq
             uint32_t ds;
             const uint32_t q = quantize_group_q8_1(xi[u], s_mode, &ds);
             uint8_t *blk = xq + q8_block_index(ks[u], row[u], n_super_, M, order) * Q8_BYTES;
-            if (!in_extent(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
+            if (!JQ_IN_EXTENT(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
             reinterpret_cast<uint32_t *>(blk + Q8_QS_OFFSET)[lane] = q;
             if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = ds;
         }
@@ -93,7 +93,7 @@ quantize_q8_1_pairs_kernel_sm100(const float *__restrict__ x, uint8_t *__restric
                 row[u] = p / n_pairs_row;
                 pr[u] = p - row[u] * n_pairs_row;
                 const float4 *src = reinterpret_cast<const float4 *>(x + (int64_t)row[u] * K + (int64_t)pr[u] * (2 * SUPER)) + 2 * lane;
-                if (in_extent(bounds.x, src, 2 * sizeof(float4), bounds.fault)) {
+                if (JQ_IN_EXTENT(bounds.x, src, 2 * sizeof(float4), bounds.fault)) {
                     xa[u] = __ldg(src);
                     xb[u] = __ldg(src + 1);
                 }
@@ -109,7 +109,7 @@ quantize_q8_1_pairs_kernel_sm100(const float *__restrict__ x, uint8_t *__restric
             quantize_8_per_lane_q8_1(v, s_mode, &q, &ds);
             const int64_t ks = 2 * (int64_t)pr[u] + (lane >> 4);  // this lane's block of the pair
             uint8_t *blk = xq + q8_block_index(ks, row[u], n_super_, M, order) * Q8_BYTES;
-            if (!in_extent(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
+            if (!JQ_IN_EXTENT(bounds.xq, blk, Q8_BYTES, bounds.fault)) continue;
             reinterpret_cast<uint2 *>(blk + Q8_QS_OFFSET)[lane & 15] = q;
             if ((lane & 3) == 0) reinterpret_cast<uint32_t *>(blk)[(lane & 15) >> 2] = ds;
         }
