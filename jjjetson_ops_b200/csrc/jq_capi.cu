@@ -703,6 +703,7 @@ int jq_device_fault(int clear, int *fault_out) {
     if (clear && v != 0) {
         const int zero = 0;
         JQ_CUDA_TRY(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
+        if (int rc = reset_gemm_f16_split_state()) return rc;
     }
     if (fault_out) *fault_out = v;
     if (v == 3)

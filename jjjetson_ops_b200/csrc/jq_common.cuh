@@ -161,6 +161,9 @@ int launch_gemm_tc(cudaStream_t st, const void *d_w, const void *d_xq, float *d_
                    int64_t N, int64_t M, int order);
 int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K,
                     int64_t N, int64_t M, int order);
+// Zeroes the per-tile counts of the fp16-operand GEMM's split-K epilogue (a kernel that gave up may have left them
+// half-way); called when the fault word is cleared.
+int reset_gemm_f16_split_state();
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__

@@ -106,7 +106,19 @@ struct HfParams {
     int K, order, n_super;
     uint32_t row_bytes;
     unsigned long long *trace;  // tracing aid (or nullptr): SM clock stamps of CTA (0,0), rows of 8
+    // Split K (few output tiles, long K): blockIdx.z takes the 128-value chunks [z * chunks_per_split, ...) and the
+    // splits of a tile add their partial results to y in the order of z (so the sum is formed the same way every
+    // time): tile_sem[tile] counts the epilogue warps that have finished, split z goes ahead at 16 * z, the last
+    // warp of the last split puts the count back to zero.
+    int k_splits, chunks_per_split;
+    int *tile_sem;
+    uint32_t poll_limit;
 };
+
+// Counts of finished epilogue warps per output tile (split K); zero between launches.  Part of the library image, like
+// the fault word: launches that split K must not overlap on one device (they do not on one stream).
+constexpr int HF_MAX_SPLIT_TILES = 128;
+__device__ int g_tile_sem[HF_MAX_SPLIT_TILES];
 
 // Tracing aid.  Row c (stage, < 64) of block `who`: 0 = weight warp 0, 1 = activation warp 4, 2 = the MMA thread.
 // Producer columns: 0 loop top, 1 past the barrier, 2 copies of stage c + 2 issued, 3 operand stage free,
@@ -250,7 +262,9 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t n0 = (int64_t)blockIdx.x * HF_BN, m0 = (int64_t)blockIdx.y * HF_BM;
-    const int n_chunks = p.K / SUPER;
+    // this CTA's chunks of K: c counts them from 0 (ring slots, parities), c0 + c is the chunk of the matrix (copies)
+    const int c0 = (int)blockIdx.z * p.chunks_per_split;
+    const int n_chunks = min(p.chunks_per_split, p.K / SUPER - c0);
 
     if (tid == 0) {
         for (int s = 0; s < HF_STAGES; ++s) {
@@ -358,11 +372,53 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
             for (int j = 0; j < 32; ++j) sts_f32(stage_blk + (lane * HF_OUT_PITCH + j) * 4, __uint_as_float(v[j]));
             __syncwarp();
             const int64_t n = n0 + cb * 32 + lane;
+            const int z = (int)blockIdx.z;
+            int *sem = p.k_splits > 1 ? p.tile_sem + (blockIdx.y * gridDim.x + blockIdx.x) : nullptr;
+            bool go = true;
+            if (z > 0) {
+                // the splits below this one have added their parts: all sixteen warps of each
+                if (lane == 0) {
+                    go = false;
+                    for (uint32_t spin = 0; spin < p.poll_limit && !go; ++spin) {
+                        int seen;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(sem) : "memory");
+                        go = seen >= HF_PROD_WARPS * z;
+                    }
+                    if (!go) report_fault(p.fault, 1);
+                }
+                go = __shfl_sync(0xFFFFFFFFu, go ? 1 : 0, 0) != 0;
+                __threadfence();  // every lane's reads of y come after the count was seen
+            }
+            if (z > 0) {
+                // all of this lane's partial sums of the earlier splits are requested before the first is used
+                float prev[32];
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) {
+                    prev[rr] = 0.0f;
+                    if (go && m_first + rr < p.M && n < p.N && JQ_IN_EXTENT(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
+                        prev[rr] = __ldcg(p.y + (m_first + rr) * p.N + n);
+                }
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) {
+                    const float val = __uint_as_float(lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4)) + prev[rr];
+                    if (go && m_first + rr < p.M && n < p.N && JQ_IN_EXTENT(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
+                        p.y[(m_first + rr) * p.N + n] = val;
+                }
+            } else {
 #pragma unroll 8
-            for (int rr = 0; rr < 32; ++rr) {
-                const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
-                if (m_first + rr < p.M && n < p.N && JQ_IN_EXTENT(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
-                    p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
+                for (int rr = 0; rr < 32; ++rr) {
+                    const uint32_t val = lds_u32(stage_blk + (rr * HF_OUT_PITCH + lane) * 4);
+                    if (m_first + rr < p.M && n < p.N && JQ_IN_EXTENT(p.ext_y, p.y + (m_first + rr) * p.N + n, sizeof(float), p.fault))
+                        p.y[(m_first + rr) * p.N + n] = __uint_as_float(val);
+                }
+            }
+            if (sem != nullptr) {
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();
+                    const int before = atomicAdd(sem, 1);
+                    if (before == HF_PROD_WARPS * p.k_splits - 1) atomicExch(sem, 0);  // the last warp of the last split re-arms the tile
+                }
             }
         }
     } else if (warp == HF_COPY_WARP) {
@@ -377,14 +433,14 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
                     const int pair = c >> 1, ws = pair & 1;
                     if (pair >= HF_RAWW_SLOTS && !mbar_wait_bounded(&raww_empty[ws], (uint32_t)((pair >> 1) - 1) & 1u, p.fault)) break;
                     mbar_arrive_expect_tx(&raww_full[ws], HF_RAW_SLOT_BYTES);
-                    tma_load_2d(sbase + HF_RAWW_OFF + ws * HF_RAW_SLOT_BYTES, &w_map, pair * Q8_BYTES, (int)n0, &raww_full[ws]);
+                    tma_load_2d(sbase + HF_RAWW_OFF + ws * HF_RAW_SLOT_BYTES, &w_map, ((c0 + c) >> 1) * Q8_BYTES, (int)n0, &raww_full[ws]);
                 }
                 if (xround > 0 && !mbar_wait_bounded(&rawx_empty[xs], (xround - 1) & 1u, p.fault)) break;
                 mbar_arrive_expect_tx(&rawx_full[xs], HF_RAW_SLOT_BYTES);
                 if (p.order == JQ_ORDER_KSUPER_COL) {  // the tensor is [n_super * M blocks][144 bytes]
-                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, 0, (int)((int64_t)c * p.M + m0), &rawx_full[xs]);
+                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, 0, (int)((int64_t)(c0 + c) * p.M + m0), &rawx_full[xs]);
                 } else {                               // the tensor is [M columns][n_super * 144 bytes]
-                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, c * Q8_BYTES, (int)m0, &rawx_full[xs]);
+                    tma_load_2d(sbase + HF_RAWX_OFF + xs * HF_RAW_SLOT_BYTES, &x_map, (c0 + c) * Q8_BYTES, (int)m0, &rawx_full[xs]);
                 }
                 if (++xs == HF_RAWX_SLOTS) {
                     xs = 0;
@@ -433,6 +489,13 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
 
 }  // namespace
 
+int reset_gemm_f16_split_state() {
+    void *sem = nullptr;
+    JQ_CUDA_TRY(cudaGetSymbolAddress(&sem, g_tile_sem));
+    JQ_CUDA_TRY(cudaMemset(sem, 0, sizeof(int) * HF_MAX_SPLIT_TILES));
+    return JQ_OK;
+}
+
 int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d_y, int64_t K, int64_t N, int64_t M,
                     int order) {
     // a weight row's pitch, K / 32 * 18 bytes, must be a multiple of 16 for the tensor copies
@@ -461,6 +524,22 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.n_super = (int)(K / SUPER);
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
+    p.poll_limit = wait_poll_limit();
+    // Few tiles and a long K: two CTAs per tile, each half of K (whole pairs of chunks), so that twice as many SMs
+    // convert operands; both are resident at once (the second adds to what the first stored, and waits for it).
+    // Measured at M = 128, N = 4096 (32 tiles): K = 4096 28.9 -> 26.1 us, K = 8192 52.1 -> 37.9, K = 11008 68.2 ->
+    // 46.5; three and four splits are no faster (44.3, 46.4 us at K = 11008): every further split adds an ordered
+    // pass over the tile in y.
+    const int n_chunks = (int)(K / SUPER);
+    const int splits = gx * gy * 2 <= caps.sm_count && gx * gy <= HF_MAX_SPLIT_TILES && n_chunks >= 32 ? 2 : 1;
+    p.chunks_per_split = ((n_chunks + splits - 1) / splits + 1) / 2 * 2;
+    p.k_splits = (n_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    p.tile_sem = nullptr;
+    if (p.k_splits > 1) {
+        void *sem = nullptr;
+        JQ_CUDA_TRY(cudaGetSymbolAddress(&sem, g_tile_sem));
+        p.tile_sem = static_cast<int *>(sem);
+    }
     CUtensorMap w_map, x_map;
     if (int rc = encode_byte_map(&w_map, d_w, p.row_bytes, (uint64_t)N, p.row_bytes, Q8_BYTES, 128)) return rc;
     const uint64_t x_row = (uint64_t)p.n_super * Q8_BYTES;
@@ -470,7 +549,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
         return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_f16_kernel), HF_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
-    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy), HF_THREADS, HF_SMEM_BYTES, st>>>(p, w_map, x_map);
+    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)p.k_splits), HF_THREADS, HF_SMEM_BYTES, st>>>(p, w_map, x_map);
     JQ_CUDA_TRY(cudaGetLastError());
     return JQ_OK;
 }

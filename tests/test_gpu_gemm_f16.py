@@ -99,3 +99,23 @@ def test_gemm_f16_matches_integer_kernel_closely(env):
     y_int = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_MMA).cpu().numpy()
     y_f16 = c.mul_mat_q4_0_q8_1(d_w, d_xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_F16).cpu().numpy()
     assert env.O.err_max_rel(y_f16, y_int) <= TOL_F16_FORMULA
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 128), (11008, 4096, 128), (8192, 300, 70), (2048, 1000, 64)])
+def test_gemm_f16_split_k_is_ordered(env, K, N, M):
+    """Few output tiles and a long K: the kernel splits K over several CTAs per tile, which add their parts to y in a
+    fixed order.  Right against the oracle (a sample of rows at the large sizes), and bit-equal from run to run."""
+    c = env.c
+    rng = np.random.default_rng(K + N + M)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    wq = env.O.quantize_q4_0(w)
+    rows = None if N <= 1000 else np.sort(rng.choice(N, size=96, replace=False))
+    _check(env, wq, x, K, N, M, c.ORDER_COL_KSUPER, c.S_D_SUM_Q, rows)
+    xq = env.up(env.O.quantize_q8_1(x, c.ORDER_COL_KSUPER, c.S_D_SUM_Q))
+    d_w = env.up(wq)
+    runs = [c.mul_mat_q4_0_q8_1(d_w, xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_F16).cpu().numpy() for _ in range(4)]
+    for y in runs[1:]:
+        assert np.array_equal(y, runs[0])
+    exact = c.mul_mat_q4_0_q8_1(d_w, xq, K, N, M, c.ORDER_COL_KSUPER, c.KERNEL_GEMM_MMA).cpu().numpy()
+    assert env.O.err_max_rel(runs[0], exact) <= TOL_F16_FORMULA
