@@ -1291,7 +1291,12 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
         }
     } else {
         switch (nsb) {
-            case 1: return run_dp4a<2, 1, 8, 1>(st, p, caps);
+            case 1:
+                // two columns keep 64 activation words per lane: 12 + 1 warps of 128 registers fit the register file.
+                // cfg2, medians of 5 x 128 steps, consumer warps 8 / 10 / 12 / 14: fused linear 9.41 / 9.12 / 8.71 /
+                // 9.10 us, multiply on ready blocks 8.42 / 8.32 / 8.58 / 9.00 us
+                if (p.x_f32 != nullptr) return run_dp4a<2, 1, 12, 1>(st, p, caps);
+                return run_dp4a<2, 1, 10, 1>(st, p, caps);
             case 2: return run_dp4a<2, 2, 7, 1>(st, p, caps);
             default: break;
         }
