@@ -1284,8 +1284,12 @@ int launch_gemv_dp4a(cudaStream_t st, const void *d_w, const void *d_xq, const f
                 // (20 consumer warps instead of 16 fit the register file and change nothing: 6.22 us either way)
                 if (p.x_f32 != nullptr || x_words) return run_dp4a<1, 1, 16, 1>(st, p, caps);
                 return run_dp4a<1, 1, 8, 2>(st, p, caps);
-            case 2: return run_dp4a<1, 2, 8, 1>(st, p, caps);
-            case 3: return run_dp4a<1, 3, 7, 1>(st, p, caps);  // 7 + 1 warps: 255 registers per thread
+            case 2:
+                // long slabs stream better with 12 consumer warps (K = 8192, N = 28672 on ready blocks: 22.9 -> 21.6 us),
+                // short ones start faster with 8 (N = 4096: 6.56 against 7.01 us)
+                if (N >= 16384) return run_dp4a<1, 2, 12, 1>(st, p, caps);
+                return run_dp4a<1, 2, 8, 1>(st, p, caps);
+            case 3: return run_dp4a<1, 3, 7, 1>(st, p, caps);  // (9 consumer warps: K = 11008, N = 4096 7.3 -> 9.6 us)
             case 4: return run_dp4a<1, 4, 7, 1>(st, p, caps);
             default: break;
         }
