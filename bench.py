@@ -386,8 +386,11 @@ def run_ours(args) -> None:
             dist.all_gather_into_tensor(gather, d_y)
 
     def preamble():
-        # Untimed steps ahead of the timed ones.  The processes replay their graphs some tens of microseconds apart:
-        # a step that needs every rank's previous output makes the early ranks wait here, not inside the timed region.
+        # Untimed steps ahead of the timed ones, inside the same graph: the first timed step then follows a step, as
+        # every other one does (it is launched while its predecessor drains), and the first event is recorded on a
+        # branch of the capture.  With several ranks the processes replay their graphs some tens of microseconds
+        # apart: a step that needs every rank's previous output makes the early ranks wait here, not inside the
+        # timed region.
         if tagged is not None:
             tagged.linear(weights[R - 1], K, rank * N, N, x=d_x)  # the chain's first step has activations of its own
             step(R - 1)
@@ -400,7 +403,7 @@ def run_ours(args) -> None:
     seconds, used_graph = time_graph_steps(
         torch, step, args.steps, args.warmup, barrier,
         finalize=tagged.read if tagged is not None else (bands.wait if bands is not None else None),
-        preamble=preamble if world > 1 else None)
+        preamble=preamble)
     sampler.stop()
     if dist is not None:
         t = torch.tensor([seconds], dtype=torch.float64, device=dev)
