@@ -213,6 +213,10 @@ def time_graph_steps(torch, step_fn, steps, warmup, barrier, finalize=None, prea
     they then bracket the device time of the K steps and not the launch latency of the graph itself (about 10 us on
     the device, which at K = 20 steps of 7 us is 7 % of the region).  `preamble` is queued, untimed, ahead of the
     timed steps (a chain of steps that feed one another needs a first step with an input of its own)."""
+    if preamble is None:
+        def preamble():  # one untimed step ahead of the timed ones: the first timed step then follows a step, like the rest
+            step_fn(steps)
+
     stream = torch.cuda.Stream()
     side = torch.cuda.Stream()
     with torch.cuda.stream(stream):
