@@ -113,6 +113,7 @@ struct HfParams {
     int k_splits, chunks_per_split;
     int *tile_sem;
     uint32_t poll_limit;
+    int static_weights;  // the weight copies may start before the previous kernel in the stream has finished
 };
 
 // Counts of finished epilogue warps per output tile (split K); zero between launches.  Part of the library image, like
@@ -300,6 +301,9 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    // Programmatic dependent launch: everything above ran while the previous kernel (the activation quantizer, as a
+    // rule) was still finishing; the activations are read, and the outputs written, only after it has.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp < HF_PROD_WARPS) {
         // =============================== producers, then epilogue ==============================
@@ -362,6 +366,7 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
         // instruction writes 128 contiguous bytes of one output row
         if (alive && __all_sync(0xFFFFFFFFu, mbar_wait_bounded(acc_full, 0u, p.fault))) {
             tc_fence_after();
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // (long past: orders the stores to y after the previous kernel)
             const int cb = warp >> 2;  // which 32 of the 128 weight rows
             const uint32_t stage_blk = sbase + warp * (32 * HF_OUT_PITCH * 4);
             const int64_t m_first = m0 + (warp & 3) * 32;
@@ -428,8 +433,14 @@ gemm_q4_0_q8_1_f16_kernel(const HfParams p, const __grid_constant__ CUtensorMap 
         if (lane == 0) {
             int xs = 0;
             uint32_t xround = 0;
+            if (!p.static_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int c = 0; c < n_chunks; ++c) {
-                if ((c & 1) == 0) {
+                if (c == 0 && p.static_weights) {
+                    // the first pair of weight chunks is requested ahead of the wait for the previous kernel
+                    mbar_arrive_expect_tx(&raww_full[0], HF_RAW_SLOT_BYTES);
+                    tma_load_2d(sbase + HF_RAWW_OFF, &w_map, (c0 >> 1) * Q8_BYTES, (int)n0, &raww_full[0]);
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                } else if ((c & 1) == 0) {
                     const int pair = c >> 1, ws = pair & 1;
                     if (pair >= HF_RAWW_SLOTS && !mbar_wait_bounded(&raww_empty[ws], (uint32_t)((pair >> 1) - 1) & 1u, p.fault)) break;
                     mbar_arrive_expect_tx(&raww_full[ws], HF_RAW_SLOT_BYTES);
@@ -525,6 +536,7 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
     p.row_bytes = (uint32_t)(K / QK * Q4_BYTES);
     p.trace = static_cast<unsigned long long *>(next_trace_slot());
     p.poll_limit = wait_poll_limit();
+    p.static_weights = option_value(JQ_OPT_STATIC_WEIGHTS) != 0 ? 1 : 0;
     // Few tiles and a long K: two CTAs per tile, each half of K (whole pairs of chunks), so that twice as many SMs
     // convert operands; both are resident at once (the second adds to what the first stored, and waits for it).
     // Measured at M = 128, N = 4096 (32 tiles): K = 4096 28.9 -> 26.1 us, K = 8192 52.1 -> 37.9, K = 11008 68.2 ->
@@ -549,8 +561,17 @@ int launch_gemm_f16(cudaStream_t st, const void *d_w, const void *d_xq, float *d
         return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void *>(gemm_q4_0_q8_1_f16_kernel), HF_SMEM_BYTES)) return rc;
     (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be taken for this launch's
-    gemm_q4_0_q8_1_f16_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)p.k_splits), HF_THREADS, HF_SMEM_BYTES, st>>>(p, w_map, x_map);
-    JQ_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)gx, (unsigned)gy, (unsigned)p.k_splits);
+    cfg.blockDim = dim3(HF_THREADS);
+    cfg.dynamicSmemBytes = HF_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_q4_0_q8_1_f16_kernel, p, w_map, x_map));
     return JQ_OK;
 }
 
