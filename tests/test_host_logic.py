@@ -110,3 +110,27 @@ def test_sharded_linear_gathers_on_two_gloo_ranks():
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(r[1] for r in results) and all(r[2] == (3, 160) for r in results)
     assert sorted(r[3] for r in results) == [(0, 64), (64, 160)]  # 5 units of 32 rows: 2 + 3
+
+
+@pytest.mark.parametrize("K,n_total,world", [(4096, 22016, 2), (4096, 88064, 8), (8192, 28672, 4), (4096, 4096, 8), (11008, 11008, 2)])
+def test_segments_of_samples_every_band(K, n_total, world):
+    """The activations a tagged sharded layer reads from the previous layer's gathered output: runs of 8 columns spread
+    evenly over the row, as bench.py asks for them.  The mapping must stay inside the row, keep 16-byte alignment of the
+    8-byte words (even offsets), take exactly K columns and touch every rank's band."""
+    import torch
+
+    from jjjetson_ops_b200.sharded import segments_of
+
+    seg_len = 8
+    stride = (n_total // (K // seg_len)) // 2 * 2
+    assert stride >= seg_len and stride % 2 == 0
+    assert (K // seg_len - 1) * stride + seg_len <= n_total
+    y = torch.arange(2 * n_total, dtype=torch.float32).reshape(2, n_total)
+    x = segments_of(y, K, seg_len, stride)
+    assert x.shape == (2, K)
+    cols = x[0].to(torch.int64)
+    k = torch.arange(K)
+    assert torch.equal(cols, (k // seg_len) * stride + k % seg_len)
+    assert torch.equal(x[1], x[0] + n_total)
+    band = n_total // world
+    assert set((cols // band).tolist()) == set(range(world))
