@@ -242,7 +242,7 @@ void *mapped_alias(const void *host_ptr) {
 // With a single block it can also publish a completion ticket in mapped host memory, which the
 // host polls instead of paying a stream synchronisation's wake-up latency.
 __global__ void copy_f32_kernel(float *__restrict__ dst, const float *__restrict__ src, int64_t n,
-                                volatile unsigned *done_flag, unsigned ticket) {
+                                volatile unsigned *done_flag, unsigned *count) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
@@ -257,8 +257,11 @@ __global__ void copy_f32_kernel(float *__restrict__ dst, const float *__restrict
         __threadfence_system();
         __syncthreads();
         if (threadIdx.x == 0) {
-            // ticket == 0: count completions on the device (lets a captured graph be replayed)
-            *done_flag = ticket != 0 ? ticket : *done_flag + 1;
+            // completions are counted on the device (a captured graph can be replayed, and the count in host memory
+            // is only ever written over the bus, never read)
+            const unsigned c = *count + 1u;
+            *count = c;
+            *done_flag = c;
             __threadfence_system();
         }
     }
@@ -856,6 +859,7 @@ struct jq_weights {
     // completion ticket in pinned, mapped host memory (written by the copy kernel, polled by the host)
     unsigned *h_done = nullptr;
     unsigned *d_done = nullptr;
+    unsigned *d_count = nullptr;  // the completion count kept on the device (the copy kernel never reads the one in host memory)
     unsigned ticket = 0;
     // the three launches of a zero-copy call (quantize, multiply, copy back) as one graph, built the
     // second time the same buffers and batch size are seen
@@ -886,6 +890,11 @@ int jq_weights_create(const void *host_w_q4_0, int64_t N, int64_t K, jq_weights 
     if (e == cudaSuccess && cudaHostAlloc(reinterpret_cast<void **>(&w->h_done), 64, cudaHostAllocMapped) == cudaSuccess) {
         *w->h_done = 0;
         if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&w->d_done), w->h_done, 0) != cudaSuccess) w->d_done = nullptr;
+        if (w->d_done != nullptr && (cudaMalloc(reinterpret_cast<void **>(&w->d_count), sizeof(unsigned)) != cudaSuccess ||
+                                     cudaMemset(w->d_count, 0, sizeof(unsigned)) != cudaSuccess)) {
+            (void)cudaGetLastError();
+            w->d_done = nullptr;
+        }
     } else {
         (void)cudaGetLastError();  // no ticket: completion falls back to stream synchronisation
     }
@@ -907,6 +916,7 @@ int jq_weights_destroy(jq_weights *w) {
     cudaFree(w->d_y);
     if (w->graph) cudaGraphExecDestroy(w->graph);
     if (w->h_done) cudaFreeHost(w->h_done);
+    cudaFree(w->d_count);
     if (w->stream) cudaStreamDestroy(w->stream);
     delete w;
     return JQ_OK;
@@ -943,7 +953,7 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
     const bool zero_copy_out = w->y_alias != nullptr && y_count * sizeof(float) <= (1u << 20) && ((uintptr_t)w->y_alias & 15u) == 0;
     const bool ticketed = zero_copy_in && zero_copy_out && y_count <= 65536 && w->d_done != nullptr && quant_workspace == nullptr;
 
-    auto enqueue = [&](unsigned ticket) -> int {
+    auto enqueue = [&]() -> int {
         if (zero_copy_in) {
             if (int rc = launch_quantize_q8_1(w->stream, w->x_alias, w->d_ws, w->K, M, JQ_ORDER_COL_KSUPER, s_mode)) return rc;
             if (int rc = dispatch_mul_mat(w->stream, w->d_w, w->d_ws, static_cast<float *>(w->d_y), w->K, w->N, M,
@@ -971,7 +981,7 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
             cfg.numAttrs = 1;
             volatile unsigned *flag = ticketed ? w->d_done : nullptr;
             JQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, copy_f32_kernel, w->y_alias, static_cast<const float *>(w->d_y),
-                                           (int64_t)y_count, flag, ticket));
+                                           (int64_t)y_count, flag, w->d_count));
         } else {
             JQ_CUDA_TRY(cudaMemcpyAsync(y, w->d_y, y_count * sizeof(float), cudaMemcpyDeviceToHost, w->stream));
         }
@@ -996,7 +1006,7 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
             // third call with the same buffers: record the three launches once, replay them from now on
             cudaGraph_t g = nullptr;
             if (cudaStreamBeginCapture(w->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-                const int rc = enqueue(0u);
+                const int rc = enqueue();
                 const cudaError_t e = cudaStreamEndCapture(w->stream, &g);
                 if (rc == JQ_OK && e == cudaSuccess && g != nullptr) {
                     if (cudaGraphInstantiate(&w->graph, g, 0) != cudaSuccess) w->graph = nullptr;
@@ -1013,7 +1023,7 @@ int jq_linear_q4_0_host(jq_weights *w, const float *x, uint8_t *quant_workspace,
     unsigned expect = 0;
     if (ticketed) expect = w->ticket + 1;  // the flag counts completed ticketed calls
     if (!launched) {
-        if (int rc = enqueue(0u)) {
+        if (int rc = enqueue()) {
             // part of the call may be queued: drain it and take the count as it stands, so that the next
             // call's expectation matches the device again
             cudaStreamSynchronize(w->stream);
