@@ -599,6 +599,14 @@ __device__ __forceinline__ void dp4a_slice(const uint32_t (&wv)[18], const int (
     }
 }
 
+// The consumer warps of a CTA meet on an mbarrier (one arrival per warp) with a bounded wait: a warp whose wait for a
+// stage ran out has left the kernel, and the others must not wait for it for ever, as they would at a hardware barrier.
+__device__ __forceinline__ bool consumers_meet(uint64_t *bar, int lane, int *fault, uint32_t limit) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    return mbar_wait_bounded(bar, 0u, fault, limit);
+}
+
 template <int M_T, int NSB, int NW, int MINB>
 __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -607,6 +615,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     uint64_t *x_ready = full + 24;
     uint64_t *x_full = full + 25;
     unsigned long long *ticket_slot = reinterpret_cast<unsigned long long *>(full + 26);
+    uint64_t *meet = full + 27;  // two meetings of the consumer warps in the all-gather epilogues
     float *ybuf = reinterpret_cast<float *>(smem + GV_BAR_BYTES);
     uint8_t *xs = smem + GV_BAR_BYTES + p.y_bytes;
     uint8_t *ring = xs + p.x_bytes;
@@ -619,6 +628,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         }
         mbar_init(x_ready, NW);
         mbar_init(x_full, 1);
+        mbar_init(meet, NW);
+        mbar_init(meet + 1, NW);
         fence_mbar_init();
         // Tagged all-gather: this launch's number comes from a count that every launch raises by 65536, a share per
         // CTA.  The next launch in the stream starts only after every CTA of this one has passed the trigger below,
@@ -821,7 +832,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
         // ---- all-gather epilogue, tagged words: each value and the number of this all-gather in one 8-byte store
         // to every rank's buffer.  Nothing follows the stores: no flag, no release, nobody waits here.
         const GatherArgs &ga = p.gather;
-        named_bar_sync(1, NW * 32);  // the band of this CTA is complete in shared memory
+        if (!consumers_meet(meet, lane, p.fault, p.poll_limit)) return;  // the band of this CTA is complete in shared memory
         const int rows_cta = (int)(r_end - r_begin);
         for (int idx = warp; idx < ga.world * p.M; idx += NW) {
             const int hop = idx / p.M, m = idx - hop * p.M;
@@ -839,7 +850,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     } else if (p.gather.world > 0) {
         // ---- all-gather epilogue: this CTA's rows of the band go to every rank's buffer ----------
         const GatherArgs &ga = p.gather;
-        named_bar_sync(1, NW * 32);  // the band of this CTA is complete in shared memory
+        if (!consumers_meet(meet, lane, p.fault, p.poll_limit)) return;  // the band of this CTA is complete in shared memory
         const int rows_cta = (int)(r_end - r_begin);
         for (int idx = warp; idx < ga.world * p.M; idx += NW) {
             const int q = idx / p.M, m = idx - q * p.M;
@@ -851,7 +862,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                 if (JQ_IN_EXTENT(p.ext_peer[q], dst + i, sizeof(float), p.fault)) dst[i] = src[i];
             }
         }
-        named_bar_sync(1, NW * 32);  // all of this CTA's peer stores have been issued
+        if (!consumers_meet(meet + 1, lane, p.fault, p.poll_limit)) return;  // all of this CTA's peer stores have been issued
         if (warp == 0) {
             // Tell every rank that this CTA's part of the band is there: a release at system scope (cumulative
             // over the stores that the barrier ordered before it) adding this CTA's share to the count the
