@@ -329,6 +329,10 @@ def run_ours(args) -> None:
     # inference setting: weights are uploaded once and never rewritten, so consecutive steps may
     # overlap the next step's weight stream with the previous step's tail
     capi.set_option(capi.OPT_STATIC_WEIGHTS, 0 if args.no_overlap else 1)
+    if world > 1:
+        # a step waits on the device for the other ranks' output; the processes reach their first launches up to some
+        # hundred milliseconds apart (set-up, graph capture), so the bounded waits get 2^25 polls (seconds, not hours)
+        capi.set_option(capi.OPT_WAIT_POLL_LIMIT, 1 << 25)
     peaks = measured_peaks()
     M = args.m
     if args.shape == "cfg4":
