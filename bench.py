@@ -1001,6 +1001,8 @@ def measure_extras(torch, capi, synth, dev, peaks):
     # cfg5: the five projections of one Llama-7B decoder layer as one dependent chain in one graph
     for Mc in (1, 128):
         out["cfg5_chain_M%d" % Mc] = bench_layer_chain(torch, capi, synth, dev, peaks, Mc)
+        # the same pass the way the model container runs it: gate | up as one matrix, like q | k | v
+        out["cfg5_chain_M%d_gate_up_fused" % Mc] = bench_layer_chain(torch, capi, synth, dev, peaks, Mc, fuse_gate_up=True)
 
     # lm_head as a quantized GEMV: a 32000 x 4096 table (Llama-2 vocabulary), 73.7 MB
     t = bench_linear(4096, 32000, 1, steps=100, fused=False)
@@ -1265,11 +1267,13 @@ def bench_layer_dataflow(torch, capi, synth, dev, peaks, M):
     return res
 
 
-def bench_layer_chain(torch, capi, synth, dev, peaks, M):
+def bench_layer_chain(torch, capi, synth, dev, peaks, M, fuse_gate_up=False):
     """QKV 4096->12288, O 4096->4096 (fed the first 4096 columns of the QKV output), gate and up
     4096->11008 (fed the O output), down 11008->4096 (fed a synthetic N(0,1) tensor, as configuration 5
     says).  Every step quantizes its own input.  Several independent layers' worth of weights rotate
-    so that each pass streams its weights from HBM."""
+    so that each pass streams its weights from HBM.  With ``fuse_gate_up`` the gate and up matrices, which
+    read the same input and lie back to back in the model container, run as one 4096->22016 call the way
+    QKV does: four launches a pass, the same bytes and operations."""
     rng = np.random.default_rng(4)
     shapes = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate", 4096, 11008), ("up", 4096, 11008), ("down", 11008, 4096)]
     layer_bytes = sum(capi.q4_0_bytes(n, k) for _, k, n in shapes)
@@ -1291,6 +1295,11 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
     y_o = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
     y_gate = torch.zeros((M, 11008), dtype=torch.float32, device=dev)
     y_up = torch.zeros((M, 11008), dtype=torch.float32, device=dev)
+    y_gate_up = torch.zeros((M, 22016), dtype=torch.float32, device=dev) if fuse_gate_up else None
+    if fuse_gate_up:
+        for ws in layers:  # gate | up adjacent, as jq_model_q4_0 lays them out
+            ws[2] = torch.cat([ws[2], ws[3]], dim=0).contiguous()
+            ws[3] = None
     y_down = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
     o_in = torch.zeros((M, 4096), dtype=torch.float32, device=dev)
 
@@ -1303,8 +1312,11 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
             o_in.copy_(y_qkv[:, :4096])
             o_src = o_in
         capi.linear_q4_0(w[1], o_src, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_o)
-        capi.linear_q4_0(w[2], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_gate)
-        capi.linear_q4_0(w[3], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_up)
+        if fuse_gate_up:
+            capi.linear_q4_0(w[2], y_o, 22016, capi.S_D_SUM_Q, ws=scratch, out=y_gate_up)
+        else:
+            capi.linear_q4_0(w[2], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_gate)
+            capi.linear_q4_0(w[3], y_o, 11008, capi.S_D_SUM_Q, ws=scratch, out=y_up)
         capi.linear_q4_0(w[4], xdown, 4096, capi.S_D_SUM_Q, ws=scratch, out=y_down)
 
     steps = 40 if M == 1 else 10
@@ -1315,7 +1327,8 @@ def bench_layer_chain(torch, capi, synth, dev, peaks, M):
     del layers
     torch.cuda.empty_cache()
     return {"us": t * 1e6, "GB/s": alg / t / 1e9, "frac_hbm": alg / t / 1e9 / peaks["hbm_gbs"], "TOPS": ops / t / 1e12,
-            "launches_per_pass": "5 linears" + ("" if M == 1 else " (+1 slice copy)"), "weight_copies": R}
+            "launches_per_pass": ("4 linears (gate and up as one 4096->22016 call)" if fuse_gate_up else "5 linears")
+            + ("" if M == 1 else " (+1 slice copy)"), "weight_copies": R}
 
 
 def run_case(args) -> None:
