@@ -607,7 +607,7 @@ __device__ __forceinline__ bool consumers_meet(uint64_t *bar, int lane, int *fau
     return mbar_wait_bounded(bar, 0u, fault, limit);
 }
 
-template <int M_T, int NSB, int NW, int MINB>
+template <int M_T, int NSB, int NW, int MINB, bool TAGGED>
 __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -660,7 +660,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
 
     // Activations may come from, and outputs may be read by, the previous kernel.  Activations that arrive as
     // tagged words order themselves: that kernel does not wait for its predecessor before its last instruction.
-    const bool tagged = p.gather.ticket != nullptr;
+    // (The tagged form is an instance of its own: in one kernel its stores in the row loop cost the plain form two
+    // registers and half a percent.)
+    constexpr bool tagged = TAGGED;  // p.gather.ticket != nullptr
     const bool x_tagged = tagged && p.gather.x_words != nullptr;
     if (!x_tagged) griddep_wait();
     uint32_t gather_epoch = 0;  // number of this all-gather (previous ones finished: *epoch_ptr)
@@ -733,6 +735,22 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     const bool single_mat = p.n_mats <= 1;
     float *const y_cta = p.gather.world > 0 ? ybuf : (single_mat ? p.y + r_begin : nullptr);
     const size_t y_pitch = p.gather.world > 0 ? (size_t)p.y_rows : (size_t)p.N;
+    // Tagged words leave as their rows finish: lane j of each half-warp stores to rank (rank + 1 + j) % world (the
+    // ranks start on different peers; the local copy comes last), so the words are on their way while the rest of
+    // the slab is still being multiplied, and nothing is left to push at the end.
+    unsigned long long *word_dst = nullptr;
+#ifdef JQ_BOUNDS_CHECK
+    int word_peer = 0;
+#endif
+    if (tagged && (lane & 15) < p.gather.world) {
+        const int q = (p.gather.rank + 1 + (lane & 15)) % p.gather.world;
+        word_dst = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(p.gather.y_peer[q]) +
+                                                          (size_t)(gather_epoch & 1u) * p.gather.y_stride_bytes) +
+                   p.gather.n_offset + r_begin;
+#ifdef JQ_BOUNDS_CHECK
+        word_peer = q;
+#endif
+    }
     const uint32_t row_off = (uint32_t)warp * p.row_bytes + (uint32_t)lane * 72u;
     int s = 0;
     uint32_t parity = 0;
@@ -800,7 +818,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
                 float v = (upper ? accB[m] : accA[m]) + __shfl_xor_sync(0xFFFFFFFFu, give, 16, 32);
 #pragma unroll
                 for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off, 32);
-                if ((lane & 15) == 0 && m < p.M && (upper ? hasB : hasA)) {
+                if (tagged) {
+                    if (word_dst != nullptr && m < p.M && (upper ? hasB : hasA)) {
+                        unsigned long long *dst = word_dst + (size_t)m * p.gather.N_total + (size_t)rel;
+                        if (JQ_IN_EXTENT(p.ext_peer[word_peer], dst, sizeof(unsigned long long), p.fault)) st_word(dst, v, gather_epoch);
+                    }
+                } else if ((lane & 15) == 0 && m < p.M && (upper ? hasB : hasA)) {
                     if (y_cta != nullptr) {  // the band's staging buffer in shared memory, or a single matrix's output
 #ifdef JQ_BOUNDS_CHECK
                         float *dst = y_cta + (size_t)m * y_pitch + (size_t)rel;
@@ -831,20 +854,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, MINB) gemv_dp4a_kernel(const Ge
     if (tagged) {
         // ---- all-gather epilogue, tagged words: each value and the number of this all-gather in one 8-byte store
         // to every rank's buffer.  Nothing follows the stores: no flag, no release, nobody waits here.
-        const GatherArgs &ga = p.gather;
-        if (!consumers_meet(meet, lane, p.fault, p.poll_limit)) return;  // the band of this CTA is complete in shared memory
-        const int rows_cta = (int)(r_end - r_begin);
-        for (int idx = warp; idx < ga.world * p.M; idx += NW) {
-            const int hop = idx / p.M, m = idx - hop * p.M;
-            const int q = (ga.rank + 1 + hop) % ga.world;  // the ranks start on different peers; the local copy comes last
-            unsigned long long *dst = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(ga.y_peer[q]) +
-                                                                             (size_t)(gather_epoch & 1u) * ga.y_stride_bytes) +
-                                      (size_t)m * ga.N_total + ga.n_offset + r_begin;
-            const float *src = ybuf + (size_t)m * p.y_rows;
-            for (int i = lane; i < rows_cta; i += 32) {
-                if (JQ_IN_EXTENT(p.ext_peer[q], dst + i, sizeof(unsigned long long), p.fault)) st_word(dst + i, src[i], gather_epoch);
-            }
-        }
+        // (the words went out row by row)
         if (threadIdx.x == 0) trace_fine(p, 6);  // warp 0: its stores are issued
         griddep_wait();  // a launch never ends before the one ahead of it
     } else if (p.gather.world > 0) {
@@ -1127,7 +1137,7 @@ int run_dp4a(cudaStream_t st, GemvParams &p, const DeviceCaps &caps) {
 #ifdef JQ_BOUNDS_CHECK
     p.smem_total = (uint32_t)smem;
 #endif
-    auto kernel = gemv_dp4a_kernel<M_T, NSB, NW, MINB>;
+    auto kernel = p.gather.ticket != nullptr ? gemv_dp4a_kernel<M_T, NSB, NW, MINB, true> : gemv_dp4a_kernel<M_T, NSB, NW, MINB, false>;
     if (int rc = ensure_smem_attr(kernel, smem)) return rc;
     const int64_t want = (p.N + p.rows_per_stage - 1) / p.rows_per_stage;
     const int grid = (int)min((int64_t)caps.sm_count * MINB, max((int64_t)1, want));
