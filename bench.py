@@ -373,7 +373,7 @@ def run_ours(args) -> None:
         from jjjetson_ops_b200.sharded import TaggedBands, segments_of
 
         tagged = TaggedBands(M, N * world, dev)
-        x_stride = (N * world // (K // 8)) // 2 * 2  # runs of 8 words spread evenly over the whole gathered row
+        x_stride = (N * world // (K // 8)) // 4 * 4  # runs of 8 words spread evenly over the whole gathered row
         collective = ("fused, tagged words; each step's activations are read from the previous step's gathered output "
                       "(8 words out of every %d: every CTA of every rank feeds every CTA of the next step)" % x_stride)
     elif collective in ("fused", "fused_flags"):
@@ -746,7 +746,7 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
         if M <= 2:
             # the decode form: tagged words, every step fed by the gathered output of the step before it
             tb = TaggedBands(M, n_total, dev)
-            seg, seg_stride = 8, (n_total // (K // 8)) // 2 * 2
+            seg, seg_stride = 8, (n_total // (K // 8)) // 4 * 4
             def step_tagged(i):
                 tb.linear(shards[i % R], K, rank * N, N, source=tb, seg_len=seg, seg_stride=seg_stride)
 
@@ -853,7 +853,7 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
         _, k, n = shapes[j]
         src = tch[feeds[j]]
         if source_words:
-            tch[j].linear(w, k, rank * (n // world), n // world, source=src, seg_len=8, seg_stride=(src.N_total // (k // 8)) // 2 * 2,
+            tch[j].linear(w, k, rank * (n // world), n // world, source=src, seg_len=8, seg_stride=(src.N_total // (k // 8)) // 4 * 4,
                           back=backs[j])
         else:
             tch[j].linear(w, k, rank * (n // world), n // world, x=x)
@@ -880,7 +880,7 @@ def measure_sharded_extras(torch, capi, synth, dev, dist, rank, world, peaks):
     for j in range(5):
         _, k, n = shapes[j]
         src = outs[feeds[j]]
-        x_in = segments_of(src, k, 8, (src.shape[1] // (k // 8)) // 2 * 2)
+        x_in = segments_of(src, k, 8, (src.shape[1] // (k // 8)) // 4 * 4)
         tagged_layer(j, wl[j])
         outs[j] = tch[j].read().clone()
         want = capi.linear_q4_0(wl[j], x_in, n // world, capi.S_D_SUM_Q)

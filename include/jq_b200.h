@@ -249,7 +249,9 @@ int jq_allgather_wait_device(void *stream, const void *d_flags, int world, const
  *                    that, e.g. the second of two projections fed by the same output): row m, activation k is
  *                    word m * x_row_words + (k / x_seg_len) * x_seg_stride + k % x_seg_len of buffer (g & 1).
  *                    x_seg_len = K takes the first K words of a row; K / world words from the start of every
- *                    rank's band make the call depend on all ranks.
+ *                    rank's band make the call depend on all ranks.  x_seg_len is a multiple of 8, x_seg_stride
+ *                    and x_row_words are even; when both are multiples of 4 (and the buffers 32-byte aligned)
+ *                    the words are polled with 32-byte loads, which halves the polling time.
  * A call that consumes words needs no other ordering.  A call with plain d_x that follows other tagged calls
  * must come after a jq_allgather_tagged_read_device (or a stream synchronisation after one) so that no rank
  * overwrites a buffer another rank still reads.  All ranks make the same sequence of calls.  Waits are bounded

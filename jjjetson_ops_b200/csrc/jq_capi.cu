@@ -609,6 +609,7 @@ int jq_linear_q4_0_allgather_tagged_device(void *stream, const void *d_w, const 
         ga.x_seg_len = (int)x_seg_len;
         ga.x_seg_stride = x_seg_stride;
         ga.x_back = x_back;
+        ga.x_wide = (x_seg_stride & 3) == 0 && (x_row_words & 3) == 0 && ((uintptr_t)d_x_words & 31u) == 0 && (x_stride_bytes & 31u) == 0;
     }
     ga.world = world;
     ga.rank = rank;

@@ -129,6 +129,7 @@ struct GatherArgs {
     int64_t x_row_words = 0;                      // words per row there (that all-gather's N_total)
     int x_seg_len = 0;                            // activation k of a row is word (k / x_seg_len) * x_seg_stride +
     int64_t x_seg_stride = 0;                     // k % x_seg_len of that row (x_seg_len a multiple of 8)
+    int x_wide = 0;                               // every lane's eight words start on a 32-byte boundary: 256-bit loads
 };
 
 // Waits (bounded) on the stream until all `world` flags have reached *d_epoch.

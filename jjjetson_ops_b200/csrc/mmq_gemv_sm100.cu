@@ -210,6 +210,14 @@ __device__ __forceinline__ uint4 ld_words2(const unsigned long long *src) {
     return r;
 }
 
+// four neighbouring words (32-byte aligned) in one load
+__device__ __forceinline__ void ld_words4(const unsigned long long *src, uint4 *lo, uint4 *hi) {
+    unsigned long long a0, a1, a2, a3;
+    asm volatile("ld.volatile.global.v4.u64 {%0, %1, %2, %3}, [%4];" : "=l"(a0), "=l"(a1), "=l"(a2), "=l"(a3) : "l"(src) : "memory");
+    *lo = make_uint4((uint32_t)a0, (uint32_t)(a0 >> 32), (uint32_t)a1, (uint32_t)(a1 >> 32));
+    *hi = make_uint4((uint32_t)a2, (uint32_t)(a2 >> 32), (uint32_t)a3, (uint32_t)(a3 >> 32));
+}
+
 // Every word of all-gather number *ticket >> 16 -> plain fp32, each thread waiting (bounded) for its own words.
 __global__ void __launch_bounds__(256) allgather_tagged_read_kernel(const unsigned long long *words, uint64_t stride_bytes,
                                                                     int64_t n_words, const unsigned long long *ticket,
@@ -443,8 +451,15 @@ __device__ __forceinline__ void stage_activations(const GemvParams &p, uint8_t *
             bool ok = false;
             const bool readable = JQ_IN_EXTENT(p.ext_x_words, src, 8 * sizeof(unsigned long long), p.fault);
             for (uint32_t spin = 0; readable && spin < p.poll_limit && !ok; ++spin) {
+                if (ga.x_wide) {
+                    // A thread's strong loads are carried out one after the other (four 16-byte loads of words that
+                    // were all there took 3 us on a loaded GPU, two 32-byte loads 1.9 us), so as few as possible.
+                    ld_words4(src, &w[0], &w[1]);
+                    ld_words4(src + 4, &w[2], &w[3]);
+                } else {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) w[u] = ld_words2(src + 2 * u);
+                    for (int u = 0; u < 4; ++u) w[u] = ld_words2(src + 2 * u);
+                }
                 ok = true;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) ok = ok && w[u].y == x_tag && w[u].w == x_tag;

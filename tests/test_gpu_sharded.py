@@ -100,7 +100,7 @@ def test_bounded_wait_gives_up_and_reports(native_lib, oracle, cuda_device):
 
 
 @pytest.mark.parametrize("K,N,M,K2,seg", [(4096, 11008, 1, 4096, None), (2048, 4096, 2, 1024, 256), (4096, 2080, 1, 2048, 512),
-                                          (8192, 8192, 1, 8192, None)])
+                                          (8192, 8192, 1, 8192, None), (4096, 11008, 1, 4096, -8), (2048, 4098, 2, 1024, 256)])
 def test_tagged_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M, K2, seg):
     """The decode form on one GPU (world = 1: ticket, tagged stores, polling loads and the reader all run,
     with itself as the only peer).  Layer 1 takes plain activations; layer 2 takes its activations from
@@ -116,8 +116,11 @@ def test_tagged_allgather_single_rank(native_lib, oracle, cuda_device, K, N, M, 
     wq1 = oracle.quantize_q4_0((rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)).astype(np.float32))
     wq2 = oracle.quantize_q4_0((rng.standard_normal((N2, K2), dtype=np.float32) * np.float32(0.02)).astype(np.float32))
     d_w1, d_w2 = torch.from_numpy(wq1).to(cuda_device), torch.from_numpy(wq2).to(cuda_device)
-    seg_len = K2 if seg is None else seg
-    seg_stride = 0 if seg is None else (N - seg_len) // (K2 // seg_len - 1) // 32 * 32
+    # a lane's eight words are read as two 32-byte loads when every run of words starts on a 32-byte boundary (the run
+    # distance and the row length multiples of four words), else as four 16-byte loads: seg = -8 gives runs of eight
+    # words every 18 words, and a row of 4098 words puts the second row of a batch of two off the boundary
+    seg_len = K2 if seg is None else abs(seg)
+    seg_stride = 0 if seg is None else (18 if seg < 0 else (N - seg_len) // (K2 // seg_len - 1) // 32 * 32)
     a = TaggedBands(M, N, cuda_device)
     b = TaggedBands(M, N2, cuda_device, share_with=a)
     try:

@@ -116,14 +116,14 @@ def test_sharded_linear_gathers_on_two_gloo_ranks():
 def test_segments_of_samples_every_band(K, n_total, world):
     """The activations a tagged sharded layer reads from the previous layer's gathered output: runs of 8 columns spread
     evenly over the row, as bench.py asks for them.  The mapping must stay inside the row, keep 16-byte alignment of the
-    8-byte words (even offsets), take exactly K columns and touch every rank's band."""
+    8-byte words in fours (offsets that are multiples of 4, so that a lane's eight words can be read as two 32-byte loads), take exactly K columns and touch every rank's band."""
     import torch
 
     from jjjetson_ops_b200.sharded import segments_of
 
     seg_len = 8
-    stride = (n_total // (K // seg_len)) // 2 * 2
-    assert stride >= seg_len and stride % 2 == 0
+    stride = (n_total // (K // seg_len)) // 4 * 4
+    assert stride >= seg_len and stride % 4 == 0
     assert (K // seg_len - 1) * stride + seg_len <= n_total
     y = torch.arange(2 * n_total, dtype=torch.float32).reshape(2, n_total)
     x = segments_of(y, K, seg_len, stride)
