@@ -215,7 +215,8 @@ class TaggedBands:
         """Queue one fused step.  The activations are the plain tensor ``x``, or an all-gather of ``source``:
         the one queued just before this call (``back`` = 0) or ``back`` calls earlier.  Activation ``k`` is
         word ``(k // seg_len) * seg_stride + k % seg_len`` of its row (``seg_len`` defaults to ``K``: the first
-        ``K`` words)."""
+        ``K`` words).  ``seg_len`` is a multiple of 8 and ``seg_stride`` even; with ``seg_stride`` and the source's
+        ``N_total`` multiples of 4 the kernel polls with 32-byte loads, which is faster."""
         capi = self._capi
         if (x is None) == (source is None):
             raise ValueError("exactly one of x and source")
