@@ -33,7 +33,7 @@ def test_synth_outliers_and_batch_prefixes():
     assert 30 <= int(big.sum()) <= 41  # 41 channels scaled by 20, the same ones in every row
 
 
-def test_algorithmic_bytes_match_the_survey_figures():
+def test_algorithmic_bytes_of_the_five_configurations():
     from jjjetson_ops_b200 import synth
 
     assert synth.algorithmic_bytes(4096, 4096, 1, fused_quantize=False) == 9458176
